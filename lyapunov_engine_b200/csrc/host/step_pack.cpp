@@ -1,0 +1,131 @@
+#include "step_pack.hpp"
+
+#include <algorithm>
+#include <stdexcept>
+#include <string>
+
+namespace lyapunov::host {
+
+PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceManager &manager,
+                     const std::vector<int> &tile_sizes, int pad_requests,
+                     const std::vector<int> &fixed_max_blocks, int32_t *dest, int64_t capacity) {
+  PackedStep p;
+  const int groups = manager.get_num_groups();
+  const int real = static_cast<int>(entries.size());
+  const int B = std::max(real, pad_requests);
+  p.num_requests = B;
+  p.num_real_requests = real;
+  p.tile_sizes = tile_sizes;
+
+  int T = 0;
+  for (const auto &e : entries) {
+    if (e.count < 1) throw std::invalid_argument("pack_step: an entry brings no token");
+    if (e.start != static_cast<int>(e.seq->get_num_computed_tokens()))
+      throw std::invalid_argument("pack_step: request " + std::to_string(e.seq->get_seq_id()) + " has " +
+                                  std::to_string(e.seq->get_num_computed_tokens()) +
+                                  " tokens in the cache but its entry starts at " + std::to_string(e.start));
+    if (static_cast<size_t>(e.start + e.count) > e.seq->get_total_len())
+      throw std::invalid_argument("pack_step: an entry runs past the request's tokens");
+    for (int32_t w : e.want)
+      if (w < 0 || w >= e.count) throw std::invalid_argument("pack_step: a wanted place lies outside the entry's tokens");
+    T += e.count;
+    p.num_wanted += static_cast<int>(e.want.size());
+    p.max_q_len = std::max(p.max_q_len, e.count);
+    p.max_context = std::max(p.max_context, e.start + e.count);
+  }
+  T += B - real;
+  if (B > real) {
+    p.max_q_len = std::max(p.max_q_len, 1);
+    p.max_context = std::max(p.max_context, 1);
+  }
+  p.num_tokens = T;
+
+  p.max_blocks.assign(groups, 1);
+  for (int g = 0; g < groups; ++g) {
+    const int bs = manager.get_block_size(g);
+    int need = 1;
+    for (const auto &e : entries) need = std::max(need, (e.start + e.count + bs - 1) / bs);
+    if (g < static_cast<int>(fixed_max_blocks.size()) && fixed_max_blocks[g] > 0) {
+      if (need > fixed_max_blocks[g]) throw std::invalid_argument("pack_step: a request needs more pages than the fixed table width");
+      need = fixed_max_blocks[g];
+    }
+    p.max_blocks[g] = need;
+  }
+
+  int64_t off = 0;
+  auto take = [&](int64_t n) { const int64_t o = off; off += (n + 3) / 4 * 4; return o; };  // 16-byte aligned parts
+  p.off_token_ids = take(T);
+  p.off_positions = take(T);
+  p.off_request_of_token = take(T);
+  p.off_cu_q = take(B + 1);
+  p.off_ctx_before = take(B);
+  p.off_state_slots = take(B);
+  p.off_wanted_rows = take(std::max(p.num_wanted, 1));
+  for (int g = 0; g < groups; ++g) p.off_block_tables.push_back(take(static_cast<int64_t>(B) * p.max_blocks[g]));
+  for (int ts : tile_sizes) {
+    if (ts < 1) throw std::invalid_argument("pack_step: tile sizes must be >= 1");
+    int n = B - real;
+    for (const auto &e : entries) n += (e.count + ts - 1) / ts;
+    p.num_tiles.push_back(n);
+    p.off_tile_request.push_back(take(n));
+    p.off_tile_q0.push_back(take(n));
+  }
+  p.total = off;
+  if (dest == nullptr) return p;
+  if (off > capacity) throw std::length_error("pack_step: the step needs " + std::to_string(off) + " integers, the buffer holds " + std::to_string(capacity));
+
+  int32_t *tok = dest + p.off_token_ids, *pos = dest + p.off_positions, *req = dest + p.off_request_of_token;
+  int32_t *cu = dest + p.off_cu_q, *ctx = dest + p.off_ctx_before, *slots = dest + p.off_state_slots;
+  int32_t *want = dest + p.off_wanted_rows;
+  int t = 0, w = 0;
+  cu[0] = 0;
+  for (int b = 0; b < B; ++b) {
+    if (b < real) {
+      const auto &e = entries[b];
+      for (int j = 0; j < e.count; ++j) {
+        tok[t + j] = e.seq->token_at(static_cast<size_t>(e.start + j));
+        pos[t + j] = e.start + j;
+        req[t + j] = b;
+      }
+      for (int32_t x : e.want) want[w++] = t + x;
+      ctx[b] = e.start;
+      slots[b] = e.seq->get_state_slot();
+      t += e.count;
+    } else {
+      tok[t] = 0; pos[t] = 0; req[t] = b;
+      ctx[b] = 0;
+      slots[b] = -1;
+      t += 1;
+    }
+    cu[b + 1] = t;
+  }
+  if (p.num_wanted == 0) want[0] = 0;
+  for (int g = 0; g < groups; ++g) {
+    int32_t *table = dest + p.off_block_tables[g];
+    const int width = p.max_blocks[g];
+    const int32_t null_page = manager.get_num_blocks(g);  // one page past the pool: the device keeps it for dummies
+    for (int b = 0; b < B; ++b) {
+      int32_t *row = table + static_cast<int64_t>(b) * width;
+      int n = 0;
+      if (b < real) {
+        const auto &tables = entries[b].seq->get_block_tables();
+        if (g < static_cast<int>(tables.size())) {
+          n = std::min<int>(width, static_cast<int>(tables[g].size()));
+          for (int i = 0; i < n; ++i) row[i] = tables[g][i] >= 0 ? tables[g][i] : null_page;
+        }
+      }
+      for (int i = n; i < width; ++i) row[i] = null_page;
+    }
+  }
+  for (size_t k = 0; k < tile_sizes.size(); ++k) {
+    int32_t *tr = dest + p.off_tile_request[k], *tq = dest + p.off_tile_q0[k];
+    int n = 0;
+    for (int b = 0; b < B; ++b) {
+      const int count = b < real ? entries[b].count : 1;
+      for (int q0 = 0; q0 < count; q0 += tile_sizes[k]) { tr[n] = b; tq[n] = q0; ++n; }
+    }
+  }
+  return p;
+}
+
+}  // namespace lyapunov::host

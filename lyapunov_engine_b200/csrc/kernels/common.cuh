@@ -1,0 +1,110 @@
+// Shared by every kernel file: the C interface's conventions, element types,
+// reductions and the device status word.
+//
+// Every launcher is `extern "C" int le_*(...)`: raw device pointers, sizes,
+// a dtype code and the CUDA stream; it returns 0 or a cudaError_t, or
+// LE_INVALID for arguments it refuses (le_last_error() then says why).  No
+// launcher allocates or synchronises.
+//
+// The reference's helpers of the same kind are csrc/include/utils/cuda_utils.cuh
+// (CUDA_CHECK, to_float/from_float, warp and block reductions).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#define LE_API extern "C" __attribute__((visibility("default")))
+
+enum : int { LE_F32 = 0, LE_BF16 = 1 };
+enum : int { LE_INVALID = -1 };
+
+// Bits of the device status word that kernels set instead of faulting.
+enum : int {
+  LE_STATUS_BAD_TOKEN = 1,     // a token id outside the vocabulary
+  LE_STATUS_BAD_PAGE = 2,      // a block table entry outside the pool
+  LE_STATUS_BAD_POSITION = 4,  // a position outside the rotary table
+  LE_STATUS_WAIT_TIMEOUT = 8,  // a bounded wait inside a kernel ran out
+};
+
+namespace le {
+
+inline char *error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+inline int invalid(const char *fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(error_buffer(), 512, fmt, args);
+  va_end(args);
+  return LE_INVALID;
+}
+
+inline int launched() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) snprintf(error_buffer(), 512, "CUDA: %s", cudaGetErrorString(e));
+  return static_cast<int>(e);
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T x);
+template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the block; every thread gets it.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float *scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float s = lane < warps ? scratch[lane] : 0.0f;
+    s = warp_sum(s);
+    if (lane == 0) scratch[32] = s;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float *scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float s = lane < warps ? scratch[lane] : -INFINITY;
+    s = warp_max(s);
+    if (lane == 0) scratch[32] = s;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+}  // namespace le
+
+#define LE_DISPATCH_DTYPE(code, T, ...)                                  \
+  do {                                                                   \
+    if ((code) == LE_F32) { using T = float; __VA_ARGS__; }              \
+    else if ((code) == LE_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+    else return le::invalid("unknown dtype code %d", (code));            \
+  } while (0)

@@ -1,0 +1,82 @@
+// Embedding gather, SwiGLU and small helpers.
+//
+// Reference counterparts: nn.Embedding (python/lyapunov_engine/models/llama.py:172,205)
+// and swiglu_kernel (csrc/kernels/fused_rmsnorm_swiglu.cu:152-179).
+#include "common.cuh"
+
+LE_API const char *le_last_error() { return le::error_buffer(); }
+
+namespace {
+
+// One block per token: row `ids[t]` of the table goes to row t of the
+// 32-bit residual stream.  An id outside the table sets the status word and
+// writes zeros instead of reading out of bounds.
+template <typename T>
+__global__ void embed_kernel(float *__restrict__ out, const T *__restrict__ table, const int32_t *__restrict__ ids,
+                             int hidden, int vocab, int *__restrict__ status) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float *dst = out + static_cast<int64_t>(t) * hidden;
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(status, LE_STATUS_BAD_TOKEN);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.0f;
+    return;
+  }
+  const T *src = table + static_cast<int64_t>(id) * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = le::to_f32(src[i]);
+}
+
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i], in 32-bit, rounded once.
+template <typename T>
+__global__ void swiglu_kernel(T *__restrict__ out, const T *__restrict__ gu, int64_t total, int inter) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int64_t t = idx / inter;
+  const int i = static_cast<int>(idx - t * inter);
+  const float g = le::to_f32(gu[t * 2 * inter + i]);
+  const float u = le::to_f32(gu[t * 2 * inter + inter + i]);
+  out[idx] = le::from_f32<T>(g / (1.0f + expf(-g)) * u);
+}
+
+template <typename TO, typename TI>
+__global__ void convert_kernel(TO *__restrict__ out, const TI *__restrict__ in, int64_t n) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = le::from_f32<TO>(le::to_f32(in[i]));
+}
+
+}  // namespace
+
+LE_API int le_embed(float *out, const void *table, int table_dtype, const int32_t *ids, int num_tokens, int hidden,
+                    int vocab, int *status, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  LE_DISPATCH_DTYPE(table_dtype, T,
+                    embed_kernel<T><<<num_tokens, threads, 0, stream>>>(out, static_cast<const T *>(table), ids, hidden, vocab, status));
+  return le::launched();
+}
+
+LE_API int le_swiglu(void *out, const void *gate_up, int dtype, int num_tokens, int inter, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int64_t total = static_cast<int64_t>(num_tokens) * inter;
+  const int threads = 256;
+  const int64_t blocks = (total + threads - 1) / threads;
+  if (blocks > 2147483647LL) return le::invalid("le_swiglu: %lld elements are too many for one launch", (long long)total);
+  LE_DISPATCH_DTYPE(dtype, T,
+                    swiglu_kernel<T><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+                        static_cast<T *>(out), static_cast<const T *>(gate_up), total, inter));
+  return le::launched();
+}
+
+// out (f32) = in (bf16) or out (bf16) = in (f32).
+LE_API int le_convert(void *out, int out_dtype, const void *in, int in_dtype, int64_t n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((n + threads - 1) / threads);
+  if (out_dtype == LE_F32 && in_dtype == LE_BF16)
+    convert_kernel<float, __nv_bfloat16><<<blocks, threads, 0, stream>>>(static_cast<float *>(out), static_cast<const __nv_bfloat16 *>(in), n);
+  else if (out_dtype == LE_BF16 && in_dtype == LE_F32)
+    convert_kernel<__nv_bfloat16, float><<<blocks, threads, 0, stream>>>(static_cast<__nv_bfloat16 *>(out), static_cast<const float *>(in), n);
+  else
+    return le::invalid("le_convert: unsupported pair of dtypes %d -> %d", in_dtype, out_dtype);
+  return le::launched();
+}

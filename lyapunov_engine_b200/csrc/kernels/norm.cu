@@ -1,0 +1,71 @@
+// RMSNorm over the 32-bit residual stream, with the residual addition fused.
+//
+//   resid[r] += delta[r]                      (when delta is given)
+//   out[r]    = resid[r] * rsqrt(mean(resid[r]^2) + eps) * weight
+//
+// Sum, mean, rsqrt and the product are 32-bit; the output is rounded once.
+// With `rows` given, only those rows are normed, into consecutive rows of
+// `out`, and the residual stream is left as it is (the final norm before the
+// output head runs on the wanted rows alone).
+//
+// Reference: rmsnorm_kernel, csrc/kernels/fused_rmsnorm_swiglu.cu:15-113 (same
+// arithmetic; its residual stream has the activations' type, ours is 32-bit).
+#include "common.cuh"
+
+namespace {
+
+template <typename TO, typename TD, int VEC>
+__global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, const TD *__restrict__ delta,
+                               const float *__restrict__ weight, const int32_t *__restrict__ rows, float eps, int hidden) {
+  __shared__ float scratch[33];
+  const int64_t src_row = rows ? rows[blockIdx.x] : blockIdx.x;
+  float *x = resid + src_row * hidden;
+  const TD *d = delta ? delta + src_row * hidden : nullptr;
+  TO *o = out + static_cast<int64_t>(blockIdx.x) * hidden;
+  const bool write_back = (d != nullptr) && (rows == nullptr);
+
+  float ss = 0.0f;
+  for (int i = threadIdx.x * VEC; i < hidden; i += blockDim.x * VEC) {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      float val = x[i + v];
+      if (d) val += le::to_f32(d[i + v]);
+      if (write_back) x[i + v] = val;
+      ss += val * val;
+    }
+  }
+  ss = le::block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / static_cast<float>(hidden) + eps);
+  for (int i = threadIdx.x * VEC; i < hidden; i += blockDim.x * VEC) {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      float val = x[i + v];
+      if (d && !write_back) val += le::to_f32(d[i + v]);
+      o[i + v] = le::from_f32<TO>(val * inv * weight[i + v]);
+    }
+  }
+}
+
+template <typename TO, typename TD>
+int launch(void *out, float *resid, const void *delta, const float *weight, const int32_t *rows, float eps,
+           int num_rows, int hidden, cudaStream_t stream) {
+  int threads = 32;
+  while (threads < 512 && threads * 8 < hidden) threads *= 2;
+  if (hidden % 4 == 0)
+    rmsnorm_kernel<TO, TD, 4><<<num_rows, threads, 0, stream>>>(static_cast<TO *>(out), resid, static_cast<const TD *>(delta), weight, rows, eps, hidden);
+  else
+    rmsnorm_kernel<TO, TD, 1><<<num_rows, threads, 0, stream>>>(static_cast<TO *>(out), resid, static_cast<const TD *>(delta), weight, rows, eps, hidden);
+  return le::launched();
+}
+
+}  // namespace
+
+// `out_dtype` is the type of `out` and of `delta` (the activations' type).
+LE_API int le_rmsnorm(void *out, int out_dtype, float *resid, const void *delta, const float *weight,
+                      const int32_t *rows, float eps, int num_rows, int hidden, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (hidden <= 0) return le::invalid("le_rmsnorm: hidden must be positive");
+  if (out_dtype == LE_F32) return launch<float, float>(out, resid, delta, weight, rows, eps, num_rows, hidden, stream);
+  if (out_dtype == LE_BF16) return launch<__nv_bfloat16, __nv_bfloat16>(out, resid, delta, weight, rows, eps, num_rows, hidden, stream);
+  return le::invalid("le_rmsnorm: unknown dtype code %d", out_dtype);
+}

@@ -1,0 +1,247 @@
+"""LLMEngine: requests in, tokens out.
+
+The reference's names and calls are kept
+(python/lyapunov_engine/engine/llm_engine.py:18-55,93-312): ``EngineConfig``,
+``RequestOutput``, ``LLMEngine.add_request`` in both call shapes,
+``has_unfinished_requests`` and ``step``; ``generate`` loops ``step`` for a
+list of prompts.  Behind them: the C++ scheduler decides each step's batch
+(portions of prompts beside decoded tokens under one token budget), the step
+function runs it, the sampler picks tokens on the device, one small transfer
+brings them back, and the scheduler finishes and frees.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import build, ops
+from ..cache import DeviceCache
+from ..config.base import read_config_json
+from ..models.model import Model
+from ..registry import spec_for
+from ..sampling import Sampler, SamplingParams
+from ..weights.loader import FolderWeights, RandomWeights
+from .runtime import Runtime, parse_dtype
+from .step import ModelRunner
+
+
+class EngineConfig:
+    """Runtime options, with the reference's names and defaults
+    (python/lyapunov_engine/engine/llm_engine.py:18-38); ``dtype`` is bfloat16
+    or float32 here, and ``max_model_len`` bounds a request's length (default:
+    the model's ``max_position_embeddings``, capped by what the pages hold)."""
+
+    def __init__(self, model_config=None, num_blocks: int = 1024, num_gpu_blocks: int | None = None,
+                 block_size: int = 16, max_num_seqs: int = 64, max_num_batched_tokens: int = 2048,
+                 dtype=torch.bfloat16, device: str = "cuda:0", max_model_len: int | None = None,
+                 max_prefill_chunk: int = 0, use_cuda_graphs: bool = True, seed: int = 0):
+        self.model_config = model_config
+        self.num_blocks = num_gpu_blocks if num_gpu_blocks is not None else num_blocks
+        self.block_size = block_size
+        self.max_num_seqs = max_num_seqs
+        self.max_num_batched_tokens = max_num_batched_tokens
+        self.dtype = parse_dtype(dtype)
+        self.device = device
+        self.max_model_len = max_model_len
+        self.max_prefill_chunk = max_prefill_chunk
+        self.use_cuda_graphs = use_cuda_graphs
+        self.seed = seed
+
+
+class RequestOutput:
+    def __init__(self, request_id, prompt_tokens, output_tokens, finished, finish_reason=None, error=None):
+        self.request_id = request_id
+        self.prompt_tokens = prompt_tokens
+        self.output_tokens = output_tokens
+        self.finished = finished
+        self.is_finished = finished
+        self.finish_reason = finish_reason   # "stop", "length", "abort" or "error"
+        self.error = error
+
+    def __repr__(self):
+        return (f"RequestOutput(request_id={self.request_id!r}, output_tokens={self.output_tokens!r}, "
+                f"finished={self.finished}, finish_reason={self.finish_reason!r})")
+
+
+class LoadedModel:
+    """A model with its weights on the device."""
+
+    def __init__(self, spec, model, runtime):
+        self.spec, self.model, self.runtime = spec, model, runtime
+        self.config = spec
+
+
+def load_model(folder: str | None = None, dtype=torch.bfloat16, device: str = "cuda:0", config: dict | None = None,
+               random_seed: int | None = None, max_model_len: int | None = None, std: float = 0.02,
+               norm_jitter: float = 0.0) -> LoadedModel:
+    """Builds the model that config.json names and binds its weights: from the
+    folder's safetensors files, or, with ``random_seed``, from that seed
+    (``config`` then gives the content of a config.json and no folder is
+    needed)."""
+    dtype = parse_dtype(dtype)
+    raw = config if config is not None else read_config_json(folder)
+    spec = spec_for(raw)
+    runtime = Runtime(device, dtype, max_model_len=max_model_len or spec.max_positions)
+    model = Model(spec)
+    decls = model.tensors()
+    with torch.cuda.device(runtime.device):
+        if random_seed is not None:
+            source = RandomWeights(decls, dtype, runtime.device, random_seed, std, norm_jitter)
+        else:
+            source = FolderWeights(folder, decls, dtype, runtime.device)
+        model.bind(source.get, runtime)
+        source.release()
+    return LoadedModel(spec, model, runtime)
+
+
+class LLMEngine:
+    def __init__(self, model: LoadedModel, config: EngineConfig | None = None, **options):
+        if config is None:
+            config = EngineConfig(**options)
+        if not isinstance(model, LoadedModel):
+            raise TypeError("LLMEngine takes a model from load_model() or LLMEngine.from_pretrained()")
+        self.config = config
+        self.loaded = model
+        self.runtime = model.runtime
+        if config.dtype != self.runtime.dtype:
+            raise ValueError(f"the model was loaded as {self.runtime.dtype}, the engine is configured as {config.dtype}")
+        self.host = build.load_host()
+        spec = model.spec
+        self.block_size = config.block_size
+        self.num_blocks = config.num_blocks
+        capacity = self.num_blocks * self.block_size
+        self.max_model_len = min(config.max_model_len or spec.max_positions, spec.max_positions,
+                                 self.runtime.max_model_len or spec.max_positions)
+        if model.model.groups:
+            self.max_model_len = min(self.max_model_len, capacity)
+        with torch.cuda.device(self.runtime.device):
+            self.cache = DeviceCache(model.model, self.runtime, self.num_blocks, self.block_size, config.max_num_seqs)
+            self.runner = ModelRunner(model.model, self.cache, self.runtime, config.max_num_batched_tokens,
+                                      config.max_num_seqs, self.max_model_len, config.use_cuda_graphs)
+            self.sampler = Sampler(self.runtime.device, config.max_num_seqs)
+        self.block_manager = self.cache.manager
+        sched = self.host.SchedulerConfig()
+        sched.max_num_seqs = config.max_num_seqs
+        sched.max_num_batched_tokens = config.max_num_batched_tokens
+        sched.max_model_len = self.max_model_len
+        sched.eos_token_ids = list(spec.eos_token_ids)
+        sched.max_prefill_chunk = config.max_prefill_chunk
+        self.scheduler = self.host.ContinuousScheduler(sched, self.block_manager)
+        self.req_counter = 0
+        self.active_sequences: dict[int, tuple] = {}
+        self._tokens_host = torch.empty(config.max_num_seqs + 1, dtype=torch.int32, pin_memory=True)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    # ---- construction in one call
+    @classmethod
+    def from_pretrained(cls, model_dir: str, dtype=torch.bfloat16, device: str = "cuda:0", **options) -> "LLMEngine":
+        config = EngineConfig(dtype=dtype, device=device, **options)
+        loaded = load_model(model_dir, config.dtype, device, max_model_len=config.max_model_len)
+        return cls(loaded, config)
+
+    # ---- the reference's interface
+    def add_request(self, arg1, arg2=None, arg3=None):
+        """``add_request(prompt_tokens, sampling_params)`` or
+        ``add_request(request_id, prompt_tokens, sampling_params)``."""
+        if isinstance(arg1, (int, str)) and isinstance(arg2, (list, tuple)):
+            request_id, prompt_tokens, sampling = arg1, list(arg2), arg3 or SamplingParams()
+        elif isinstance(arg1, (list, tuple)):
+            request_id = self.req_counter
+            prompt_tokens = list(arg1)
+            sampling = arg2 if isinstance(arg2, SamplingParams) else SamplingParams()
+        else:
+            raise TypeError("add_request(prompt_tokens, sampling_params) or add_request(request_id, prompt_tokens, sampling_params)")
+        if not prompt_tokens:
+            raise ValueError("the prompt is empty")
+        vocab = self.loaded.spec.vocab_size
+        for t in prompt_tokens:
+            if not 0 <= int(t) < vocab:
+                raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
+        seq_id = self.req_counter
+        self.req_counter += 1
+        c = self.host.SamplingParams()
+        c.temperature, c.top_p, c.top_k = sampling.temperature, sampling.top_p, sampling.top_k
+        c.max_tokens, c.ignore_eos, c.seed = sampling.max_tokens, sampling.ignore_eos, int(sampling.seed) & (2**64 - 1)
+        seq = self.host.Sequence(seq_id, [int(t) for t in prompt_tokens], c)
+        self.scheduler.add_sequence(seq)
+        self.active_sequences[seq_id] = (seq, sampling, request_id)
+        return request_id
+
+    def abort_request(self, request_id) -> None:
+        for seq_id, (seq, _, rid) in list(self.active_sequences.items()):
+            if rid == request_id:
+                self.scheduler.abort_sequence(seq_id)
+                del self.active_sequences[seq_id]
+
+    def has_unfinished_requests(self) -> bool:
+        return self.scheduler.has_unfinished_sequences()
+
+    def step(self) -> list[RequestOutput]:
+        """One scheduler step: returns an output for every request that was in
+        the step (and for those that failed or were finished by it)."""
+        if not self.has_unfinished_requests():
+            return []
+        out = self.scheduler.schedule()
+        outputs: list[RequestOutput] = []
+        for seq in out.finished_seqs:
+            outputs.append(self._output(seq))
+        if not out.entries:
+            return outputs
+        with torch.cuda.device(self.runtime.device):
+            logits = self.runner.step(out.entries)
+            sampled = out.sampled_seqs
+            tokens: list[int] = []
+            n = len(sampled)
+            if n:
+                params = [self.active_sequences[s.get_seq_id()][1] for s in sampled]
+                indices = [s.get_total_len() for s in sampled]
+                ids = self.sampler.sample(logits, params, indices)
+                # one transfer: the chosen ids and the kernels' status word
+                both = torch.cat([ids, self.runtime.status[:1]])
+                self._tokens_host[:n + 1].copy_(both, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                host = self._tokens_host[:n + 1].tolist()
+                tokens, status = host[:n], host[n]
+                self.d2h_bytes += 4 * (n + 1)
+                if status:
+                    ops.check_status(self.runtime.status)
+        self.scheduler.post_step(out, tokens)
+        for seq in out.scheduled_seqs:
+            outputs.append(self._output(seq))
+        return outputs
+
+    def _output(self, seq) -> RequestOutput:
+        seq_id = seq.get_seq_id()
+        _, _, request_id = self.active_sequences.get(seq_id, (None, None, seq_id))
+        finished = seq.is_finished()
+        o = RequestOutput(request_id, seq.get_prompt_tokens(), seq.get_output_tokens(), finished,
+                          seq.finish_reason() if finished else None, seq.get_error() or None)
+        if finished:
+            self.active_sequences.pop(seq_id, None)
+        return o
+
+    # ---- convenience
+    def generate(self, prompts, sampling_params=None) -> list[RequestOutput]:
+        """Runs every prompt (lists of token ids) to its end and returns the
+        outputs in the order of the prompts.  ``sampling_params``: one for all,
+        or one per prompt."""
+        if prompts and isinstance(prompts[0], int):
+            prompts = [prompts]
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params or SamplingParams()] * len(prompts)
+        order = []
+        for i, (p, sp) in enumerate(zip(prompts, sampling_params)):
+            order.append(self.add_request(f"generate-{self.req_counter}-{i}", list(p), sp))
+        done: dict = {}
+        while self.has_unfinished_requests():
+            for o in self.step():
+                if o.finished and o.request_id in order:
+                    done[o.request_id] = o
+        return [done[r] for r in order]
+
+    def stats(self) -> dict:
+        s = self.scheduler.get_stats()
+        return {"steps": s.steps, "prefill_tokens": s.prefill_tokens, "decode_tokens": s.decode_tokens,
+                "preemptions": s.preemptions, "failed": s.failed, "graph_steps": self.runner.num_graph_steps,
+                "free_blocks": self.block_manager.get_num_free_blocks() if self.loaded.model.groups else 0,
+                "cache_bytes": self.cache.bytes()}

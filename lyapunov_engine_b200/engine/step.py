@@ -1,0 +1,193 @@
+"""The step function: run the tokens of one batch through the model, from the
+cache, and return the logits at the wanted places.
+
+A batch is a list of entries (request, its next tokens [start, start + count),
+the places among them whose logits are wanted).  Portions of prompts stand
+beside single decoded tokens, cut anywhere; all of them run as one batch of
+T = sum(count) rows.  The host sends one block of integers per step
+(``pack_step``); everything else already lives on the device.
+
+Steps that hold single decoded tokens only can run as a captured CUDA graph of
+fixed shape (the batch padded to the next bucket), which removes the launch
+cost of the ~10 kernels per layer.
+
+The reference's step (python/lyapunov_engine/engine/llm_engine.py:219-312)
+runs whole prompts one by one or one token per request, never a mix.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import build, ops
+from ..parts import attention_kernels
+
+
+class StepContext:
+    """The step's integers on the device (views into one buffer) and the few
+    numbers the host keeps."""
+    __slots__ = ("num_tokens", "num_requests", "num_wanted", "max_q_len", "max_context", "pure_decode",
+                 "token_ids", "positions", "request_of_token", "cu_q", "ctx_before", "state_slots", "wanted_rows",
+                 "block_tables", "tiles", "workspace", "status", "q_lens")
+
+
+class ModelRunner:
+    def __init__(self, model, cache, runtime, max_num_batched_tokens: int, max_num_seqs: int, max_model_len: int,
+                 use_cuda_graphs: bool = True, check_status: bool = False):
+        self.host = build.load_host()
+        self.model, self.cache, self.runtime = model, cache, runtime
+        self.max_num_batched_tokens, self.max_num_seqs, self.max_model_len = max_num_batched_tokens, max_num_seqs, max_model_len
+        self.use_cuda_graphs = use_cuda_graphs
+        self.check_status = check_status
+        self.tile_sizes = attention_kernels.tile_sizes()
+        self.fixed_max_blocks = [(max_model_len + cache.block_size - 1) // cache.block_size for _ in model.groups]
+        self._capacity = 0
+        self._ring: list = []
+        self._ring_pos = 0
+        self._device_ints = None
+        self._graphs: dict[int, "_DecodeGraph"] = {}
+        self.num_steps = 0
+        self.num_graph_steps = 0
+        self._reserve(self._upper_bound(max_num_batched_tokens, max_num_seqs))
+
+    # ---- integer buffers
+    def _upper_bound(self, tokens: int, requests: int) -> int:
+        n = 4 * tokens + 16 * (requests + 1)
+        n += sum(requests * w for w in self.fixed_max_blocks)
+        for ts in self.tile_sizes:
+            n += 2 * (tokens // ts + requests + 4)
+        return n + 64
+
+    def _reserve(self, n: int) -> None:
+        if n <= self._capacity:
+            return
+        self._capacity = n
+        self._ring = [(torch.empty(n, dtype=torch.int32, pin_memory=True), torch.cuda.Event()) for _ in range(4)]
+        for _, ev in self._ring:
+            ev.record()
+        self._device_ints = torch.empty(n, dtype=torch.int32, device=self.runtime.device)
+        self._graphs.clear()  # they point into the old buffer
+
+    def _pack(self, entries, pad_requests=0, fixed=False, all_wanted=False):
+        fixed_blocks = self.fixed_max_blocks if fixed else []
+        layout = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks, 0, 0)
+        if layout.total > self._capacity:
+            self._reserve(int(layout.total * 1.5))
+        pinned, event = self._ring[self._ring_pos]
+        self._ring_pos = (self._ring_pos + 1) % len(self._ring)
+        event.synchronize()
+        layout = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks,
+                                     pinned.data_ptr(), self._capacity)
+        if all_wanted:
+            n = layout.num_requests
+            pinned.numpy()[layout.off_wanted_rows:layout.off_wanted_rows + n] = np.arange(n, dtype=np.int32)
+        self._device_ints[:layout.total].copy_(pinned[:layout.total], non_blocking=True)
+        event.record()
+        return layout
+
+    def _context(self, layout, workspace, num_wanted=None) -> StepContext:
+        d = self._device_ints
+        T, B = layout.num_tokens, layout.num_requests
+        c = StepContext()
+        c.num_tokens, c.num_requests = T, B
+        c.num_wanted = layout.num_wanted if num_wanted is None else num_wanted
+        c.max_q_len, c.max_context = layout.max_q_len, layout.max_context
+        c.pure_decode = layout.max_q_len == 1
+        c.token_ids = d[layout.off_token_ids:layout.off_token_ids + T]
+        c.positions = d[layout.off_positions:layout.off_positions + T]
+        c.request_of_token = d[layout.off_request_of_token:layout.off_request_of_token + T]
+        c.cu_q = d[layout.off_cu_q:layout.off_cu_q + B + 1]
+        c.ctx_before = d[layout.off_ctx_before:layout.off_ctx_before + B]
+        c.state_slots = d[layout.off_state_slots:layout.off_state_slots + B]
+        c.wanted_rows = d[layout.off_wanted_rows:layout.off_wanted_rows + max(c.num_wanted, 1)][:c.num_wanted]
+        c.block_tables = [d[o:o + B * w].view(B, w) for o, w in zip(layout.off_block_tables, layout.max_blocks)]
+        c.tiles = {ts: (d[a:a + n], d[b:b + n], n) for ts, a, b, n in
+                   zip(layout.tile_sizes, layout.off_tile_request, layout.off_tile_q0, layout.num_tiles)}
+        c.workspace = workspace
+        c.status = self.runtime.status
+        return c
+
+    # ---- the step
+    def step(self, entries):
+        """Runs the entries as one batch.  Returns float32 logits [wanted, vocab]
+        in the order of the entries and of their ``want`` lists, or None when
+        nothing is wanted.  The tensor is scratch: it is overwritten by the
+        next step."""
+        if not entries:
+            return None
+        self.num_steps += 1
+        total = sum(e.count for e in entries)
+        if total > self.max_num_batched_tokens:
+            raise ValueError(f"the step brings {total} tokens, max_num_batched_tokens is {self.max_num_batched_tokens}")
+        if len(entries) > self.max_num_seqs:
+            raise ValueError(f"the step brings {len(entries)} requests, max_num_seqs is {self.max_num_seqs}")
+        decode_only = all(e.count == 1 for e in entries)
+        if self.use_cuda_graphs and decode_only:
+            logits = self._graph_step(entries)
+        else:
+            layout = self._pack(entries)
+            ctx = self._context(layout, self.runtime.workspace)
+            logits = self.model.forward(ctx, self.cache)
+        if self.check_status:
+            ops.check_status(self.runtime.status)
+        return logits
+
+    # ---- decode steps as CUDA graphs
+    def _bucket(self, n: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        return min(b, max(self.max_num_seqs, n))
+
+    def _graph_step(self, entries):
+        bucket = self._bucket(len(entries))
+        graph = self._graphs.get(bucket)
+        if graph is None:
+            graph = _DecodeGraph(self, bucket, entries)
+            self._graphs[bucket] = graph
+        self.num_graph_steps += 1
+        logits = graph.run(entries)
+        rows = [i for i, e in enumerate(entries) if len(e.want)]
+        if not rows:
+            return None
+        if len(rows) == len(entries):
+            return logits[:len(entries)]
+        return logits[torch.tensor(rows, device=logits.device)]
+
+
+class _DecodeGraph:
+    """One captured decode step for a fixed number of rows."""
+
+    def __init__(self, runner: ModelRunner, bucket: int, entries):
+        from .runtime import Workspace
+
+        self.runner, self.bucket = runner, bucket
+        self.workspace = Workspace(runner.runtime.device, pin_old=True)
+        self.capacity_at_capture = runner._capacity
+        # The first call runs eagerly (it warms every kernel and library up
+        # with the real entries, so nothing is computed twice), the second is
+        # captured.
+        self.graph = None
+        self.logits = None
+
+    def run(self, entries):
+        r = self.runner
+        layout = r._pack(entries, pad_requests=self.bucket, fixed=True, all_wanted=True)
+        if r._capacity != self.capacity_at_capture:
+            raise RuntimeError("the integer buffer moved after a decode graph was captured")
+        if self.graph is None:
+            ctx = r._context(layout, self.workspace, num_wanted=self.bucket)
+            if self.logits is None:
+                self.logits = r.model.forward(ctx, r.cache)   # eager warm-up on the real data
+                self._warm = True
+                return self.logits
+            # Capture.  The step's integers are already on the device; the
+            # captured kernels read them from the same addresses every time.
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.logits = r.model.forward(ctx, r.cache)
+            self.graph = graph
+            # Capturing does not run the kernels: replay for this step's result.
+        self.graph.replay()
+        return self.logits

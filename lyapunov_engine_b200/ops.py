@@ -1,0 +1,276 @@
+"""Thin Python layer over the kernel libraries (ctypes, raw device pointers).
+
+Every function here launches hand-written sm_100a kernels on the current torch
+stream and returns at once.  There is no eager or CPU fallback: tensors must be
+CUDA tensors, and when a library cannot be built or loaded the call raises.
+The reference pairs every kernel with an eager fallback inside the same
+function (python/lyapunov_engine/ops.py:12-216); here the plain twins live in
+the tests only.
+
+Matrix products in bfloat16 go to the library (cuBLAS through torch), as the
+reference's do (nn.Linear, python/lyapunov_engine/models/llama.py:45-48,112-117,177);
+32-bit products use the package's own FP32 kernel, never a tensor-core mode.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a block table entry outside the page pool",
+               4: "a position outside the rotary table", 8: "a bounded wait inside a kernel ran out"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, got {dtype}")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("lyapunov_engine_b200 kernels run on CUDA tensors only (there is no CPU path)")
+
+
+_core = None
+_attention: dict[int, ctypes.CDLL] = {}
+
+_CORE_SIGNATURES = {
+    "le_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "le_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "le_convert": [c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p],
+    "le_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p],
+    "le_rope_kv_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "le_gemm_simt": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
+                     c_void_p],
+    "le_argmax": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p],
+    "le_sample": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_void_p, c_void_p],
+}
+_ATTENTION_SIGNATURES = {
+    "le_attention_generic": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_float, c_void_p, c_void_p],
+}
+
+
+def _declare(lib, signatures):
+    for name, args in signatures.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue
+        fn.argtypes = args
+        fn.restype = c_int
+    lib.le_last_error_fn = getattr(lib, "le_last_error", None)
+    if lib.le_last_error_fn is not None:
+        lib.le_last_error_fn.restype = ctypes.c_char_p
+
+
+def core():
+    global _core
+    if _core is None:
+        lib = build.load_core()
+        _declare(lib, _CORE_SIGNATURES)
+        _core = lib
+    return _core
+
+
+def attention_lib(head_dim: int):
+    lib = _attention.get(head_dim)
+    if lib is None:
+        lib = build.load_attention(head_dim)
+        _declare(lib, _ATTENTION_SIGNATURES)
+        _declare(lib, _EXTRA_ATTENTION_SIGNATURES)
+        _attention[head_dim] = lib
+    return lib
+
+
+_EXTRA_ATTENTION_SIGNATURES: dict[str, list] = {}
+
+
+def _check(code: int, name: str, lib=None):
+    if code != 0:
+        lib = lib or core()
+        detail = ""
+        fn = getattr(lib, "le_last_error_fn", None) or getattr(core(), "le_last_error_fn", None)
+        if fn is not None:
+            detail = (fn() or b"").decode(errors="replace")
+        raise KernelError(f"{name} failed ({code}): {detail}")
+
+
+def new_status(device) -> torch.Tensor:
+    """The status word kernels set instead of faulting on bad indices."""
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor) -> None:
+    """Reads the status word (this waits for the device) and raises if a kernel
+    met an index it refused to follow."""
+    word = int(status[0].item())
+    if word:
+        status.zero_()
+        what = "; ".join(text for bit, text in STATUS_BITS.items() if word & bit)
+        raise KernelError(f"a kernel refused bad input: {what}")
+
+
+# --------------------------------------------------------------------------
+def embed(out_resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> None:
+    """out_resid[t] (float32) = table[ids[t]]."""
+    _need_cuda(out_resid, table, ids)
+    T, H = out_resid.shape
+    assert out_resid.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == H
+    assert out_resid.is_contiguous() and table.is_contiguous()
+    _check(core().le_embed(_ptr(out_resid), _ptr(table), dtype_code(table.dtype), _ptr(ids), T, H, table.shape[0],
+                           _ptr(status), _stream()), "le_embed")
+
+
+def swiglu(out: torch.Tensor, gate_up: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _need_cuda(out, gate_up)
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and out.is_contiguous() and gate_up.is_contiguous()
+    assert out.dtype == gate_up.dtype
+    _check(core().le_swiglu(_ptr(out), _ptr(gate_up), dtype_code(out.dtype), T, I, _stream()), "le_swiglu")
+
+
+def convert(out: torch.Tensor, src: torch.Tensor) -> None:
+    _need_cuda(out, src)
+    assert out.numel() == src.numel() and out.is_contiguous() and src.is_contiguous()
+    _check(core().le_convert(_ptr(out), dtype_code(out.dtype), _ptr(src), dtype_code(src.dtype), out.numel(),
+                             _stream()), "le_convert")
+
+
+def rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, rows=None) -> None:
+    """resid += delta (when given and ``rows`` is None); out = rmsnorm(resid) * weight.
+    With ``rows`` (int32 indices) only those rows are normed, into out[0..len(rows))."""
+    _need_cuda(out, resid, delta, weight, rows)
+    H = resid.shape[1]
+    n = out.shape[0]
+    assert resid.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == H
+    assert out.shape[1] == H and out.is_contiguous() and resid.is_contiguous()
+    if delta is not None:
+        assert delta.dtype == out.dtype and delta.shape == resid.shape and delta.is_contiguous()
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.numel() >= n
+    else:
+        assert n == resid.shape[0]
+    _check(core().le_rmsnorm(_ptr(out), dtype_code(out.dtype), _ptr(resid), _ptr(delta), _ptr(weight), _ptr(rows),
+                             float(eps), n, H, _stream()), "le_rmsnorm")
+
+
+def rope_kv_write(qkv, k_cache, v_cache, cos_sin, positions, request_of_token, block_table, num_heads, num_kv_heads,
+                  head_dim, page_size, write_kv, status) -> None:
+    """Rotates queries (in place) and keys of the fused qkv rows and writes keys
+    and values into the paged cache [pages, kv_heads, page, head_dim]."""
+    _need_cuda(qkv, k_cache, cos_sin, positions, block_table)
+    T = qkv.shape[0]
+    assert qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim and qkv.is_contiguous()
+    assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+    assert block_table.dtype == torch.int32 and block_table.is_contiguous()
+    max_pos, rot = cos_sin.shape
+    if write_kv:
+        assert k_cache.dtype == qkv.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert k_cache.shape[1:] == (num_kv_heads, page_size, head_dim), (k_cache.shape, num_kv_heads, page_size)
+    num_pages = k_cache.shape[0] if k_cache is not None else 0
+    _check(core().le_rope_kv_write(_ptr(qkv), dtype_code(qkv.dtype), _ptr(k_cache), _ptr(v_cache), _ptr(cos_sin),
+                                   _ptr(positions), _ptr(request_of_token), _ptr(block_table), block_table.shape[1],
+                                   T, num_heads, num_kv_heads, head_dim, rot, max_pos, page_size, num_pages,
+                                   1 if write_kv else 0, _ptr(status), _stream()), "le_rope_kv_write")
+
+
+def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T on the FP32 pipes (inputs float32 or
+    bfloat16, 32-bit accumulation in ascending k)."""
+    _need_cuda(out, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N) and a.dtype == w.dtype
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(core().le_gemm_simt(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), dtype_code(a.dtype), M, N, K,
+                               a.stride(0), w.stride(0), out.stride(0), _stream()), "le_gemm_simt")
+
+
+def linear(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
+    """out = a @ w^T.  float32: the package's FP32 kernel.  bfloat16: the
+    library product (cuBLAS), 32-bit accumulation; when ``out`` is float32 the
+    product is written in 32 bits without an intermediate rounding."""
+    if a.dtype == torch.float32:
+        gemm_simt(out, a, w)
+        return
+    _need_cuda(out, a, w)
+    if out.dtype == torch.bfloat16:
+        torch.mm(a, w.t(), out=out)
+    else:
+        gemm_bf16_f32out(out, a, w)
+
+
+_mm_out_dtype_ok = None
+
+
+def gemm_bf16_f32out(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
+    """bfloat16 inputs, float32 output (the output head's logits)."""
+    global _mm_out_dtype_ok
+    if _mm_out_dtype_ok is None:
+        try:
+            torch.mm(a[:1], w[:8].t(), out_dtype=torch.float32)
+            _mm_out_dtype_ok = True
+        except (TypeError, RuntimeError):
+            _mm_out_dtype_ok = False
+    K, N = a.shape[1], w.shape[0]
+    if _mm_out_dtype_ok and K % 8 == 0 and N % 8 == 0:
+        torch.mm(a, w.t(), out_dtype=torch.float32, out=out)
+    else:
+        gemm_simt(out, a, w)
+
+
+def attention_generic(out, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, tile_request, tile_q0,
+                      num_tiles, num_heads, num_kv_heads, head_dim, page_size, window, scale, status) -> None:
+    _need_cuda(out, q, k_cache, v_cache, block_table)
+    lib = attention_lib(head_dim)
+    assert out.is_contiguous() and out.shape[1] == num_heads * head_dim
+    assert k_cache.shape[1:] == (num_kv_heads, page_size, head_dim)
+    _check(lib.le_attention_generic(_ptr(out), out.stride(0), _ptr(q), q_stride, _ptr(k_cache), _ptr(v_cache),
+                                    dtype_code(out.dtype), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
+                                    _ptr(ctx_before), _ptr(tile_request), _ptr(tile_q0), num_tiles, num_heads,
+                                    num_kv_heads, page_size, k_cache.shape[0], int(window or 0), float(scale),
+                                    _ptr(status), _stream()), "le_attention_generic", lib)
+
+
+def argmax(out: torch.Tensor, logits: torch.Tensor) -> None:
+    _need_cuda(out, logits)
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and logits.stride(1) == 1
+    _check(core().le_argmax(_ptr(out), _ptr(logits), n, V, logits.stride(0), _stream()), "le_argmax")
+
+
+def sample(out, logits, temperature, top_p, top_k, seeds, uniforms=None, probs_out=None) -> None:
+    """One token per row of ``logits`` [n, V] float32: greedy where temperature
+    < 1e-4, else temperature / top-k / top-p sampling.  ``seeds`` is int32
+    [n, 3]: seed low word, seed high word, counter."""
+    _need_cuda(out, logits, temperature, top_p, top_k, seeds)
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and logits.stride(1) == 1
+    assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32
+    assert top_k.dtype == torch.int32 and seeds.dtype == torch.int32
+    _check(core().le_sample(_ptr(out), _ptr(logits), n, V, logits.stride(0), _ptr(temperature), _ptr(top_p),
+                            _ptr(top_k), _ptr(seeds), _ptr(uniforms), _ptr(probs_out), _stream()), "le_sample")
