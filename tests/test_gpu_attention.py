@@ -1,0 +1,100 @@
+"""The attention kernels alone against plain attention over gathered pages:
+mixed batches (portions beside single tokens), scattered pages, windows, head
+sizes in steps of 16, and inputs made so that one far key decides the result."""
+import pytest
+import torch
+
+import plain_llama
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def build_case(dtype, nh, nkv, hd, page, q_lens, ctx_before, seed, window=None, spike=True):
+    """Random K/V for every request in scattered pages, queries for the step's
+    tokens; returns device tensors and the plain result."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(q_lens)
+    totals = [c + q for c, q in zip(ctx_before, q_lens)]
+    max_blocks = max((t + page - 1) // page for t in totals) + 1
+    pages_needed = sum((t + page - 1) // page for t in totals)
+    num_pages = pages_needed + 3
+    perm = torch.randperm(num_pages - 1, generator=g)[:pages_needed].tolist()   # the last page stays unused
+    table = torch.full((B, max_blocks), num_pages - 1, dtype=torch.int32)
+    k_cache = torch.randn(num_pages, nkv, page, hd, generator=g).to(dtype)     # stale garbage everywhere
+    v_cache = torch.randn(num_pages, nkv, page, hd, generator=g).to(dtype)
+    T = sum(q_lens)
+    q = torch.randn(T, nh * hd, generator=g)
+    ks, vs = [], []
+    nxt = 0
+    for b in range(B):
+        k = torch.randn(nkv, totals[b], hd, generator=g)
+        v = torch.randn(nkv, totals[b], hd, generator=g)
+        if spike and totals[b] > 3:
+            # one far key answers the last query of the request strongly
+            far = 1 if window is None else max(0, totals[b] - (window or totals[b]))
+            t_last = sum(q_lens[:b + 1]) - 1
+            for h in range(nh):
+                k[h // (nh // nkv), far] = q[t_last, h * hd:(h + 1) * hd] * 1.5
+        k, v = k.to(dtype), v.to(dtype)
+        ks.append(k.float()); vs.append(v.float())
+        for i in range((totals[b] + page - 1) // page):
+            pg = perm[nxt]; nxt += 1
+            table[b, i] = pg
+            n = min(page, totals[b] - i * page)
+            k_cache[pg, :, :n] = k[:, i * page:i * page + n]
+            v_cache[pg, :, :n] = v[:, i * page:i * page + n]
+    q = q.to(dtype)
+    want = torch.zeros(T, nh * hd)
+    t0 = 0
+    for b in range(B):
+        for j in range(q_lens[b]):
+            p = ctx_before[b] + j
+            lo = max(0, p - window + 1) if window else 0
+            qq = q[t0 + j].float().view(nh, 1, hd)
+            o = plain_llama.plain_attention(qq, ks[b][:, lo:p + 1], vs[b][:, lo:p + 1]) if False else None
+            # plain attention of one query over its visible keys (no mask needed)
+            kk = ks[b][:, lo:p + 1].repeat_interleave(nh // nkv, 0)
+            vv = vs[b][:, lo:p + 1].repeat_interleave(nh // nkv, 0)
+            s = torch.matmul(qq, kk.transpose(-1, -2)) / (hd ** 0.5)
+            want[t0 + j] = torch.matmul(torch.softmax(s, -1), vv).reshape(-1)
+        t0 += q_lens[b]
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    return dict(q=q.to(DEV), k=k_cache.to(DEV), v=v_cache.to(DEV), table=table.to(DEV), cu=cu.to(DEV),
+                ctx=torch.tensor(ctx_before, dtype=torch.int32, device=DEV), want=want, T=T)
+
+
+def tiles(q_lens, size):
+    req, q0 = [], []
+    for b, n in enumerate(q_lens):
+        for s in range(0, n, size):
+            req.append(b); q0.append(s)
+    return (torch.tensor(req, dtype=torch.int32, device=DEV), torch.tensor(q0, dtype=torch.int32, device=DEV), len(req))
+
+
+CASES = [
+    # nh, nkv, hd, page, q_lens, ctx_before, window
+    (4, 2, 16, 4, [5, 1, 17], [0, 9, 3], None),
+    (3, 1, 32, 8, [1, 1, 1, 1], [0, 7, 8, 40], None),
+    (6, 3, 64, 16, [33, 2, 1], [100, 0, 515], None),
+    (8, 8, 48, 2, [40], [0], None),
+    (2, 1, 128, 16, [3, 70], [61, 2], None),
+    (4, 2, 80, 4, [9, 1], [30, 77], 12),
+    (2, 2, 256, 16, [18, 1], [0, 33], None),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", CASES)
+def test_generic_kernel(case, dtype):
+    from lyapunov_engine_b200 import ops
+    nh, nkv, hd, page, q_lens, ctx_before, window = case
+    c = build_case(dtype, nh, nkv, hd, page, q_lens, ctx_before, seed=hd + page, window=window)
+    out = torch.zeros(c["T"], nh * hd, dtype=dtype, device=DEV)
+    status = ops.new_status(DEV)
+    tr, tq, n = tiles(q_lens, 16)
+    ops.attention_generic(out, c["q"], c["q"].stride(0), c["k"], c["v"], c["table"], c["cu"], c["ctx"], tr, tq, n,
+                          nh, nkv, hd, page, window, 1.0 / hd ** 0.5, status)
+    ops.check_status(status)
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(out.float().cpu(), c["want"], **tol)

@@ -1,0 +1,223 @@
+"""Each kernel alone against its plain reference (float32 torch ops written
+here or in plain_llama.py), at sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+import plain_llama
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def ops():
+    from lyapunov_engine_b200 import ops as o
+    return o
+
+
+def tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,hidden", [(1, 64), (7, 100), (33, 2050), (5, 8192), (3, 13)])
+def test_rmsnorm_with_residual(dtype, rows, hidden):
+    g = torch.Generator().manual_seed(rows * hidden)
+    resid = torch.randn(rows, hidden, generator=g) * 3
+    delta = torch.randn(rows, hidden, generator=g).to(dtype)
+    w = 1 + 0.1 * torch.randn(hidden, generator=g)
+    eps = 1e-6
+    r = resid.to(DEV)
+    out = torch.empty(rows, hidden, dtype=dtype, device=DEV)
+    ops().rmsnorm(out, r, delta.to(DEV), w.to(DEV), eps)
+    summed = resid + delta.float()
+    torch.testing.assert_close(r.cpu(), summed, atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(out.float().cpu(), plain_llama.plain_rmsnorm(summed, w, eps), **tol(dtype))
+    # without delta, and on chosen rows only (the residual stream stays as it is)
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32)
+    out2 = torch.empty(2, hidden, dtype=dtype, device=DEV)
+    before = r.clone()
+    ops().rmsnorm(out2, r, delta.to(DEV), w.to(DEV), eps, rows=idx.to(DEV))
+    assert torch.equal(r, before)
+    want = plain_llama.plain_rmsnorm(summed + delta.float(), w, eps)[idx.long()]
+    torch.testing.assert_close(out2.float().cpu(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_and_bad_token(dtype):
+    o = ops()
+    table = torch.randn(37, 24).to(dtype)
+    ids = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32)
+    status = o.new_status(DEV)
+    out = torch.empty(5, 24, device=DEV)
+    o.embed(out, table.to(DEV), ids.to(DEV), status)
+    assert torch.equal(out.cpu(), table.float()[ids.long()])
+    o.check_status(status)
+    o.embed(out, table.to(DEV), torch.tensor([1, 37, 2, -1, 3], dtype=torch.int32, device=DEV), status)
+    with pytest.raises(o.KernelError, match="token id"):
+        o.check_status(status)
+    assert torch.equal(out[1].cpu(), torch.zeros(24))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,inter", [(1, 8), (9, 330), (4, 1000)])
+def test_swiglu(dtype, rows, inter):
+    gu = (torch.randn(rows, 2 * inter) * 3).to(dtype)
+    out = torch.empty(rows, inter, dtype=dtype, device=DEV)
+    ops().swiglu(out, gu.to(DEV))
+    want = plain_llama.plain_swiglu(gu[:, :inter].float(), gu[:, inter:].float())
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,page,rot", [(4, 2, 16, 4, 16), (3, 1, 48, 8, 48), (5, 5, 128, 16, 128), (2, 1, 64, 2, 32)])
+def test_rope_and_cache_write(dtype, nh, nkv, hd, page, rot):
+    o = ops()
+    g = torch.Generator().manual_seed(hd)
+    # two requests: tokens at scattered positions
+    positions = torch.tensor([0, 1, 2, 3, 4, 11, 12, 13], dtype=torch.int32)
+    request = torch.tensor([0, 0, 0, 0, 0, 1, 1, 1], dtype=torch.int32)
+    T = positions.numel()
+    pages = 9
+    table = torch.tensor([[3, 1, 8, 8, 8, 8, 8], [0, 2, 4, 5, 6, 7, 8]], dtype=torch.int32)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype)
+    inv = plain_llama.plain_inv_freq(rot, 10000.0, None)
+    ang = torch.outer(torch.arange(40).float(), inv)
+    cos_sin = torch.cat([ang.cos(), ang.sin()], -1).contiguous()
+    k_cache = torch.zeros(pages, nkv, page, hd, dtype=dtype, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    status = o.new_status(DEV)
+    dq = qkv.to(DEV)
+    o.rope_kv_write(dq, k_cache, v_cache, cos_sin.to(DEV), positions.to(DEV), request.to(DEV), table.to(DEV), nh, nkv,
+                    hd, page, True, status)
+    o.check_status(status)
+    x = qkv.float().view(T, nh + 2 * nkv, hd)
+    cos, sin = plain_llama.plain_cos_sin(positions, inv)   # [T, rot]
+
+    def rotate(h):   # [T, heads, hd]
+        head = plain_llama.plain_rotate_half(h[..., :rot].transpose(0, 1), cos, sin).transpose(0, 1)
+        return torch.cat([head, h[..., rot:]], -1)
+    q_want, k_want, v_want = rotate(x[:, :nh]), rotate(x[:, nh:nh + nkv]), x[:, nh + nkv:]
+    got = dq.float().cpu().view(T, nh + 2 * nkv, hd)
+    torch.testing.assert_close(got[:, :nh], q_want, **tol(dtype))
+    kc, vc = k_cache.float().cpu(), v_cache.float().cpu()
+    for t in range(T):
+        p, b = int(positions[t]), int(request[t])
+        pg = int(table[b, p // page])
+        torch.testing.assert_close(kc[pg, :, p % page], k_want[t], **tol(dtype))
+        torch.testing.assert_close(vc[pg, :, p % page], v_want[t], atol=0, rtol=0)
+    # nothing else was touched
+    written = torch.zeros(pages, page, dtype=torch.bool)
+    for t in range(T):
+        p, b = int(positions[t]), int(request[t])
+        written[int(table[b, p // page]), p % page] = True
+    assert kc.abs().sum((1, 3))[~written].sum() == 0
+    # a page id outside the pool is refused, not followed
+    bad = table.clone()
+    bad[0, 0] = pages
+    o.rope_kv_write(dq, k_cache, v_cache, cos_sin.to(DEV), positions.to(DEV), request.to(DEV), bad.to(DEV), nh, nkv,
+                    hd, page, True, status)
+    with pytest.raises(o.KernelError, match="block table"):
+        o.check_status(status)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (5, 67, 33), (130, 515, 96), (64, 64, 64), (3, 1000, 136), (257, 70, 328)])
+def test_gemm_fp32_pipes(M, N, K):
+    g = torch.Generator().manual_seed(M + N + K)
+    a, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    out = torch.empty(M, N, device=DEV)
+    ops().gemm_simt(out, a.to(DEV), w.to(DEV))
+    want = (a.double() @ w.double().t()).float()
+    torch.testing.assert_close(out.cpu(), want, atol=1e-5 * math.sqrt(K), rtol=1e-5)
+    # bfloat16 inputs, 32-bit accumulation
+    ab, wb = a.bfloat16(), w.bfloat16()
+    out32 = torch.empty(M, N, device=DEV)
+    ops().gemm_simt(out32, ab.to(DEV), wb.to(DEV))
+    torch.testing.assert_close(out32.cpu(), (ab.double() @ wb.double().t()).float(), atol=1e-5 * math.sqrt(K), rtol=1e-5)
+
+
+def test_gemm_rows_do_not_depend_on_the_batch():
+    """A token's projection is bit-for-bit the same alone and among others."""
+    g = torch.Generator().manual_seed(0)
+    a, w = torch.randn(77, 200, generator=g).to(DEV), torch.randn(150, 200, generator=g).to(DEV)
+    whole = torch.empty(77, 150, device=DEV)
+    ops().gemm_simt(whole, a, w)
+    for lo, hi in [(0, 1), (5, 6), (63, 70), (76, 77)]:
+        part = torch.empty(hi - lo, 150, device=DEV)
+        ops().gemm_simt(part, a[lo:hi].contiguous(), w)
+        assert torch.equal(part, whole[lo:hi])
+
+
+@pytest.mark.parametrize("M,N,K", [(4, 515, 96), (33, 1000, 136), (64, 128256 // 64, 256)])
+def test_linear_bf16(M, N, K):
+    g = torch.Generator().manual_seed(N)
+    a, w = torch.randn(M, K, generator=g).bfloat16(), torch.randn(N, K, generator=g).bfloat16()
+    want = (a.double() @ w.double().t()).float()
+    out32 = torch.empty(M, N, device=DEV)
+    ops().linear(out32, a.to(DEV), w.to(DEV))
+    torch.testing.assert_close(out32.cpu(), want, atol=1e-3, rtol=1e-4)
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops().linear(out16, a.to(DEV), w.to(DEV))
+    torch.testing.assert_close(out16.float().cpu(), want, atol=0.05, rtol=1e-2)
+
+
+def test_argmax_first_of_equal_maxima():
+    logits = torch.randn(6, 1003)
+    logits[2, 17] = logits[2, 900] = 50.0
+    logits[4, 1002] = 60.0
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops().argmax(out, logits.to(DEV))
+    assert out.cpu().tolist() == [plain_llama.plain_greedy(r) for r in logits]
+    assert out[2].item() == 17
+
+
+@pytest.mark.parametrize("vocab", [50, 1003, 128256])
+def test_sampling_filters_match_the_reference_rule(vocab):
+    o = ops()
+    g = torch.Generator().manual_seed(vocab)
+    n = 6
+    logits = torch.randn(n, vocab, generator=g) * 2.5
+    temperature = torch.tensor([1.0, 0.7, 1.3, 0.0, 0.5, 2.0])
+    top_k = torch.tensor([-1, 5, -1, -1, 40, 0], dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 0.8, 1.0, 0.6, 0.95])
+    u = torch.tensor([0.3, 0.999, 0.0, 0.5, 0.42, 0.77])
+    seeds = torch.zeros(n, 3, dtype=torch.int32)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    probs = torch.empty(n, vocab, device=DEV)
+    o.sample(out, logits.to(DEV), temperature.to(DEV), top_p.to(DEV), top_k.to(DEV), seeds.to(DEV), u.to(DEV), probs)
+    probs, out = probs.cpu(), out.cpu()
+    for i in range(n):
+        if temperature[i] < 1e-4:
+            assert out[i].item() == plain_llama.plain_greedy(logits[i])
+            continue
+        want = plain_llama.plain_filtered_probs(logits[i], float(temperature[i]), int(top_k[i]), float(top_p[i]))
+        assert ((probs[i] > 0) == (want > 0)).all(), f"row {i}: kept sets differ"
+        torch.testing.assert_close(probs[i].double(), want, atol=1e-6, rtol=1e-4)
+        cdf = torch.cumsum(want, 0)
+        k = int(out[i])
+        assert want[k] > 0
+        lo = float(cdf[k] - want[k]); hi = float(cdf[k])
+        assert lo - 1e-4 <= float(u[i]) * float(cdf[-1]) <= hi + 1e-4, f"row {i}: token {k} covers [{lo}, {hi}), u = {u[i]}"
+
+
+def test_sampling_frequencies_and_batch_independence():
+    o = ops()
+    vocab, n = 11, 4000
+    logits = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, 3.0, -2.0, 0.2, 0.1, 1.5, -0.5])
+    rows = logits.repeat(n, 1).to(DEV)
+    seeds = torch.zeros(n, 3, dtype=torch.int32)
+    seeds[:, 0] = 1234
+    seeds[:, 2] = torch.arange(n)
+    args = (torch.full((n,), 0.9).to(DEV), torch.full((n,), 1.0).to(DEV), torch.full((n,), -1, dtype=torch.int32).to(DEV))
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    o.sample(out, rows, *args, seeds.to(DEV))
+    freq = torch.bincount(out.cpu().long(), minlength=vocab).double() / n
+    want = plain_llama.plain_filtered_probs(logits, 0.9, -1, 1.0)
+    assert (freq - want).abs().max() < 4 * math.sqrt(0.25 / n)
+    # the same (seed, counter) gives the same token whatever the batch
+    one = torch.empty(1, dtype=torch.int32, device=DEV)
+    for i in (0, 17, 3999):
+        o.sample(one, rows[i:i + 1], *(a[i:i + 1] for a in args), seeds[i:i + 1].to(DEV))
+        assert one.item() == out[i].item()
