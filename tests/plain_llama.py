@@ -134,18 +134,26 @@ def plain_attention(q, k, v, window: int | None = None) -> torch.Tensor:
     return torch.matmul(probs, v)
 
 
-def plain_attention_layer(x, wq, wk, wv, wo, nh, nkv, hd, cos, sin, window=None):
+def rounded(x: torch.Tensor, act_dtype) -> torch.Tensor:
+    """What storing an activation in ``act_dtype`` does to it (nothing when
+    act_dtype is None).  With act_dtype=torch.bfloat16 the plain implementation
+    models a pipeline whose activations between matrix products are bfloat16
+    while the residual stream, norms, softmax and rotation stay 32-bit."""
+    return x if act_dtype is None else x.to(act_dtype).to(x.dtype)
+
+
+def plain_attention_layer(x, wq, wk, wv, wo, nh, nkv, hd, cos, sin, window=None, act_dtype=None):
     """q/k/v projections, head split, RoPE on q and k, attention, o projection
     (python/lyapunov_engine/models/llama.py:61-106)."""
     T = x.shape[0]
-    q = (x @ wq.T).view(T, nh, hd).transpose(0, 1)
-    k = (x @ wk.T).view(T, nkv, hd).transpose(0, 1)
-    v = (x @ wv.T).view(T, nkv, hd).transpose(0, 1)
-    q = plain_rotate_half(q, cos, sin)
-    k = plain_rotate_half(k, cos, sin)
-    o = plain_attention(q, k, v, window)
+    q = rounded(x @ wq.T, act_dtype).view(T, nh, hd).transpose(0, 1)
+    k = rounded(x @ wk.T, act_dtype).view(T, nkv, hd).transpose(0, 1)
+    v = rounded(x @ wv.T, act_dtype).view(T, nkv, hd).transpose(0, 1)
+    q = rounded(plain_rotate_half(q, cos, sin), act_dtype)
+    k = rounded(plain_rotate_half(k, cos, sin), act_dtype)
+    o = rounded(plain_attention(q, k, v, window), act_dtype)
     o = o.transpose(0, 1).contiguous().view(T, nh * hd)
-    return o @ wo.T
+    return rounded(o @ wo.T, act_dtype)
 
 
 def plain_swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -154,42 +162,45 @@ def plain_swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return gate / (1.0 + torch.exp(-gate)) * up
 
 
-def plain_mlp(x, w_gate, w_up, w_down) -> torch.Tensor:
+def plain_mlp(x, w_gate, w_up, w_down, act_dtype=None) -> torch.Tensor:
     """down(silu(gate(x)) * up(x)) (python/lyapunov_engine/models/llama.py:119-122)."""
-    return plain_swiglu(x @ w_gate.T, x @ w_up.T) @ w_down.T
+    act = plain_swiglu(rounded(x @ w_gate.T, act_dtype), rounded(x @ w_up.T, act_dtype))
+    return rounded(rounded(act, act_dtype) @ w_down.T, act_dtype)
 
 
-def plain_block(h, w: dict, prefix: str, cfg: dict, cos, sin, window=None):
+def plain_block(h, w: dict, prefix: str, cfg: dict, cos, sin, window=None, act_dtype=None):
     """Pre-norm residual block (python/lyapunov_engine/models/llama.py:136-165)."""
     eps = float(cfg["rms_norm_eps"])
     nh = cfg["num_attention_heads"]
     nkv = cfg.get("num_key_value_heads", nh)
     hd = head_dim_of(cfg)
-    n = plain_rmsnorm(h, w[prefix + "input_layernorm.weight"], eps)
+    n = rounded(plain_rmsnorm(h, w[prefix + "input_layernorm.weight"], eps), act_dtype)
     a = plain_attention_layer(
         n,
         w[prefix + "self_attn.q_proj.weight"],
         w[prefix + "self_attn.k_proj.weight"],
         w[prefix + "self_attn.v_proj.weight"],
         w[prefix + "self_attn.o_proj.weight"],
-        nh, nkv, hd, cos, sin, window,
+        nh, nkv, hd, cos, sin, window, act_dtype,
     )
     h = h + a
-    n = plain_rmsnorm(h, w[prefix + "post_attention_layernorm.weight"], eps)
+    n = rounded(plain_rmsnorm(h, w[prefix + "post_attention_layernorm.weight"], eps), act_dtype)
     m = plain_mlp(
         n,
         w[prefix + "mlp.gate_proj.weight"],
         w[prefix + "mlp.up_proj.weight"],
         w[prefix + "mlp.down_proj.weight"],
+        act_dtype,
     )
     return h + m
 
 
-def plain_forward(cfg: dict, w: dict, ids, windows=None) -> torch.Tensor:
+def plain_forward(cfg: dict, w: dict, ids, windows=None, act_dtype=None) -> torch.Tensor:
     """Logits [T, V] of one whole sequence starting at position 0
     (python/lyapunov_engine/models/llama.py:196-225).  The output head is
     ``lm_head.weight`` when the folder has it, else the embedding matrix
-    (python/lyapunov_engine/models/weight_loader.py:102-109)."""
+    (python/lyapunov_engine/models/weight_loader.py:102-109).  ``act_dtype``:
+    see ``rounded``."""
     ids = torch.as_tensor(ids)
     T = ids.shape[0]
     dtype = w["model.embed_tokens.weight"].dtype
@@ -200,8 +211,8 @@ def plain_forward(cfg: dict, w: dict, ids, windows=None) -> torch.Tensor:
     cos, sin = cos.to(dtype), sin.to(dtype)
     for i in range(cfg["num_hidden_layers"]):
         window = windows[i] if windows is not None else None
-        h = plain_block(h, w, f"model.layers.{i}.", cfg, cos, sin, window)
-    n = plain_rmsnorm(h, w["model.norm.weight"], float(cfg["rms_norm_eps"]))
+        h = plain_block(h, w, f"model.layers.{i}.", cfg, cos, sin, window, act_dtype)
+    n = rounded(plain_rmsnorm(h, w["model.norm.weight"], float(cfg["rms_norm_eps"])), act_dtype)
     head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
     return n @ head.T
 

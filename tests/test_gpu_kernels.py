@@ -80,8 +80,8 @@ def test_rope_and_cache_write(dtype, nh, nkv, hd, page, rot):
     positions = torch.tensor([0, 1, 2, 3, 4, 11, 12, 13], dtype=torch.int32)
     request = torch.tensor([0, 0, 0, 0, 0, 1, 1, 1], dtype=torch.int32)
     T = positions.numel()
-    pages = 9
-    table = torch.tensor([[3, 1, 8, 8, 8, 8, 8], [0, 2, 4, 5, 6, 7, 8]], dtype=torch.int32)
+    pages = 12
+    table = torch.tensor([[3, 1, 9, 11, 11, 11, 11], [0, 2, 4, 5, 6, 7, 8]], dtype=torch.int32)
     qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype)
     inv = plain_llama.plain_inv_freq(rot, 10000.0, None)
     ang = torch.outer(torch.arange(40).float(), inv)

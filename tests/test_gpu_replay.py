@@ -24,9 +24,14 @@ PROMPTS = {"tiny_a": (5, 17, 33, 38), "tiny_b": (1, 8, 40, 97), "tiny_c": (8, 33
 
 # float32: different summation orders of the same 32-bit arithmetic.
 F32_TOL = dict(atol=1e-4, rtol=1e-4)
-# bfloat16 activations between 32-bit accumulations: each rounding is 2^-9
-# relative; over the ~10 roundings a layer that is a few 1e-2 of the logits' scale.
-BF16_REL = 0.03
+# bfloat16: the plain implementation rounds its activations to bfloat16 where the
+# pipeline stores them (plain_llama.rounded).  What is left is the order of
+# accumulation inside the products now and then flipping one of those roundings
+# by a unit in the last place, which peaked attention then amplifies.  That
+# noise is measured, not guessed: the plain implementation is run with 32-bit
+# and with 64-bit accumulation, and the engine may differ from it by three
+# times the largest difference between those two.
+BF16_FLOORS = 3.0
 
 
 @pytest.fixture(scope="module")
@@ -43,9 +48,12 @@ def models(tmp_path_factory):
         prompt_lens = {f"r{i}": n for i, n in enumerate(PROMPTS[name])}
         rounded = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
         ref32 = {r: plain_llama.plain_forward(cfg, w, ids) for r, ids in requests.items()}
-        ref16 = {r: plain_llama.plain_forward(cfg, rounded, ids) for r, ids in requests.items()}
+        ref16 = {r: plain_llama.plain_forward(cfg, rounded, ids, act_dtype=torch.bfloat16) for r, ids in requests.items()}
+        rounded64 = {k: v.double() for k, v in rounded.items()}
+        floor = max(float((plain_llama.plain_forward(cfg, rounded64, ids, act_dtype=torch.bfloat16).float() - ref16[r]).abs().max())
+                    for r, ids in requests.items())
         out[name] = dict(cfg=cfg, page=page, folders=folders, requests=requests, prompt_lens=prompt_lens,
-                         ref={"float32": ref32, "bfloat16": ref16})
+                         ref={"float32": ref32, "bfloat16": ref16}, bf16_floor=floor)
     return out
 
 
@@ -63,8 +71,7 @@ def check(m, trace, dtype, tmp_path, live, what, child=False):
     assert len(got) == expected
     if dtype == "float32":
         return ru.compare(got, ref, what=what, **F32_TOL)
-    scale = max(float(r.abs().max()) for r in ref.values())
-    return ru.compare(got, ref, atol=BF16_REL * scale, rtol=0.0, what=what)
+    return ru.compare(got, ref, atol=BF16_FLOORS * m["bf16_floor"] + 1e-3, rtol=0.0, what=what)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -109,7 +116,7 @@ def test_mixed_with_page_reuse(models, name, dtype, tmp_path):
             weights = {k: v.to(torch.bfloat16).float() for k, v in weights.items()}
     for rid, ids in requests.items():
         if rid not in ref:
-            ref[rid] = plain_llama.plain_forward(cfg, weights, ids)
+            ref[rid] = plain_llama.plain_forward(cfg, weights, ids, act_dtype=torch.bfloat16 if dtype == "bfloat16" else None)
     m2 = dict(m, requests=requests, prompt_lens=prompt_lens, ref={dtype: ref})
     trace = ru.mixed_trace(requests, prompt_lens, chunk=16, max_live=4, seed=3)
     assert any(len(s["entries"]) >= 3 for s in trace.steps)
