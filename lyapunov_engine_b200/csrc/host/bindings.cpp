@@ -140,7 +140,8 @@ PYBIND11_MODULE(_host, m) {
       .def("get_num_running_sequences", &ContinuousScheduler::get_num_running_sequences)
       .def("schedule", &ContinuousScheduler::schedule)
       .def("post_step", &ContinuousScheduler::post_step)
-      .def("get_stats", &ContinuousScheduler::get_stats);
+      .def("get_stats", &ContinuousScheduler::get_stats)
+      .def("get_config", &ContinuousScheduler::get_config);
 
   py::class_<PackedStep>(m, "PackedStep")
       .def_readonly("num_tokens", &PackedStep::num_tokens)
