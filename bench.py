@@ -1,0 +1,337 @@
+"""Benchmark: decode tokens a second of the engine on Llama-3.2-1B shapes
+(random weights, synthetic tokens), one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+A step is one decode step of a batch of 8 requests at context 4096.  `value`
+times K steps on the device (CUDA events) through the step function and the
+sampler; `e2e` times the same through the Python entry point
+(LLMEngine.step(): host tokens in, host tokens out).  The line also carries a
+2,048-token prefill, decode at batch 1 and 64, and the decode step's HBM
+roofline.  Every step reads all weights (2.5 GB) and the live cache, far more
+than the 126 MB L2, so nothing is served from cache between timed steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 128256, "hidden_size": 2048,
+    "intermediate_size": 8192, "num_hidden_layers": 16, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 64, "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": True, "hidden_act": "silu", "attention_bias": False, "mlp_bias": False,
+    "bos_token_id": 128000, "eos_token_id": 128001, "torch_dtype": "bfloat16",
+}
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+BLOCK_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = dict(FALLBACK_PEAKS, source="fallback")
+    try:
+        with open(path) as f:
+            raw = json.load(f)
+        for key in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+            if key in raw and isinstance(raw[key], (int, float)):
+                out[key] = float(raw[key])
+        out["source"] = "measured"
+    except (OSError, ValueError):
+        pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def mark(self):
+        return len(self.rows)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, begin=0, end=None):
+        rows = [r for r in self.rows[begin:end] if len(r) >= 7]
+        if not rows:
+            rows = [r for r in self.rows if len(r) >= 7]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(int(float(r[0])) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(float(rows[0][1])), "reasons": reasons,
+                "samples": len(rows), "power_w": max(float(r[2]) for r in rows)}
+
+
+def decode_bytes(cfg, batch, context):
+    """Bytes one decode step must read: every weight it uses once, and the
+    keys and values of the live requests (bfloat16)."""
+    H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (nh + 2 * nkv) * hd * H + H * nh * hd + 2 * I * H + H * I
+    weights = 2 * (L * per_layer + V * H) + 4 * (2 * L + 1) * H
+    kv = 2 * batch * context * 2 * nkv * hd * L
+    return weights + kv
+
+
+def prefill_flops(cfg, tokens):
+    H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (nh + 2 * nkv) * hd * H + H * nh * hd + 2 * I * H + H * I
+    linear = 2 * tokens * L * per_layer + 2 * V * H
+    attention = 4 * nh * hd * tokens * (tokens + 1) // 2 * L
+    return linear + attention
+
+
+def run_ours(args):
+    import torch
+
+    from lyapunov_engine_b200 import EngineConfig, LLMEngine, SamplingParams, build, load_model, ops
+
+    cfg = dict(LLAMA_1B)
+    layers_full = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    pk = peaks()
+    torch.cuda.set_device(0)
+    host = build.load_host()
+    max_batch = 64
+    num_blocks = (max_batch * (CONTEXT + 64) + 2 * PREFILL_TOKENS) // BLOCK_SIZE
+    loaded = load_model(config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", max_model_len=CONTEXT + 64)
+    engine = LLMEngine(loaded, EngineConfig(num_blocks=num_blocks, block_size=BLOCK_SIZE, max_num_seqs=max_batch,
+                                            max_num_batched_tokens=8192, dtype="bfloat16", device="cuda:0",
+                                            max_model_len=CONTEXT + 64))
+    runner, manager, sampler = engine.runner, engine.block_manager, engine.sampler
+    gen = torch.Generator().manual_seed(0)
+    vocab = cfg["vocab_size"]
+    # Synthetic cache content: timing does not depend on what the pages hold,
+    # but a softmax over zeros would be a degenerate case.
+    for pools in engine.cache.streams:
+        for s in pools:
+            s.k.normal_(0, 1)
+            s.v.normal_(0, 1)
+    greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
+
+    def timed_decode(batch, steps, warmup, context_end):
+        """K decode steps of `batch` requests whose last step runs at
+        `context_end` tokens: step function + sampler, timed on the device."""
+        start_len = context_end - (steps + warmup)
+        seqs = []
+        for i in range(batch):
+            ids = torch.randint(0, vocab, (start_len + 1,), generator=gen).tolist()
+            s = host.Sequence(10_000 + i, ids, host.SamplingParams())
+            assert manager.grow(s, start_len)
+            s.set_num_computed_tokens(start_len)
+            seqs.append(s)
+        params = [greedy] * batch
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+        def one_step():
+            entries = []
+            for s in seqs:
+                n = s.get_num_computed_tokens()
+                assert manager.grow(s, n + 1)
+                entries.append(host.StepEntry(s, n, 1, [0]))
+            logits = runner.step(entries)
+            ids = sampler.sample(logits, params, [0] * batch)
+            for s in seqs:
+                s.set_num_computed_tokens(s.get_num_computed_tokens() + 1)
+                s.extend_prompt([1])
+            return ids
+
+        for _ in range(warmup):
+            one_step()
+        torch.cuda.synchronize()
+        before = dict(ops.counters)
+        graph_before = runner.num_graph_steps
+        begin.record()
+        for _ in range(steps):
+            one_step()
+        end.record()
+        torch.cuda.synchronize()
+        ms = begin.elapsed_time(end) / steps
+        for s in seqs:
+            manager.free(s)
+        return ms, runner.num_graph_steps - graph_before, before
+
+    def timed_prefill(tokens, repeats, warmup):
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = []
+        for r in range(warmup + repeats):
+            ids = torch.randint(0, vocab, (tokens,), generator=gen).tolist()
+            s = host.Sequence(20_000 + r, ids, host.SamplingParams())
+            assert manager.grow(s, tokens)
+            torch.cuda.synchronize()
+            begin.record()
+            logits = runner.step([host.StepEntry(s, 0, tokens, [tokens - 1])])
+            sampler.sample(logits, [greedy], [0])
+            end.record()
+            torch.cuda.synchronize()
+            if r >= warmup:
+                best.append(begin.elapsed_time(end))
+            manager.free(s)
+        best.sort()
+        return best[len(best) // 2]
+
+    clocks = ClockSampler()
+    clocks.start()
+    time.sleep(0.3)
+
+    # ---- headline: batch 8 at context 4096
+    batch = 8
+    kernels_per_step = None
+    timed_decode(batch, 4, 2, CONTEXT - 200)   # captures the graph for this batch outside the timed call
+    ops.counters["own_kernels"] = ops.counters["library_products"] = 0
+    m0 = clocks.mark()
+    ms8, graph_steps, _ = timed_decode(batch, args.steps, args.warmup, CONTEXT)
+    m1 = clocks.mark()
+    value = batch * 1000.0 / ms8
+
+    # kernels per decode step: count launches of one eager step of the same shape
+    runner.use_cuda_graphs = False
+    ops.counters["own_kernels"] = ops.counters["library_products"] = 0
+    timed_decode(batch, 1, 0, CONTEXT - 300)
+    kernels_per_step = dict(ops.counters)
+    runner.use_cuda_graphs = True
+
+    points = {}
+    for b in (1, 64):
+        timed_decode(b, 4, 2, CONTEXT - 200)
+        ms, _, _ = timed_decode(b, args.steps, args.warmup, CONTEXT)
+        points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+        points[f"decode_b{b}_ms"] = round(ms, 4)
+        points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(cfg, b, CONTEXT) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+
+    # ---- prefill of 2,048 tokens
+    pre_ms = timed_prefill(PREFILL_TOKENS, 5, 3)
+    flops = prefill_flops(cfg, PREFILL_TOKENS)
+    prefill = {"value": round(PREFILL_TOKENS * 1000.0 / pre_ms, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)}
+
+    # ---- end to end through the entry point: host tokens in, host tokens out
+    e2e_steps, e2e_warm = args.steps, args.warmup
+    prompt_len = CONTEXT - (e2e_steps + e2e_warm) - 1
+    sp = SamplingParams(temperature=0.0, max_tokens=e2e_steps + e2e_warm + 1, ignore_eos=True)
+    for i in range(batch):
+        engine.add_request(f"bench-{i}", torch.randint(0, vocab, (prompt_len,), generator=gen).tolist(), sp)
+    while any(seq.get_output_len() == 0 for seq, _, _ in engine.active_sequences.values()):
+        engine.step()                               # prefill (portions under the token budget)
+    for _ in range(e2e_warm):
+        engine.step()
+    torch.cuda.synchronize()
+    d2h0 = engine.d2h_bytes
+    t0 = time.perf_counter()
+    produced = 0
+    for _ in range(e2e_steps):
+        produced += len(engine.step())
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    d2h = (engine.d2h_bytes - d2h0) / e2e_steps
+    layout = host.pack_step([host.StepEntry(seq, seq.get_num_computed_tokens(), 1, [0]) for seq, _, _ in
+                             engine.active_sequences.values()], manager, runner.tile_sizes, batch,
+                            runner.fixed_max_blocks, 0, 0)
+    h2d = 4 * layout.total
+    while engine.has_unfinished_requests():
+        engine.step()
+    e2e = {"value": round(produced / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_s * 1000 / e2e_steps, 4)}
+    clocks.stop()
+
+    nbytes = decode_bytes(cfg, batch, CONTEXT)
+    achieved = nbytes / (ms8 * 1e-3) / 1e9
+    line = {
+        "metric": "decode tokens/s, Llama-3.2-1B shapes, batch 8, context 4096",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms8, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), token ids uniform over the vocabulary",
+        "config": {"model": "Llama-3.2-1B shapes", "layers": cfg["num_hidden_layers"], "layers_of_model": layers_full,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": batch,
+                   "seq_len": CONTEXT, "page": BLOCK_SIZE, "parallelism": "single GPU",
+                   "timing": "CUDA events; working set per step > L2", "cuda_graph": graph_steps > 0,
+                   "peaks": pk["source"]},
+        "clocks": clocks.summary(m0, m1),
+        "e2e": e2e,
+        "gpu_launches": kernels_per_step["own_kernels"] * args.steps,
+        "library_products": kernels_per_step["library_products"] * args.steps,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": nbytes},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_reference(args):
+    why = reference_unavailable()
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def reference_unavailable() -> str:
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "lyapunov_engine")):
+        return "IanConery/lyapunov-engine is not installed under baseline/_ref (see DESIGN.md, reference arm)"
+    return ("the reference's generation loop cannot produce this metric: its model never writes the KV cache and "
+            "its engine needs a CUDA extension built for sm_86/89/90 only")
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=64)
+    p.add_argument("--warmup", type=int, default=8)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
+    args = p.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

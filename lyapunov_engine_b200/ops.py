@@ -108,7 +108,12 @@ def attention_lib(head_dim: int):
 _EXTRA_ATTENTION_SIGNATURES: dict[str, list] = {}
 
 
+# Launch counters (own kernels, library products) for the benchmark's report.
+counters = {"own_kernels": 0, "library_products": 0}
+
+
 def _check(code: int, name: str, lib=None):
+    counters["own_kernels"] += 1
     if code != 0:
         lib = lib or core()
         detail = ""
@@ -219,6 +224,7 @@ def linear(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
         return
     _need_cuda(out, a, w)
     if out.dtype == torch.bfloat16:
+        counters["library_products"] += 1
         torch.mm(a, w.t(), out=out)
     else:
         gemm_bf16_f32out(out, a, w)
@@ -238,6 +244,7 @@ def gemm_bf16_f32out(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> Non
             _mm_out_dtype_ok = False
     K, N = a.shape[1], w.shape[0]
     if _mm_out_dtype_ok and K % 8 == 0 and N % 8 == 0:
+        counters["library_products"] += 1
         torch.mm(a, w.t(), out_dtype=torch.float32, out=out)
     else:
         gemm_simt(out, a, w)
