@@ -1,0 +1,167 @@
+"""Generation through the Python entry point and the command line, against the
+plain implementation; the scheduler's pre-emption with a real model; each part
+of a layer alone."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import fixtures
+import plain_llama
+from lyapunov_engine_b200 import EngineConfig, LLMEngine, SamplingParams, load_model
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name, cfg, seed in (("a", fixtures.TINY_A, 0), ("b", fixtures.TINY_B, 1)):
+        w = fixtures.make_weights(cfg, seed, 0.05, 0.1, 4.0)
+        d32 = fixtures.write_model_folder(str(tmp_path_factory.mktemp(name + "32")), cfg, w, torch.float32)
+        d16 = fixtures.write_model_folder(str(tmp_path_factory.mktemp(name + "16")), cfg, w, torch.bfloat16)
+        out[name] = (cfg, w, d32, d16)
+    return out
+
+
+@pytest.mark.parametrize("name,page", [("a", fixtures.TINY_A_PAGE), ("b", fixtures.TINY_B_PAGE)])
+def test_greedy_generation_equals_the_plain_implementation(folders, name, page):
+    cfg, w, d32, _ = folders[name]
+    lens = (5, 17, 33) if name == "a" else (1, 8, 40, 97)
+    steps = 16 if name == "a" else 24
+    prompts = [fixtures.random_ids(cfg, n, 30 + n) for n in lens]
+    # prompts are cut into portions of at most 16 tokens and run beside decoded tokens
+    engine = LLMEngine.from_pretrained(d32, dtype="float32", num_blocks=64, block_size=page, max_num_seqs=4,
+                                       max_num_batched_tokens=20, max_prefill_chunk=16)
+    outs = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=steps, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.output_tokens == plain_llama.plain_greedy_generate(cfg, w, p, steps)
+        assert o.finished and o.finish_reason == "length" and o.prompt_tokens == p
+    st = engine.stats()
+    assert st["graph_steps"] > 0 and st["free_blocks"] == 64 and engine.block_manager.audit() == ""
+
+
+def test_generation_survives_preemption(folders):
+    """So few pages that requests are pre-empted and recomputed: the tokens are
+    the same as without pressure."""
+    cfg, w, d32, _ = folders["a"]
+    prompts = [fixtures.random_ids(cfg, n, 70 + n) for n in (9, 14, 11, 6)]
+    engine = LLMEngine.from_pretrained(d32, dtype="float32", num_blocks=14, block_size=4, max_num_seqs=4,
+                                       max_num_batched_tokens=32)
+    outs = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.output_tokens == plain_llama.plain_greedy_generate(cfg, w, p, 20), o
+    assert engine.stats()["preemptions"] > 0 and engine.block_manager.audit() == ""
+    assert engine.block_manager.get_num_free_blocks() == 14
+
+
+def test_end_of_sequence_stops_and_too_long_fails(folders):
+    cfg, w, d32, _ = folders["b"]
+    prompt = fixtures.random_ids(cfg, 12, 5)
+    free_run = plain_llama.plain_greedy_generate(cfg, w, prompt, 12)
+    raw = dict(cfg, eos_token_id=[free_run[4], 9999 % cfg["vocab_size"]])
+    import json
+    import shutil
+    import tempfile
+    with tempfile.TemporaryDirectory() as d:
+        shutil.copy(os.path.join(d32, "model.safetensors"), d)
+        json.dump(raw, open(os.path.join(d, "config.json"), "w"))
+        engine = LLMEngine.from_pretrained(d, dtype="float32", num_blocks=32, block_size=8, max_num_seqs=2,
+                                           max_num_batched_tokens=64, max_model_len=40)
+        o1, o2, o3 = engine.generate([prompt, prompt, fixtures.random_ids(cfg, 40, 6)],
+                                     [SamplingParams(temperature=0.0, max_tokens=12),
+                                      SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True),
+                                      SamplingParams(temperature=0.0, max_tokens=4)])
+    first_stop = free_run.index(free_run[4])
+    assert o1.output_tokens == free_run[:first_stop + 1] and o1.finish_reason == "stop"
+    assert o2.output_tokens == free_run and o2.finish_reason == "length"
+    assert o3.finish_reason == "error" and "max_model_len" in o3.error
+
+
+def test_temperature_sampling_is_seeded_and_batch_independent(folders):
+    cfg, w, _, d16 = folders["b"]
+    prompts = [fixtures.random_ids(cfg, n, 90 + n) for n in (7, 23, 4)]
+    sp = [SamplingParams(temperature=0.9, top_k=40, top_p=0.95, max_tokens=10, ignore_eos=True, seed=100 + i) for i in range(3)]
+    engine = LLMEngine.from_pretrained(d16, dtype="bfloat16", num_blocks=64, block_size=8, max_num_seqs=4,
+                                       max_num_batched_tokens=64)
+    together = [o.output_tokens for o in engine.generate(prompts, sp)]
+    alone = [engine.generate([p], [s])[0].output_tokens for p, s in zip(prompts, sp)]
+    assert together == alone
+    other = engine.generate([prompts[0]], [SamplingParams(temperature=0.9, max_tokens=10, ignore_eos=True, seed=7)])
+    assert other[0].output_tokens != together[0] and all(0 <= t < cfg["vocab_size"] for t in other[0].output_tokens)
+
+
+def test_command_line(folders):
+    cfg, w, d32, _ = folders["a"]
+    prompt = fixtures.random_ids(cfg, 9, 3)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "lyapunov"), "generate", "--model", d32, "--prompt-ids",
+           ",".join(map(str, prompt)), "--max-tokens", "6", "--temperature", "0", "--dtype", "float32",
+           "--block-size", "4", "--num-blocks", "32", "--max-num-seqs", "2", "--max-batched-tokens", "64", "--ignore-eos"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    last = out.stdout.strip().split("\n")[-1]
+    assert [int(t) for t in last.split()] == plain_llama.plain_greedy_generate(cfg, w, prompt, 6)
+
+
+def test_no_cpu_path():
+    from lyapunov_engine_b200 import ops
+    with pytest.raises(ops.KernelError, match="CUDA"):
+        ops.swiglu(torch.zeros(2, 4), torch.zeros(2, 8))
+    with pytest.raises(ops.KernelError, match="CPU"):
+        load_model(config=fixtures.TINY_A, random_seed=0, dtype="float32", device="cpu")
+
+
+# ---- each part of a layer alone, against its plain function
+class _Ctx:
+    pass
+
+
+def _runtime(dtype):
+    from lyapunov_engine_b200.engine.runtime import Runtime
+    return Runtime("cuda:0", dtype, max_model_len=64)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_parts_alone(dtype):
+    from lyapunov_engine_b200.parts import FEED_FORWARDS, NORMS, POSITION_ENCODINGS, PartSpec
+    rt = _runtime(dtype)
+    g = torch.Generator().manual_seed(0)
+    Hh, Ii, T = 72, 200, 11
+    tensors = {"n": 1 + 0.1 * torch.randn(Hh, generator=g), "g": torch.randn(Ii, Hh, generator=g) * 0.1,
+               "u": torch.randn(Ii, Hh, generator=g) * 0.1, "d": torch.randn(Hh, Ii, generator=g) * 0.1}
+
+    def get(name):
+        t = tensors[name]
+        return t.to("cuda:0", torch.float32 if name == "n" else dtype)
+    ctx = _Ctx()
+    ctx.workspace = rt.workspace
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+    rounded = {k: (v if k == "n" else v.to(dtype).float()) for k, v in tensors.items()}
+
+    norm = NORMS.build(PartSpec("rmsnorm", {"hidden_size": Hh, "eps": 1e-6, "weight_name": "n"}))
+    assert [d.name for d in norm.tensors()] == ["n"] and norm.tensors()[0].role == "vector"
+    norm.bind(get, rt)
+    resid = torch.randn(T, Hh, generator=g)
+    delta = torch.randn(T, Hh, generator=g).to(dtype)
+    r = resid.to("cuda:0")
+    out = norm.apply(r, delta.to("cuda:0"))
+    torch.testing.assert_close(out.float().cpu(), plain_llama.plain_rmsnorm(resid + delta.float(), tensors["n"], 1e-6), **tol)
+
+    ff = FEED_FORWARDS.build(PartSpec("gated_silu", {"hidden_size": Hh, "intermediate_size": Ii, "gate_name": "g",
+                                                     "up_name": "u", "down_name": "d"}))
+    assert [d.shape for d in ff.tensors()] == [(Ii, Hh), (Ii, Hh), (Hh, Ii)]
+    ff.bind(get, rt)
+    x = torch.randn(T, Hh, generator=g).to(dtype)
+    y = ff.forward(x.to("cuda:0"), ctx)
+    want = plain_llama.plain_mlp(x.float(), rounded["g"], rounded["u"], rounded["d"], act_dtype=None if dtype == torch.float32 else dtype)
+    torch.testing.assert_close(y.float().cpu(), want, **tol)
+
+    scaling = dict(fixtures.TINY_B["rope_scaling"])
+    rope = POSITION_ENCODINGS.build(PartSpec("rotary", {"head_dim": 32, "theta": 500000.0, "max_positions": 64, "scaling": scaling}))
+    table = rope.build_table(64)
+    inv = plain_llama.plain_inv_freq(32, 500000.0, scaling)
+    cos, sin = plain_llama.plain_cos_sin(torch.arange(64), inv)
+    assert torch.equal(table[:, :16], cos[:, :16]) and torch.equal(table[:, 16:], sin[:, :16])
