@@ -163,6 +163,9 @@ PYBIND11_MODULE(_host, m) {
       .def_readonly("off_tile_request", &PackedStep::off_tile_request)
       .def_readonly("off_tile_q0", &PackedStep::off_tile_q0)
       .def_readonly("num_tiles", &PackedStep::num_tiles)
+      .def_readonly("num_tiles_multi", &PackedStep::num_tiles_multi)
+      .def_readonly("off_decode_requests", &PackedStep::off_decode_requests)
+      .def_readonly("num_decode", &PackedStep::num_decode)
       .def_readonly("total", &PackedStep::total);
 
   m.def(

@@ -62,11 +62,18 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
   p.off_state_slots = take(B);
   p.off_wanted_rows = take(std::max(p.num_wanted, 1));
   for (int g = 0; g < groups; ++g) p.off_block_tables.push_back(take(static_cast<int64_t>(B) * p.max_blocks[g]));
+  p.num_decode = B - real;
+  for (const auto &e : entries) p.num_decode += e.count == 1;
+  p.off_decode_requests = take(std::max(p.num_decode, 1));
   for (int ts : tile_sizes) {
     if (ts < 1) throw std::invalid_argument("pack_step: tile sizes must be >= 1");
-    int n = B - real;
-    for (const auto &e : entries) n += (e.count + ts - 1) / ts;
+    int n = B - real, multi = 0;
+    for (const auto &e : entries) {
+      n += (e.count + ts - 1) / ts;
+      if (e.count > 1) multi += (e.count + ts - 1) / ts;
+    }
     p.num_tiles.push_back(n);
+    p.num_tiles_multi.push_back(multi);
     p.off_tile_request.push_back(take(n));
     p.off_tile_q0.push_back(take(n));
   }
@@ -117,12 +124,22 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
       for (int i = n; i < width; ++i) row[i] = null_page;
     }
   }
+  {
+    int32_t *dec = dest + p.off_decode_requests;
+    int n = 0;
+    for (int b = 0; b < B; ++b)
+      if ((b < real ? entries[b].count : 1) == 1) dec[n++] = b;
+    if (n == 0) dec[0] = 0;
+  }
   for (size_t k = 0; k < tile_sizes.size(); ++k) {
     int32_t *tr = dest + p.off_tile_request[k], *tq = dest + p.off_tile_q0[k];
     int n = 0;
-    for (int b = 0; b < B; ++b) {
-      const int count = b < real ? entries[b].count : 1;
-      for (int q0 = 0; q0 < count; q0 += tile_sizes[k]) { tr[n] = b; tq[n] = q0; ++n; }
+    for (int pass = 0; pass < 2; ++pass) {   // requests with several tokens first, then single tokens
+      for (int b = 0; b < B; ++b) {
+        const int count = b < real ? entries[b].count : 1;
+        if ((pass == 0) != (count > 1)) continue;
+        for (int q0 = 0; q0 < count; q0 += tile_sizes[k]) { tr[n] = b; tq[n] = q0; ++n; }
+      }
     }
   }
   return p;

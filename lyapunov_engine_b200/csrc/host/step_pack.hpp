@@ -28,8 +28,11 @@ struct PackedStep {
   std::vector<int64_t> off_block_tables;  // per group, [B, max_blocks[g]]
   std::vector<int> max_blocks;
   std::vector<int> tile_sizes;
-  std::vector<int64_t> off_tile_request, off_tile_q0;  // per tile size
+  std::vector<int64_t> off_tile_request, off_tile_q0;  // per tile size; multi-token requests first
   std::vector<int> num_tiles;
+  std::vector<int> num_tiles_multi;  // how many of them belong to requests that bring more than one token
+  int64_t off_decode_requests{0};    // the requests that bring exactly one token (padding included)
+  int num_decode{0};
   int64_t total{0};      // integers used
 };
 

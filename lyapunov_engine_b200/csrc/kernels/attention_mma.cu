@@ -1,0 +1,561 @@
+// Tensor-core attention over the paged cache for bfloat16, head sizes 16..128:
+//   * le_attention_prefill_bf16: portions of prompts (any number of query
+//     tokens per request), FlashAttention-2 style: a block owns 64 query
+//     tokens of one head, walks the keys in tiles of 64 with a running maximum
+//     and sum, S = Q K^T and O += P V on mma.sync m16n8k16 with 32-bit
+//     accumulators, softmax in 32 bits (exp2 with the scale folded in);
+//   * le_attention_decode_bf16: single decoded tokens, the keys of a request
+//     split over several blocks (flash-decoding) so that a small batch still
+//     fills the GPU; the query heads of one group are the 16 rows of the MMA
+//     and share every key and value that is read; partial results (32-bit
+//     output, maximum, sum) go to scratch memory and le_attention_merge sums
+//     them.
+// Keys and values are gathered row by row through the block table with
+// 16-byte cp.async copies into a swizzled shared-memory tile, several tiles in
+// flight, so any page size works and a page's rows need not be adjacent.
+// One formula for every cut: the query at absolute position p sees keys
+// max(0, p - window + 1) .. p of its own request.
+//
+// Reference: flash_attn_v2.cu:13-212 (contiguous keys, scalar dot products,
+// top-left mask), flash_decoding.cu:13-147 (contiguous keys, every thread
+// walks the whole partition), paged_attention.cu:9-109 (one key at a time).
+// Compiled once per head size (LE_HEAD_DIM).
+#include "common.cuh"
+
+#ifndef LE_HEAD_DIM
+#error "compile with -DLE_HEAD_DIM=<head size>"
+#endif
+
+#if LE_HEAD_DIM <= 128
+
+namespace {
+
+constexpr int HD = LE_HEAD_DIM;
+constexpr int CPR = HD / 8;        // 16-byte chunks per row
+constexpr int KSTEPS = HD / 16;    // k-steps of S = Q K^T
+constexpr int NT_O = HD / 8;       // n-tiles of the output
+constexpr int BN = 64;             // keys per tile
+constexpr float LOG2E = 1.4426950408889634f;
+
+using bf16 = __nv_bfloat16;
+
+// Element (row, 16-byte chunk) of a [rows][HD] tile lives at this chunk index:
+// an XOR swizzle inside each 128-byte line so that the 8 rows one ldmatrix
+// reads fall into different banks.
+__device__ __forceinline__ int swizzled_chunk(int row, int chunk) {
+  const int id = row * CPR + chunk;
+  const int line = id >> 3, pos = id & 7;
+  const int key = (CPR >= 8) ? (row & 7) : (line & 7);
+  return (line << 3) | (pos ^ key);
+}
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem, bool valid) {
+  const int bytes = valid ? 16 : 0;   // zero-fill when the row is not there
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(smem)), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// Copies keys [k0, k0 + BN) of one kv head into a swizzled tile; rows at or
+// after `k_end` are zero-filled.  `threads` threads take part.
+__device__ __forceinline__ void load_kv_tile(bf16 *k_tile, bf16 *v_tile, const bf16 *__restrict__ k_cache,
+                                             const bf16 *__restrict__ v_cache, const int32_t *__restrict__ table,
+                                             int k0, int k_end, int kvh, int num_kv_heads, int page_size, int num_pages,
+                                             int tid, int threads, int *status) {
+  for (int c = tid; c < BN * CPR; c += threads) {
+    const int row = c / CPR, chunk = c % CPR;
+    const int pos = k0 + row;
+    bool valid = pos < k_end;
+    int64_t offset = 0;
+    if (valid) {
+      const int page = table[pos / page_size];
+      if (page < 0 || page >= num_pages) {
+        atomicOr(status, LE_STATUS_BAD_PAGE);
+        valid = false;
+      } else {
+        offset = ((static_cast<int64_t>(page) * num_kv_heads + kvh) * page_size + pos % page_size) * HD + chunk * 8;
+      }
+    }
+    const int dst = swizzled_chunk(row, chunk) * 8;
+    cp_async16(k_tile + dst, k_cache + offset, valid);
+    cp_async16(v_tile + dst, v_cache + offset, valid);
+  }
+}
+
+// S[16 x 64] += Q[16 x HD] K^T for one warp: q fragments in registers, keys
+// rows [key0, key0 + 8 * NT) of the tile.
+template <int NT>
+__device__ __forceinline__ void scores(float (&s)[NT][4], const uint32_t (&qf)[KSTEPS][4], const bf16 *k_tile, int key0, int lane) {
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+    for (int nt = 0; nt < NT; nt += 2) {
+      uint32_t b[4];
+      const int j = lane >> 3;
+      const int row = key0 + nt * 8 + (j >> 1) * 8 + (lane & 7);
+      ldmatrix_x4(b, k_tile + swizzled_chunk(row, ks * 2 + (j & 1)) * 8);
+      mma_bf16(s[nt], qf[ks], b[0], b[1]);
+      mma_bf16(s[nt + 1], qf[ks], b[2], b[3]);
+    }
+  }
+}
+
+// O[16 x HD] += P[16 x 16*KK] V for one warp: probabilities as A fragments.
+template <int KK>
+__device__ __forceinline__ void weighted_values(float (&o)[NT_O][4], const uint32_t (&pf)[KK][4], const bf16 *v_tile, int key0, int lane) {
+#pragma unroll
+  for (int kk = 0; kk < KK; ++kk) {
+#pragma unroll
+    for (int nt = 0; nt < NT_O; nt += 2) {
+      uint32_t b[4];
+      const int j = lane >> 3;
+      const int row = key0 + kk * 16 + (j & 1) * 8 + (lane & 7);
+      ldmatrix_x4_trans(b, v_tile + swizzled_chunk(row, nt + (j >> 1)) * 8);
+      mma_bf16(o[nt], pf[kk], b[0], b[1]);
+      mma_bf16(o[nt + 1], pf[kk], b[2], b[3]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- prefill
+constexpr int PF_BM = 64;
+constexpr int PF_THREADS = 128;
+constexpr int PF_STAGES = 2;
+
+__global__ void __launch_bounds__(PF_THREADS)
+attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 *__restrict__ q, int64_t q_stride,
+                         const bf16 *__restrict__ k_cache, const bf16 *__restrict__ v_cache,
+                         const int32_t *__restrict__ block_table, int max_blocks, const int32_t *__restrict__ cu_q,
+                         const int32_t *__restrict__ ctx_before, const int32_t *__restrict__ tile_request,
+                         const int32_t *__restrict__ tile_q0, int num_heads, int num_kv_heads, int page_size,
+                         int num_pages, int window, float scale, int *__restrict__ status) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  bf16 *q_tile = reinterpret_cast<bf16 *>(smem_raw);
+  bf16 *k_tiles = q_tile + PF_BM * HD;
+  bf16 *v_tiles = k_tiles + PF_STAGES * BN * HD;
+
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int kvh = head / (num_heads / num_kv_heads);
+  const int b = tile_request[tile];
+  const int q0 = tile_q0[tile];
+  const int q_len = cu_q[b + 1] - cu_q[b];
+  const int rows = min(PF_BM, q_len - q0);
+  const int tok0 = cu_q[b] + q0;
+  const int p0 = ctx_before[b] + q0;
+  const int p_last = p0 + rows - 1;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int32_t *table = block_table + static_cast<int64_t>(b) * max_blocks;
+
+  // queries of this tile (rows beyond the request's tokens are zero)
+  for (int c = tid; c < PF_BM * CPR; c += PF_THREADS) {
+    const int row = c / CPR, chunk = c % CPR;
+    const bool valid = row < rows;
+    const bf16 *src = q + (tok0 + (valid ? row : 0)) * q_stride + head * HD + chunk * 8;
+    cp_async16(q_tile + swizzled_chunk(row, chunk) * 8, src, valid);
+  }
+  int k_begin = 0;
+  if (window > 0) k_begin = max(0, p0 - window + 1) / BN * BN;
+  const int k_end = p_last + 1;
+  const int num_tiles = (k_end - k_begin + BN - 1) / BN;
+
+  load_kv_tile(k_tiles, v_tiles, k_cache, v_cache, table, k_begin, k_end, kvh, num_kv_heads, page_size, num_pages, tid,
+               PF_THREADS, status);
+  cp_async_commit();
+
+  uint32_t qf[KSTEPS][4];
+  float o[NT_O][4];
+#pragma unroll
+  for (int nt = 0; nt < NT_O; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};   // rows g and g + 8 of this warp
+  const float sl2 = scale * LOG2E;
+  const int row_lo = warp * 16 + g, row_hi = row_lo + 8;
+  const int p_row[2] = {p0 + row_lo, p0 + row_hi};
+  const int lo_row[2] = {window > 0 ? max(0, p_row[0] - window + 1) : 0, window > 0 ? max(0, p_row[1] - window + 1) : 0};
+  const bool row_ok[2] = {row_lo < rows, row_hi < rows};
+
+  for (int it = 0; it < num_tiles; ++it) {
+    const int k0 = k_begin + it * BN;
+    const int stage = it % PF_STAGES;
+    if (it + 1 < num_tiles) {
+      const int next = (it + 1) % PF_STAGES;
+      load_kv_tile(k_tiles + next * BN * HD, v_tiles + next * BN * HD, k_cache, v_cache, table, k0 + BN, k_end, kvh,
+                   num_kv_heads, page_size, num_pages, tid, PF_THREADS, status);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (it == 0) {
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        const int j = lane >> 3;
+        const int row = warp * 16 + (j & 1) * 8 + (lane & 7);
+        ldmatrix_x4(qf[ks], q_tile + swizzled_chunk(row, ks * 2 + (j >> 1)) * 8);
+      }
+    }
+    // a warp whose rows all lie before this tile's first key has nothing to do
+    const bf16 *k_tile = k_tiles + stage * BN * HD, *v_tile = v_tiles + stage * BN * HD;
+    float s[BN / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+    scores<BN / 8>(s, qf, k_tile, 0, lane);
+
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        const int pos = k0 + nt * 8 + 2 * t + (e & 1);
+        const bool seen = row_ok[r] && pos <= p_row[r] && pos >= lo_row[r];
+        s[nt][e] = seen ? s[nt][e] * sl2 : -INFINITY;
+        tile_max[r] = fmaxf(tile_max[r], s[nt][e]);
+      }
+    }
+    float alpha[2], m_new[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+      m_new[r] = fmaxf(m_run[r], tile_max[r]);
+      alpha[r] = (m_new[r] == -INFINITY) ? 1.0f : exp2f(m_run[r] - m_new[r]);
+      m_run[r] = m_new[r];
+      l_run[r] *= alpha[r];
+    }
+    uint32_t pf[BN / 16][4];
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        const float p = (s[nt][e] == -INFINITY) ? 0.0f : exp2f(s[nt][e] - m_new[r]);
+        s[nt][e] = p;
+        l_run[r] += p;
+      }
+    }
+#pragma unroll
+    for (int kk = 0; kk < BN / 16; ++kk) {
+      pf[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      pf[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      pf[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      pf[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT_O; ++nt) {
+      o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0];
+      o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
+    }
+    weighted_values<BN / 16>(o, pf, v_tile, 0, lane);
+    __syncthreads();   // everyone is done with this stage before it is filled again
+  }
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  const float inv[2] = {l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f};
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (!row_ok[r]) continue;
+    bf16 *dst = out + (tok0 + (r ? row_hi : row_lo)) * out_stride + head * HD;
+#pragma unroll
+    for (int nt = 0; nt < NT_O; ++nt) {
+      *reinterpret_cast<uint32_t *>(dst + nt * 8 + 2 * t) = pack_bf16(o[nt][2 * r] * inv[r], o[nt][2 * r + 1] * inv[r]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- decode
+constexpr int DC_THREADS = 128;
+constexpr int DC_STAGES = 4;
+
+// Scratch per (request, head, split): HD floats of unnormalised output, then
+// the maximum (in log2 units) and the sum.
+__global__ void __launch_bounds__(DC_THREADS)
+attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__restrict__ part_o, float *__restrict__ part_ml,
+                        const bf16 *__restrict__ q, int64_t q_stride, const bf16 *__restrict__ k_cache,
+                        const bf16 *__restrict__ v_cache, const int32_t *__restrict__ block_table, int max_blocks,
+                        const int32_t *__restrict__ cu_q, const int32_t *__restrict__ ctx_before,
+                        const int32_t *__restrict__ requests, int num_heads, int num_kv_heads, int page_size,
+                        int num_pages, int window, float scale, int num_splits, int *__restrict__ status) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  bf16 *k_tiles = reinterpret_cast<bf16 *>(smem_raw);
+  bf16 *v_tiles = k_tiles + DC_STAGES * BN * HD;
+
+  const int split = blockIdx.x;
+  const int group = num_heads / num_kv_heads;
+  const int row_tiles = (group + 15) / 16;
+  const int kvh = blockIdx.y / row_tiles;
+  const int h0 = kvh * group + (blockIdx.y % row_tiles) * 16;    // first query head of this block
+  const int heads_here = min(16, kvh * group + group - h0);
+  const int b = requests ? requests[blockIdx.z] : blockIdx.z;
+  const int tok = cu_q[b];                                        // a decode request brings one token
+  const int p = ctx_before[b];                                    // its position; keys 0 .. p
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int32_t *table = block_table + static_cast<int64_t>(b) * max_blocks;
+
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int total = p + 1 - lo;
+  int per_split = (total + num_splits - 1) / num_splits;
+  per_split = (per_split + BN - 1) / BN * BN;
+  const int k_begin = lo + split * per_split;
+  const int k_end = min(p + 1, k_begin + per_split);
+  const int num_tiles = k_end > k_begin ? (k_end - k_begin + BN - 1) / BN : 0;
+
+  // query fragments straight from global memory: rows are the group's heads
+  uint32_t qf[KSTEPS][4];
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = g + (i & 1) * 8;
+      const int dim = ks * 16 + 2 * t + (i >> 1) * 8;
+      qf[ks][i] = row < heads_here ? *reinterpret_cast<const uint32_t *>(q + tok * q_stride + (h0 + row) * HD + dim) : 0u;
+    }
+  }
+
+  float o[NT_O][4];
+#pragma unroll
+  for (int nt = 0; nt < NT_O; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  const float sl2 = scale * LOG2E;
+
+  // prologue: fill the pipeline
+#pragma unroll
+  for (int sidx = 0; sidx < DC_STAGES - 1; ++sidx) {
+    if (sidx < num_tiles)
+      load_kv_tile(k_tiles + sidx * BN * HD, v_tiles + sidx * BN * HD, k_cache, v_cache, table, k_begin + sidx * BN, k_end,
+                   kvh, num_kv_heads, page_size, num_pages, tid, DC_THREADS, status);
+    cp_async_commit();
+  }
+  for (int it = 0; it < num_tiles; ++it) {
+    cp_async_wait<DC_STAGES - 2>();
+    __syncthreads();                       // tile `it` has landed; the stage used by it - 1 is free
+    const int nxt = it + DC_STAGES - 1;
+    if (nxt < num_tiles) {
+      const int st = nxt % DC_STAGES;
+      load_kv_tile(k_tiles + st * BN * HD, v_tiles + st * BN * HD, k_cache, v_cache, table, k_begin + nxt * BN, k_end, kvh,
+                   num_kv_heads, page_size, num_pages, tid, DC_THREADS, status);
+    }
+    cp_async_commit();
+    const int stage = it % DC_STAGES;
+    const bf16 *k_tile = k_tiles + stage * BN * HD, *v_tile = v_tiles + stage * BN * HD;
+    const int k0 = k_begin + it * BN + warp * 16;            // this warp's 16 keys of the tile
+    if (k0 >= k_end) continue;                               // (uniform per warp)
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+    scores<2>(s, qf, k_tile, warp * 16, lane);
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int pos = k0 + nt * 8 + 2 * t + (e & 1);
+        s[nt][e] = pos < k_end ? s[nt][e] * sl2 : -INFINITY;
+        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[nt][e]);
+      }
+    }
+    float alpha[2], m_new[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+      m_new[r] = fmaxf(m_run[r], tile_max[r]);
+      alpha[r] = (m_new[r] == -INFINITY) ? 1.0f : exp2f(m_run[r] - m_new[r]);
+      m_run[r] = m_new[r];
+      l_run[r] *= alpha[r];
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pr = (s[nt][e] == -INFINITY) ? 0.0f : exp2f(s[nt][e] - m_new[e >> 1]);
+        s[nt][e] = pr;
+        l_run[e >> 1] += pr;
+      }
+    }
+    uint32_t pf[1][4];
+    pf[0][0] = pack_bf16(s[0][0], s[0][1]);
+    pf[0][1] = pack_bf16(s[0][2], s[0][3]);
+    pf[0][2] = pack_bf16(s[1][0], s[1][1]);
+    pf[0][3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+    for (int nt = 0; nt < NT_O; ++nt) {
+      o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0];
+      o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
+    }
+    weighted_values<1>(o, pf, v_tile, warp * 16, lane);
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // merge the four warps through shared memory (the tiles are no longer needed)
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  float *sm_o = reinterpret_cast<float *>(smem_raw);            // [4 warps][16 rows][HD]
+  float *sm_m = sm_o + 4 * 16 * HD;                             // [4][16]
+  float *sm_l = sm_m + 4 * 16;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = g + 8 * r;
+#pragma unroll
+    for (int nt = 0; nt < NT_O; ++nt) {
+      sm_o[(warp * 16 + row) * HD + nt * 8 + 2 * t] = o[nt][2 * r];
+      sm_o[(warp * 16 + row) * HD + nt * 8 + 2 * t + 1] = o[nt][2 * r + 1];
+    }
+    if (t == 0) {
+      sm_m[warp * 16 + row] = m_run[r];
+      sm_l[warp * 16 + row] = l_run[r];
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < heads_here * HD; i += DC_THREADS) {
+    const int row = i / HD, d = i % HD;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, sm_m[w * 16 + row]);
+    float acc = 0.0f, l = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sm_m[w * 16 + row];
+      const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
+      acc += f * sm_o[(w * 16 + row) * HD + d];
+      l += f * sm_l[w * 16 + row];
+    }
+    const int head = h0 + row;
+    if (num_splits == 1) {
+      out[tok * out_stride + head * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    } else {
+      const int64_t slot = (static_cast<int64_t>(blockIdx.z) * num_heads + head) * num_splits + split;
+      part_o[slot * HD + d] = acc;
+      if (d == 0) {
+        part_ml[slot * 2] = m;
+        part_ml[slot * 2 + 1] = l;
+      }
+    }
+  }
+}
+
+// out[request, head] = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s
+__global__ void attention_merge_kernel(bf16 *__restrict__ out, int64_t out_stride, const float *__restrict__ part_o,
+                                       const float *__restrict__ part_ml, const int32_t *__restrict__ cu_q,
+                                       const int32_t *__restrict__ requests, int num_heads, int num_splits) {
+  const int head = blockIdx.x, z = blockIdx.y;
+  const int b = requests ? requests[z] : z;
+  const int tok = cu_q[b];
+  const int64_t base = (static_cast<int64_t>(z) * num_heads + head) * num_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.0f, l = 0.0f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float ms = part_ml[(base + s) * 2];
+      if (ms == -INFINITY) continue;
+      const float f = exp2f(ms - m);
+      acc += f * part_o[(base + s) * HD + d];
+      l += f * part_ml[(base + s) * 2 + 1];
+    }
+    out[tok * out_stride + head * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+  }
+}
+
+}  // namespace
+
+LE_API int le_attention_mma_available() { return 1; }
+
+LE_API int le_attention_prefill_bf16(void *out, int64_t out_stride, const void *q, int64_t q_stride, const void *k_cache,
+                                     const void *v_cache, const int32_t *block_table, int max_blocks, const int32_t *cu_q,
+                                     const int32_t *ctx_before, const int32_t *tile_request, const int32_t *tile_q0,
+                                     int num_tiles, int num_heads, int num_kv_heads, int page_size, int num_pages,
+                                     int window, float scale, int *status, cudaStream_t stream) {
+  if (num_tiles <= 0) return 0;
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads) return le::invalid("le_attention_prefill_bf16: %d heads do not divide into %d groups", num_heads, num_kv_heads);
+  if (num_heads > 65535) return le::invalid("le_attention_prefill_bf16: too many heads for one launch");
+  const size_t smem = static_cast<size_t>(PF_BM + 2 * PF_STAGES * BN) * HD * sizeof(bf16);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return le::invalid("le_attention_prefill_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+  }
+  dim3 grid(num_tiles, num_heads);
+  attention_prefill_kernel<<<grid, PF_THREADS, smem, stream>>>(
+      static_cast<bf16 *>(out), out_stride, static_cast<const bf16 *>(q), q_stride, static_cast<const bf16 *>(k_cache),
+      static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before, tile_request, tile_q0, num_heads,
+      num_kv_heads, page_size, num_pages, window, scale, status);
+  return le::launched();
+}
+
+// Floats of scratch the decode kernel needs for `num_requests` requests.
+LE_API int64_t le_attention_decode_scratch_floats(int num_requests, int num_heads, int num_splits) {
+  return num_splits <= 1 ? 0 : static_cast<int64_t>(num_requests) * num_heads * num_splits * (HD + 2);
+}
+
+// `requests` (optional): the indices of the batch's decode requests; without
+// it requests 0 .. num_requests-1 are taken.  `scratch` holds
+// le_attention_decode_scratch_floats(...) floats.
+LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratch, const void *q, int64_t q_stride,
+                                    const void *k_cache, const void *v_cache, const int32_t *block_table, int max_blocks,
+                                    const int32_t *cu_q, const int32_t *ctx_before, const int32_t *requests,
+                                    int num_requests, int num_heads, int num_kv_heads, int page_size, int num_pages,
+                                    int window, float scale, int num_splits, int *status, cudaStream_t stream) {
+  if (num_requests <= 0) return 0;
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads) return le::invalid("le_attention_decode_bf16: %d heads do not divide into %d groups", num_heads, num_kv_heads);
+  if (num_splits < 1 || num_splits > 65535) return le::invalid("le_attention_decode_bf16: %d splits", num_splits);
+  if (num_splits > 1 && scratch == nullptr) return le::invalid("le_attention_decode_bf16: splitting the keys needs scratch memory");
+  const int group = num_heads / num_kv_heads;
+  const int row_tiles = (group + 15) / 16;
+  if (num_kv_heads * row_tiles > 65535 || num_requests > 65535) return le::invalid("le_attention_decode_bf16: the batch is too large for one launch");
+  size_t smem = static_cast<size_t>(2 * DC_STAGES * BN) * HD * sizeof(bf16);
+  const size_t merge = static_cast<size_t>(4 * 16 * HD + 2 * 4 * 16) * sizeof(float);
+  if (merge > smem) smem = merge;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return le::invalid("le_attention_decode_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+  }
+  float *part_o = scratch;
+  float *part_ml = scratch ? scratch + static_cast<int64_t>(num_requests) * num_heads * num_splits * HD : nullptr;
+  dim3 grid(num_splits, num_kv_heads * row_tiles, num_requests);
+  attention_decode_kernel<<<grid, DC_THREADS, smem, stream>>>(
+      static_cast<bf16 *>(out), out_stride, part_o, part_ml, static_cast<const bf16 *>(q), q_stride,
+      static_cast<const bf16 *>(k_cache), static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before,
+      requests, num_heads, num_kv_heads, page_size, num_pages, window, scale, num_splits, status);
+  int rc = le::launched();
+  if (rc != 0 || num_splits == 1) return rc;
+  dim3 mgrid(num_heads, num_requests);
+  attention_merge_kernel<<<mgrid, HD < 32 ? 32 : (HD > 128 ? 128 : HD), 0, stream>>>(
+      static_cast<bf16 *>(out), out_stride, part_o, part_ml, cu_q, requests, num_heads, num_splits);
+  return le::launched();
+}
+
+#else  // head sizes above 128 use the generic kernel
+
+LE_API int le_attention_mma_available() { return 0; }
+
+#endif

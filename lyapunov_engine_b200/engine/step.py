@@ -16,6 +16,8 @@ runs whole prompts one by one or one token per request, never a mix.
 """
 from __future__ import annotations
 
+import gc
+
 import numpy as np
 import torch
 
@@ -28,7 +30,8 @@ class StepContext:
     numbers the host keeps."""
     __slots__ = ("num_tokens", "num_requests", "num_wanted", "max_q_len", "max_context", "pure_decode",
                  "token_ids", "positions", "request_of_token", "cu_q", "ctx_before", "state_slots", "wanted_rows",
-                 "block_tables", "tiles", "workspace", "status", "q_lens")
+                 "block_tables", "tiles", "workspace", "status", "q_lens", "decode_requests", "num_decode",
+                 "context_bound")
 
 
 class ModelRunner:
@@ -52,7 +55,7 @@ class ModelRunner:
 
     # ---- integer buffers
     def _upper_bound(self, tokens: int, requests: int) -> int:
-        n = 4 * tokens + 16 * (requests + 1)
+        n = 4 * tokens + 20 * (requests + 1)
         n += sum(requests * w for w in self.fixed_max_blocks)
         for ts in self.tile_sizes:
             n += 2 * (tokens // ts + requests + 4)
@@ -101,8 +104,13 @@ class ModelRunner:
         c.state_slots = d[layout.off_state_slots:layout.off_state_slots + B]
         c.wanted_rows = d[layout.off_wanted_rows:layout.off_wanted_rows + max(c.num_wanted, 1)][:c.num_wanted]
         c.block_tables = [d[o:o + B * w].view(B, w) for o, w in zip(layout.off_block_tables, layout.max_blocks)]
-        c.tiles = {ts: (d[a:a + n], d[b:b + n], n) for ts, a, b, n in
-                   zip(layout.tile_sizes, layout.off_tile_request, layout.off_tile_q0, layout.num_tiles)}
+        # per tile size: (request of each tile, its first query token, tiles, tiles of multi-token requests)
+        c.tiles = {ts: (d[a:a + n], d[b:b + n], n, m) for ts, a, b, n, m in
+                   zip(layout.tile_sizes, layout.off_tile_request, layout.off_tile_q0, layout.num_tiles,
+                       layout.num_tiles_multi)}
+        c.num_decode = layout.num_decode
+        c.decode_requests = d[layout.off_decode_requests:layout.off_decode_requests + max(layout.num_decode, 1)]
+        c.context_bound = layout.max_context
         c.workspace = workspace
         c.status = self.runtime.status
         return c
@@ -177,16 +185,26 @@ class _DecodeGraph:
             raise RuntimeError("the integer buffer moved after a decode graph was captured")
         if self.graph is None:
             ctx = r._context(layout, self.workspace, num_wanted=self.bucket)
+            ctx.context_bound = r.max_model_len      # a captured step serves every later context length
             if self.logits is None:
                 self.logits = r.model.forward(ctx, r.cache)   # eager warm-up on the real data
                 self._warm = True
                 return self.logits
             # Capture.  The step's integers are already on the device; the
             # captured kernels read them from the same addresses every time.
+            # No garbage collection while capturing: destroying an older graph
+            # (or freeing device memory) during capture invalidates it.
             torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                self.logits = r.model.forward(ctx, r.cache)
+            gc.collect()
+            was_enabled = gc.isenabled()
+            gc.disable()
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self.logits = r.model.forward(ctx, r.cache)
+            finally:
+                if was_enabled:
+                    gc.enable()
             self.graph = graph
             # Capturing does not run the kernels: replay for this step's result.
         self.graph.replay()

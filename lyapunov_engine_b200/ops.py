@@ -101,11 +101,20 @@ def attention_lib(head_dim: int):
         lib = build.load_attention(head_dim)
         _declare(lib, _ATTENTION_SIGNATURES)
         _declare(lib, _EXTRA_ATTENTION_SIGNATURES)
+        lib.le_attention_mma_available.restype = c_int
+        lib.le_attention_mma_available.argtypes = []
         _attention[head_dim] = lib
     return lib
 
 
-_EXTRA_ATTENTION_SIGNATURES: dict[str, list] = {}
+_EXTRA_ATTENTION_SIGNATURES: dict[str, list] = {
+    "le_attention_prefill_bf16": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                  c_void_p, c_void_p],
+    "le_attention_decode_bf16": [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                 c_int, c_void_p, c_void_p],
+}
 
 
 # Launch counters (own kernels, library products) for the benchmark's report.
@@ -261,6 +270,50 @@ def attention_generic(out, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx
                                     _ptr(ctx_before), _ptr(tile_request), _ptr(tile_q0), num_tiles, num_heads,
                                     num_kv_heads, page_size, k_cache.shape[0], int(window or 0), float(scale),
                                     _ptr(status), _stream()), "le_attention_generic", lib)
+
+
+def attention_mma_available(head_dim: int) -> bool:
+    """Whether the tensor-core attention kernels exist for this head size."""
+    lib = attention_lib(head_dim)
+    return bool(lib.le_attention_mma_available())
+
+
+def attention_prefill_bf16(out, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, tile_request, tile_q0,
+                           num_tiles, num_heads, num_kv_heads, head_dim, page_size, window, scale, status) -> None:
+    """Tensor-core attention for requests that bring several tokens; the tiles
+    list 64 query tokens each."""
+    _need_cuda(out, q, k_cache, v_cache, block_table)
+    lib = attention_lib(head_dim)
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[1] == num_heads * head_dim
+    assert k_cache.dtype == torch.bfloat16 and k_cache.shape[1:] == (num_kv_heads, page_size, head_dim)
+    _check(lib.le_attention_prefill_bf16(_ptr(out), out.stride(0), _ptr(q), q_stride, _ptr(k_cache), _ptr(v_cache),
+                                         _ptr(block_table), block_table.shape[1], _ptr(cu_q), _ptr(ctx_before),
+                                         _ptr(tile_request), _ptr(tile_q0), num_tiles, num_heads, num_kv_heads,
+                                         page_size, k_cache.shape[0], int(window or 0), float(scale), _ptr(status),
+                                         _stream()), "le_attention_prefill_bf16", lib)
+
+
+def attention_decode_scratch_floats(head_dim: int, num_requests: int, num_heads: int, num_splits: int) -> int:
+    return 0 if num_splits <= 1 else num_requests * num_heads * num_splits * (head_dim + 2)
+
+
+def attention_decode_bf16(out, scratch, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, requests,
+                          num_requests, num_heads, num_kv_heads, head_dim, page_size, window, scale, num_splits,
+                          status) -> None:
+    """Split-key tensor-core attention for requests that bring one token.
+    ``scratch``: float32, attention_decode_scratch_floats(...) elements."""
+    _need_cuda(out, q, k_cache, v_cache, block_table, scratch)
+    lib = attention_lib(head_dim)
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[1] == num_heads * head_dim
+    assert k_cache.dtype == torch.bfloat16 and k_cache.shape[1:] == (num_kv_heads, page_size, head_dim)
+    if num_splits > 1:
+        assert scratch is not None and scratch.dtype == torch.float32
+        assert scratch.numel() >= attention_decode_scratch_floats(head_dim, num_requests, num_heads, num_splits)
+    _check(lib.le_attention_decode_bf16(_ptr(out), out.stride(0), _ptr(scratch), _ptr(q), q_stride, _ptr(k_cache),
+                                        _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
+                                        _ptr(ctx_before), _ptr(requests), num_requests, num_heads, num_kv_heads,
+                                        page_size, k_cache.shape[0], int(window or 0), float(scale), num_splits,
+                                        _ptr(status), _stream()), "le_attention_decode_bf16", lib)
 
 
 def argmax(out: torch.Tensor, logits: torch.Tensor) -> None:

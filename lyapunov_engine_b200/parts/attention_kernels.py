@@ -1,20 +1,29 @@
-"""Chooses the attention kernel for a step.
+"""Chooses the attention kernels for a step.
 
-float32: the FP32-pipe kernel for every shape.  bfloat16: the tensor-core
-kernels where they apply (portions of prompts; single decoded tokens split over
-the keys), else the same generic kernel.  All of them read keys and values
-through the block table and give the same result up to rounding.
+float32: the FP32-pipe kernel for every shape.  bfloat16 with head sizes up to
+128: the tensor-core kernels, one for the requests that bring several tokens
+(portions of prompts) and a split-key one for the requests that bring a single
+decoded token; in a mixed step both run, each on its own requests.  Other
+cases (bfloat16 with larger heads) use the generic kernel.  All of them read
+keys and values through the block table and give the same result up to
+rounding.
 """
 from __future__ import annotations
+
+import torch
 
 from .. import ops
 
 GENERIC_TILE = 16
+PREFILL_TILE = 64
+DECODE_KEYS_PER_SPLIT = 256     # a split is worth its launch from about four tiles of keys
+DECODE_MAX_SPLITS = 64
+TARGET_BLOCKS = 3 * 148         # blocks of the decode kernel that are resident at once on a B200
 
 
 def tile_sizes() -> list[int]:
     """Query-tile sizes the kernels want listed in the step's integers."""
-    return [GENERIC_TILE]
+    return [GENERIC_TILE, PREFILL_TILE]
 
 
 def prepare(head_dim: int) -> None:
@@ -22,8 +31,31 @@ def prepare(head_dim: int) -> None:
     ops.attention_lib(head_dim)
 
 
+def decode_splits(num_requests: int, num_heads: int, num_kv_heads: int, context_bound: int) -> int:
+    group = num_heads // num_kv_heads
+    blocks = num_requests * num_kv_heads * ((group + 15) // 16)
+    by_blocks = (TARGET_BLOCKS + blocks - 1) // blocks
+    by_keys = max(1, (context_bound + DECODE_KEYS_PER_SPLIT - 1) // DECODE_KEYS_PER_SPLIT)
+    return max(1, min(by_blocks, by_keys, DECODE_MAX_SPLITS))
+
+
 def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, window, scale) -> None:
-    tiles = ctx.tiles[GENERIC_TILE]
-    ops.attention_generic(out, qkv, qkv.stride(0), kv.k, kv.v, ctx.block_tables[kv.group], ctx.cu_q, ctx.ctx_before,
-                          tiles[0], tiles[1], tiles[2], num_heads, num_kv_heads, head_dim, kv.page_size, window,
-                          scale, ctx.status)
+    table = ctx.block_tables[kv.group]
+    if out.dtype == torch.bfloat16 and ops.attention_mma_available(head_dim):
+        req, q0, n_tiles, n_multi = ctx.tiles[PREFILL_TILE]
+        if n_multi:
+            ops.attention_prefill_bf16(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0,
+                                       n_multi, num_heads, num_kv_heads, head_dim, kv.page_size, window, scale,
+                                       ctx.status)
+        if ctx.num_decode:
+            splits = decode_splits(ctx.num_decode, num_heads, num_kv_heads, ctx.context_bound)
+            floats = ops.attention_decode_scratch_floats(head_dim, ctx.num_decode, num_heads, splits)
+            scratch = ctx.workspace.get("attention_scratch", (floats,), torch.float32) if floats else None
+            requests = None if ctx.num_decode == ctx.num_requests else ctx.decode_requests
+            ops.attention_decode_bf16(out, scratch, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before,
+                                      requests, ctx.num_decode, num_heads, num_kv_heads, head_dim, kv.page_size,
+                                      window, scale, splits, ctx.status)
+        return
+    req, q0, n_tiles, _ = ctx.tiles[GENERIC_TILE]
+    ops.attention_generic(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0, n_tiles,
+                          num_heads, num_kv_heads, head_dim, kv.page_size, window, scale, ctx.status)

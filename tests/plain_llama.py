@@ -112,12 +112,14 @@ def plain_rotate_half(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> 
     return x * cos + rotated * sin
 
 
-def plain_attention(q, k, v, window: int | None = None) -> torch.Tensor:
+def plain_attention(q, k, v, window: int | None = None, prob_dtype=None) -> torch.Tensor:
     """Causal grouped-query attention over a whole sequence
     (python/lyapunov_engine/ops.py:100-121): scale 1/sqrt(hd), kv heads
     repeated for their group, keys after the query masked, softmax, times V.
     q: [nh, T, hd]; k, v: [nkv, T, hd].  ``window`` (not in the reference):
-    a query at p sees keys p-window+1 .. p only."""
+    a query at p sees keys p-window+1 .. p only.  ``prob_dtype`` models a
+    pipeline that stores exp(score - max) in that type before it multiplies by
+    V (and still divides by the unrounded sum)."""
     nh, T, hd = q.shape
     nkv = k.shape[0]
     scale = 1.0 / (hd ** 0.5)
@@ -130,6 +132,9 @@ def plain_attention(q, k, v, window: int | None = None) -> torch.Tensor:
     if window is not None:
         mask |= torch.tril(torch.ones(T, T, dtype=torch.bool), diagonal=-window)
     scores = scores.masked_fill(mask, float("-inf"))
+    if prob_dtype is not None:
+        p = torch.exp(scores - scores.max(dim=-1, keepdim=True).values)
+        return torch.matmul(rounded(p, prob_dtype), v) / p.sum(dim=-1, keepdim=True)
     probs = torch.softmax(scores, dim=-1)
     return torch.matmul(probs, v)
 
@@ -142,7 +147,7 @@ def rounded(x: torch.Tensor, act_dtype) -> torch.Tensor:
     return x if act_dtype is None else x.to(act_dtype).to(x.dtype)
 
 
-def plain_attention_layer(x, wq, wk, wv, wo, nh, nkv, hd, cos, sin, window=None, act_dtype=None):
+def plain_attention_layer(x, wq, wk, wv, wo, nh, nkv, hd, cos, sin, window=None, act_dtype=None, prob_dtype=None):
     """q/k/v projections, head split, RoPE on q and k, attention, o projection
     (python/lyapunov_engine/models/llama.py:61-106)."""
     T = x.shape[0]
@@ -151,7 +156,7 @@ def plain_attention_layer(x, wq, wk, wv, wo, nh, nkv, hd, cos, sin, window=None,
     v = rounded(x @ wv.T, act_dtype).view(T, nkv, hd).transpose(0, 1)
     q = rounded(plain_rotate_half(q, cos, sin), act_dtype)
     k = rounded(plain_rotate_half(k, cos, sin), act_dtype)
-    o = rounded(plain_attention(q, k, v, window), act_dtype)
+    o = rounded(plain_attention(q, k, v, window, prob_dtype), act_dtype)
     o = o.transpose(0, 1).contiguous().view(T, nh * hd)
     return rounded(o @ wo.T, act_dtype)
 
@@ -168,7 +173,7 @@ def plain_mlp(x, w_gate, w_up, w_down, act_dtype=None) -> torch.Tensor:
     return rounded(rounded(act, act_dtype) @ w_down.T, act_dtype)
 
 
-def plain_block(h, w: dict, prefix: str, cfg: dict, cos, sin, window=None, act_dtype=None):
+def plain_block(h, w: dict, prefix: str, cfg: dict, cos, sin, window=None, act_dtype=None, prob_dtype=None):
     """Pre-norm residual block (python/lyapunov_engine/models/llama.py:136-165)."""
     eps = float(cfg["rms_norm_eps"])
     nh = cfg["num_attention_heads"]
@@ -181,7 +186,7 @@ def plain_block(h, w: dict, prefix: str, cfg: dict, cos, sin, window=None, act_d
         w[prefix + "self_attn.k_proj.weight"],
         w[prefix + "self_attn.v_proj.weight"],
         w[prefix + "self_attn.o_proj.weight"],
-        nh, nkv, hd, cos, sin, window, act_dtype,
+        nh, nkv, hd, cos, sin, window, act_dtype, prob_dtype,
     )
     h = h + a
     n = rounded(plain_rmsnorm(h, w[prefix + "post_attention_layernorm.weight"], eps), act_dtype)
@@ -195,7 +200,7 @@ def plain_block(h, w: dict, prefix: str, cfg: dict, cos, sin, window=None, act_d
     return h + m
 
 
-def plain_forward(cfg: dict, w: dict, ids, windows=None, act_dtype=None) -> torch.Tensor:
+def plain_forward(cfg: dict, w: dict, ids, windows=None, act_dtype=None, prob_dtype=None) -> torch.Tensor:
     """Logits [T, V] of one whole sequence starting at position 0
     (python/lyapunov_engine/models/llama.py:196-225).  The output head is
     ``lm_head.weight`` when the folder has it, else the embedding matrix
@@ -211,7 +216,7 @@ def plain_forward(cfg: dict, w: dict, ids, windows=None, act_dtype=None) -> torc
     cos, sin = cos.to(dtype), sin.to(dtype)
     for i in range(cfg["num_hidden_layers"]):
         window = windows[i] if windows is not None else None
-        h = plain_block(h, w, f"model.layers.{i}.", cfg, cos, sin, window, act_dtype)
+        h = plain_block(h, w, f"model.layers.{i}.", cfg, cos, sin, window, act_dtype, prob_dtype)
     n = rounded(plain_rmsnorm(h, w["model.norm.weight"], float(cfg["rms_norm_eps"])), act_dtype)
     head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
     return n @ head.T

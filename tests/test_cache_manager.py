@@ -190,9 +190,16 @@ def test_pack_step_layout():
     table = buf[p.off_block_tables[0]:p.off_block_tables[0] + B * 6].reshape(B, 6)
     assert table[0].tolist() == a.get_block_table() + [20] * 4 and table[1].tolist() == b.get_block_table() + [20] * 5
     assert table[2].tolist() == [20] * 6                       # padding writes to the page nobody owns
-    assert p.num_tiles == [5, 4]
+    assert p.num_tiles == [5, 4] and p.num_tiles_multi == [3, 2] and p.num_decode == 2
     assert buf[p.off_tile_request[0]:p.off_tile_request[0] + 5].tolist() == [0, 1, 1, 2, 3]
     assert buf[p.off_tile_q0[0]:p.off_tile_q0[0] + 5].tolist() == [0, 0, 2, 0, 0]
+    assert buf[p.off_decode_requests:p.off_decode_requests + 2].tolist() == [2, 3]
+    # single-token requests come after the others in the tile lists
+    c = host.Sequence(2, [1, 2, 3], host.SamplingParams())
+    bm.grow(c, 2); c.set_num_computed_tokens(2); bm.grow(c, 3)
+    p2 = host.pack_step([host.StepEntry(c, 2, 1, [0]), host.StepEntry(b, 0, 3, [])], bm, [2], 0, [], buf.ctypes.data, buf.size)
+    assert buf[p2.off_tile_request[0]:p2.off_tile_request[0] + 3].tolist() == [1, 1, 0] and p2.num_tiles_multi == [2]
+    assert buf[p2.off_decode_requests:p2.off_decode_requests + 1].tolist() == [0] and p2.num_decode == 1
     with pytest.raises(ValueError, match="starts at"):
         host.pack_step([host.StepEntry(a, 4, 2, [])], bm, [], 0, [], 0, 0)
     with pytest.raises(ValueError, match="wanted place"):

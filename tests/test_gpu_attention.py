@@ -98,3 +98,55 @@ def test_generic_kernel(case, dtype):
     ops.check_status(status)
     tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
     torch.testing.assert_close(out.float().cpu(), c["want"], **tol)
+
+
+MMA_CASES = CASES[:6] + [
+    (32, 8, 64, 16, [1] * 8, [4095, 17, 0, 63, 64, 1000, 2047, 300], None),     # the 1B model's decode shape
+    (24, 8, 128, 16, [200, 1, 1, 64, 1], [0, 900, 5, 64, 129], None),
+    (32, 1, 32, 8, [1, 1, 3], [77, 300, 10], None),                            # 32 query heads on one kv head: two row tiles
+    (4, 4, 96, 16, [130], [700], 256),
+    (2, 1, 112, 4, [1, 1], [511, 40], 100),
+]
+
+
+@pytest.mark.parametrize("case", MMA_CASES)
+def test_tensor_core_kernels(case):
+    """Requests with several tokens go to the prefill kernel, single tokens to
+    the split-key decode kernel, exactly as in a mixed step."""
+    from lyapunov_engine_b200 import ops
+    nh, nkv, hd, page, q_lens, ctx_before, window = case
+    dtype = torch.bfloat16
+    c = build_case(dtype, nh, nkv, hd, page, q_lens, ctx_before, seed=hd + page + len(q_lens), window=window)
+    assert ops.attention_mma_available(hd)
+    status = ops.new_status(DEV)
+    multi = [b for b, n in enumerate(q_lens) if n > 1]
+    single = [b for b, n in enumerate(q_lens) if n == 1]
+    for splits in (1, 3, 16):
+        out = torch.full((c["T"], nh * hd), 7.0, dtype=dtype, device=DEV)
+        if multi:
+            req, q0 = [], []
+            for b in multi:
+                for s in range(0, q_lens[b], 64):
+                    req.append(b); q0.append(s)
+            ops.attention_prefill_bf16(out, c["q"], c["q"].stride(0), c["k"], c["v"], c["table"], c["cu"], c["ctx"],
+                                       torch.tensor(req, dtype=torch.int32, device=DEV),
+                                       torch.tensor(q0, dtype=torch.int32, device=DEV), len(req), nh, nkv, hd, page,
+                                       window, 1.0 / hd ** 0.5, status)
+        if single:
+            floats = ops.attention_decode_scratch_floats(hd, len(single), nh, splits)
+            scratch = torch.full((max(floats, 1),), float("nan"), device=DEV)
+            requests = None if len(single) == len(q_lens) else torch.tensor(single, dtype=torch.int32, device=DEV)
+            ops.attention_decode_bf16(out, scratch, c["q"], c["q"].stride(0), c["k"], c["v"], c["table"], c["cu"],
+                                      c["ctx"], requests, len(single), nh, nkv, hd, page, window, 1.0 / hd ** 0.5,
+                                      splits, status)
+        ops.check_status(status)
+        torch.testing.assert_close(out.float().cpu(), c["want"], atol=2e-2, rtol=2e-2)
+
+
+def test_decode_splits_choice():
+    from lyapunov_engine_b200.parts.attention_kernels import decode_splits
+    assert decode_splits(64, 32, 8, 4096) == 1
+    assert decode_splits(8, 32, 8, 4096) == 7
+    assert decode_splits(1, 32, 8, 4096) == 16
+    assert decode_splits(1, 32, 8, 100) == 1
+    assert decode_splits(1, 32, 8, 131072) == 56

@@ -15,9 +15,9 @@ pytestmark = pytest.mark.gpu
 
 # name: (config, page, weight seed, std, norm_std, qk_gain)
 MODELS = {
-    "tiny_a": (fixtures.TINY_A, fixtures.TINY_A_PAGE, 0, 0.05, 0.0, 5.0),
-    "tiny_b": (fixtures.TINY_B, fixtures.TINY_B_PAGE, 1, 0.05, 0.1, 5.0),
-    "tiny_c": (fixtures.TINY_C, fixtures.TINY_C_PAGE, 2, 0.04, 0.1, 4.0),
+    "tiny_a": (fixtures.TINY_A, fixtures.TINY_A_PAGE, 0, 0.05, 0.0, 4.0),
+    "tiny_b": (fixtures.TINY_B, fixtures.TINY_B_PAGE, 1, 0.05, 0.1, 3.0),
+    "tiny_c": (fixtures.TINY_C, fixtures.TINY_C_PAGE, 2, 0.04, 0.1, 3.0),
 }
 LENGTHS = {"tiny_a": (21, 33, 49, 70), "tiny_b": (25, 32, 64, 121), "tiny_c": (40, 65, 130, 300)}
 PROMPTS = {"tiny_a": (5, 17, 33, 38), "tiny_b": (1, 8, 40, 97), "tiny_c": (8, 33, 98, 268)}
@@ -25,12 +25,15 @@ PROMPTS = {"tiny_a": (5, 17, 33, 38), "tiny_b": (1, 8, 40, 97), "tiny_c": (8, 33
 # float32: different summation orders of the same 32-bit arithmetic.
 F32_TOL = dict(atol=1e-4, rtol=1e-4)
 # bfloat16: the plain implementation rounds its activations to bfloat16 where the
-# pipeline stores them (plain_llama.rounded).  What is left is the order of
-# accumulation inside the products now and then flipping one of those roundings
-# by a unit in the last place, which peaked attention then amplifies.  That
-# noise is measured, not guessed: the plain implementation is run with 32-bit
-# and with 64-bit accumulation, and the engine may differ from it by three
-# times the largest difference between those two.
+# pipeline stores them (plain_llama.rounded), the softmax numerators included
+# (the tensor cores take them as bfloat16).  What is left is the order of
+# accumulation inside the products, and which maximum the numerators were
+# scaled by when they were rounded, now and then flipping one of those
+# roundings by a unit in the last place, which peaked attention then
+# amplifies.  That noise is measured, not guessed: the plain implementation is
+# run a second time with 64-bit accumulation and unrounded numerators, and the
+# engine may differ from the first run by three times the largest difference
+# between the two.
 BF16_FLOORS = 3.0
 
 
@@ -48,7 +51,8 @@ def models(tmp_path_factory):
         prompt_lens = {f"r{i}": n for i, n in enumerate(PROMPTS[name])}
         rounded = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
         ref32 = {r: plain_llama.plain_forward(cfg, w, ids) for r, ids in requests.items()}
-        ref16 = {r: plain_llama.plain_forward(cfg, rounded, ids, act_dtype=torch.bfloat16) for r, ids in requests.items()}
+        ref16 = {r: plain_llama.plain_forward(cfg, rounded, ids, act_dtype=torch.bfloat16, prob_dtype=torch.bfloat16)
+                 for r, ids in requests.items()}
         rounded64 = {k: v.double() for k, v in rounded.items()}
         floor = max(float((plain_llama.plain_forward(cfg, rounded64, ids, act_dtype=torch.bfloat16).float() - ref16[r]).abs().max())
                     for r, ids in requests.items())
@@ -116,7 +120,8 @@ def test_mixed_with_page_reuse(models, name, dtype, tmp_path):
             weights = {k: v.to(torch.bfloat16).float() for k, v in weights.items()}
     for rid, ids in requests.items():
         if rid not in ref:
-            ref[rid] = plain_llama.plain_forward(cfg, weights, ids, act_dtype=torch.bfloat16 if dtype == "bfloat16" else None)
+            low = torch.bfloat16 if dtype == "bfloat16" else None
+            ref[rid] = plain_llama.plain_forward(cfg, weights, ids, act_dtype=low, prob_dtype=low)
     m2 = dict(m, requests=requests, prompt_lens=prompt_lens, ref={dtype: ref})
     trace = ru.mixed_trace(requests, prompt_lens, chunk=16, max_live=4, seed=3)
     assert any(len(s["entries"]) >= 3 for s in trace.steps)
