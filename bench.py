@@ -211,6 +211,20 @@ def run_ours(args):
         best.sort()
         return best[len(best) // 2]
 
+    if args.only:
+        # A short run of one kind of step, for profilers: no CUDA graph, so
+        # that every kernel shows as its own launch.
+        runner.use_cuda_graphs = not args.no_cuda_graphs
+        if args.only == "decode":
+            ms, _, _ = timed_decode(args.batch, args.steps, args.warmup, CONTEXT)
+            print(json.dumps({"only": "decode", "batch": args.batch, "context": CONTEXT, "ms_per_step": round(ms, 4),
+                              "layers": cfg["num_hidden_layers"], "cuda_graph": runner.use_cuda_graphs}))
+        else:
+            ms = timed_prefill(PREFILL_TOKENS, args.steps, args.warmup)
+            print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(ms, 4),
+                              "layers": cfg["num_hidden_layers"]}))
+        return 0
+
     clocks = ClockSampler()
     clocks.start()
     time.sleep(0.3)
@@ -323,11 +337,15 @@ def main():
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
+    p.add_argument("--only", choices=["decode", "prefill"], default=None, help="run one kind of step and exit (for profilers)")
+    p.add_argument("--batch", type=int, default=8, help="batch of --only decode")
+    p.add_argument("--no-cuda-graphs", action="store_true", help="with --only decode: launch every kernel by itself")
     args = p.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
-    args.warmup = max(args.warmup, 3)
+    if not args.only:
+        args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
