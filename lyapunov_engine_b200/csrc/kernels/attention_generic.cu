@@ -154,6 +154,9 @@ attention_generic_kernel(T *__restrict__ out, int64_t out_stride, const T *__res
 
 LE_API int le_attention_head_dim() { return HD; }
 
+// Each library keeps its own message of the last refused call.
+LE_API const char *le_last_error() { return le::error_buffer(); }
+
 // out: [T, num_heads * HD] with row stride out_stride; q: rows of stride
 // q_stride holding num_heads * HD query values; caches [pages, kv_heads,
 // page, HD].  tile_request / tile_q0 list the tiles of 16 query tokens.

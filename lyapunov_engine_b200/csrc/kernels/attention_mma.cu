@@ -554,6 +554,65 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
   return le::launched();
 }
 
+// ---------------------------------------------------------------- no allocation
+// The same decode attention with its scratch inside the library, for callers
+// that cannot allocate (see attention_static_scratch.h for who they are and
+// what the limits are).
+#include <mutex>
+
+#include "attention_static_scratch.h"
+
+static __device__ __align__(256) float le_static_scratch[LE_STATIC_SCRATCH_FLOATS];
+
+namespace {
+
+// In host code `le_static_scratch` is only a handle for the runtime, not an
+// address a kernel could use; the device address is looked up once per device.
+int static_scratch_address(float **address) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex guard;
+  static float *per_device[kMaxDevices] = {};
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return le::invalid("le_attention_decode_bf16_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= kMaxDevices) return le::invalid("le_attention_decode_bf16_static: device %d is beyond the %d this library tracks", device, kMaxDevices);
+  std::lock_guard<std::mutex> lock(guard);
+  if (per_device[device] == nullptr) {
+    void *p = nullptr;
+    e = cudaGetSymbolAddress(&p, le_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return le::invalid("le_attention_decode_bf16_static: cudaGetSymbolAddress on device %d: %s", device, cudaGetErrorString(e));
+    per_device[device] = static_cast<float *>(p);
+  }
+  *address = per_device[device];
+  return 0;
+}
+
+}  // namespace
+
+LE_API int le_attention_decode_bf16_static(void *out, int64_t out_stride, const void *q, int64_t q_stride,
+                                           const void *k_cache, const void *v_cache, const int32_t *block_table,
+                                           int max_blocks, const int32_t *cu_q, const int32_t *ctx_before,
+                                           const int32_t *requests, int num_requests, int num_heads, int num_kv_heads,
+                                           int page_size, int num_pages, int window, float scale, int num_splits,
+                                           int *status, cudaStream_t stream) {
+  if (num_requests <= 0) return 0;
+  if (num_heads <= 0 || num_splits < 1) return le::invalid("le_attention_decode_bf16_static: %d heads, %d splits", num_heads, num_splits);
+  const int64_t need = le_attention_decode_scratch_floats(num_requests, num_heads, num_splits);
+  if (need > LE_STATIC_SCRATCH_FLOATS)
+    return le::invalid("le_attention_decode_bf16_static: %d requests x %d heads x %d splits need %lld floats of scratch, "
+                       "the built-in array holds %d; use fewer splits or le_attention_decode_bf16 with your own scratch",
+                       num_requests, num_heads, num_splits, static_cast<long long>(need), LE_STATIC_SCRATCH_FLOATS);
+  float *scratch = nullptr;
+  if (need > 0) {
+    const int rc = static_scratch_address(&scratch);
+    if (rc != 0) return rc;
+  }
+  return le_attention_decode_bf16(out, out_stride, scratch, q, q_stride, k_cache, v_cache, block_table, max_blocks, cu_q,
+                                  ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size, num_pages,
+                                  window, scale, num_splits, status, stream);
+}
+
 #else  // head sizes above 128 use the generic kernel
 
 LE_API int le_attention_mma_available() { return 0; }
