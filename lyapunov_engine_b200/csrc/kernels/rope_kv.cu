@@ -64,6 +64,76 @@ __global__ void rope_kv_kernel(T *__restrict__ qkv, T *__restrict__ k_cache, T *
   }
 }
 
+// The same work with 16-byte accesses: one block per token walks all heads;
+// a thread takes VEC consecutive dimensions of the low half together with their
+// partners in the high half.  Needs rot/2 and head_dim to be multiples of VEC.
+template <typename T>
+struct alignas(16) Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  T v[N];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_vec_kernel(T *__restrict__ qkv, T *__restrict__ k_cache, T *__restrict__ v_cache,
+                   const float *__restrict__ cos_sin, const int32_t *__restrict__ positions,
+                   const int32_t *__restrict__ request_of_token, const int32_t *__restrict__ block_table,
+                   int max_blocks, int num_heads, int num_kv_heads, int head_dim, int rot, int max_pos, int page_size,
+                   int num_pages, int write_kv, int *__restrict__ status) {
+  constexpr int VEC = Vec16<T>::N;
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  if (pos < 0 || pos >= max_pos) {
+    if (threadIdx.x == 0) atomicOr(status, LE_STATUS_BAD_POSITION);
+    return;
+  }
+  const int heads = num_heads + (write_kv ? 2 * num_kv_heads : 0);
+  const int chunks = head_dim / VEC, half_chunks = rot / 2 / VEC, rot_chunks = rot / VEC;
+  const int row = (num_heads + 2 * num_kv_heads) * head_dim;
+  T *x_row = qkv + static_cast<int64_t>(t) * row;
+  int64_t kv_base = -1;
+  if (write_kv) {
+    const int b = request_of_token[t];
+    const int page = block_table[static_cast<int64_t>(b) * max_blocks + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, LE_STATUS_BAD_PAGE);
+    } else {
+      kv_base = (static_cast<int64_t>(page) * num_kv_heads * page_size + pos % page_size) * head_dim;
+    }
+  }
+  const float *cs = cos_sin + static_cast<int64_t>(pos) * rot;
+  const int half = rot / 2;
+  for (int item = threadIdx.x; item < heads * chunks; item += blockDim.x) {
+    const int h = item / chunks, c = item % chunks;
+    const bool is_q = h < num_heads;
+    const bool is_k = !is_q && h < num_heads + num_kv_heads;
+    T *x = x_row + static_cast<int64_t>(h) * head_dim;
+    T *dst = x;
+    if (!is_q) {
+      if (kv_base < 0) continue;
+      const int kvh = is_k ? h - num_heads : h - num_heads - num_kv_heads;
+      dst = (is_k ? k_cache : v_cache) + kv_base + static_cast<int64_t>(kvh) * page_size * head_dim;
+    }
+    if ((is_q || is_k) && c < rot_chunks) {
+      if (c >= half_chunks) continue;        // the partner chunk does both
+      const Vec16<T> lo = *reinterpret_cast<const Vec16<T> *>(x + c * VEC);
+      const Vec16<T> hi = *reinterpret_cast<const Vec16<T> *>(x + half + c * VEC);
+      Vec16<T> out_lo, out_hi;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float x0 = le::to_f32(lo.v[i]), x1 = le::to_f32(hi.v[i]);
+        const float cc = cs[c * VEC + i], ss = cs[half + c * VEC + i];
+        out_lo.v[i] = le::from_f32<T>(x0 * cc - x1 * ss);
+        out_hi.v[i] = le::from_f32<T>(x1 * cc + x0 * ss);
+      }
+      *reinterpret_cast<Vec16<T> *>(dst + c * VEC) = out_lo;
+      *reinterpret_cast<Vec16<T> *>(dst + half + c * VEC) = out_hi;
+    } else if (dst != x) {
+      *reinterpret_cast<Vec16<T> *>(dst + c * VEC) = *reinterpret_cast<const Vec16<T> *>(x + c * VEC);
+    }
+  }
+}
+
 }  // namespace
 
 LE_API int le_rope_kv_write(void *qkv, int dtype, void *k_cache, void *v_cache, const float *cos_sin,
@@ -73,6 +143,15 @@ LE_API int le_rope_kv_write(void *qkv, int dtype, void *k_cache, void *v_cache, 
   if (num_tokens <= 0) return 0;
   if (rot < 0 || rot > head_dim || rot % 2) return le::invalid("le_rope_kv_write: rotary width %d must be even and at most head_dim %d", rot, head_dim);
   if (num_heads + 2 * num_kv_heads > 65535) return le::invalid("le_rope_kv_write: too many heads for one launch");
+  const int vec = dtype == LE_BF16 ? 8 : 4;
+  if (head_dim % vec == 0 && (rot / 2) % vec == 0) {
+    LE_DISPATCH_DTYPE(dtype, T,
+                      rope_kv_vec_kernel<T><<<num_tokens, 256, 0, stream>>>(
+                          static_cast<T *>(qkv), static_cast<T *>(k_cache), static_cast<T *>(v_cache), cos_sin, positions,
+                          request_of_token, block_table, max_blocks, num_heads, num_kv_heads, head_dim, rot, max_pos,
+                          page_size, num_pages, write_kv, status));
+    return le::launched();
+  }
   dim3 grid(num_tokens, num_heads + 2 * num_kv_heads);
   int threads = 32;
   while (threads < head_dim / 2 && threads < 128) threads *= 2;

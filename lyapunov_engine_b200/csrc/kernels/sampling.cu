@@ -94,6 +94,43 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(int32_t *__restrict__ o
   if (threadIdx.x == 0) out[blockIdx.x] = idx;
 }
 
+// Two stages for wide vocabularies: blocks of a row's chunks, then one block per row.
+constexpr int ARGMAX_CHUNK = 4096;
+
+__global__ void __launch_bounds__(256) argmax_partial_kernel(float *__restrict__ part_val, int32_t *__restrict__ part_idx,
+                                                             const float *__restrict__ logits, int vocab, int64_t stride,
+                                                             int chunks) {
+  __shared__ float fs[33];
+  __shared__ int is[33];
+  const int row = blockIdx.y, chunk = blockIdx.x;
+  const int begin = chunk * ARGMAX_CHUNK;
+  const int n = min(ARGMAX_CHUNK, vocab - begin);
+  const int idx = block_argmax(logits + row * stride + begin, n, fs, is);
+  if (threadIdx.x == 0) {
+    part_val[row * chunks + chunk] = fs[32];
+    part_idx[row * chunks + chunk] = begin + idx;
+  }
+}
+
+__global__ void argmax_final_kernel(int32_t *__restrict__ out, const float *__restrict__ part_val,
+                                    const int32_t *__restrict__ part_idx, int chunks) {
+  const int row = blockIdx.x;
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int c = threadIdx.x; c < chunks; c += 32) {
+    const float v = part_val[row * chunks + c];
+    const int i = part_idx[row * chunks + c];
+    if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ob > best || (ob == best && oi < idx)) { best = ob; idx = oi; }
+  }
+  if (threadIdx.x == 0) out[row] = idx;
+}
+
 // params per row: temperature, top_p (floats), top_k, seed_lo, seed_hi, counter (ints).
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(int32_t *__restrict__ out, const float *__restrict__ logits, int vocab, int64_t stride,
@@ -204,9 +241,23 @@ sample_kernel(int32_t *__restrict__ out, const float *__restrict__ logits, int v
 
 }  // namespace
 
-LE_API int le_argmax(int32_t *out, const float *logits, int num_rows, int vocab, int64_t stride, cudaStream_t stream) {
+// `scratch` (optional): room for num_rows * ceil(vocab / 4096) floats and as
+// many ints after them; with it a wide vocabulary is searched by many blocks.
+LE_API int le_argmax(int32_t *out, const float *logits, int num_rows, int vocab, int64_t stride, float *scratch,
+                     cudaStream_t stream) {
   if (num_rows <= 0) return 0;
-  argmax_kernel<<<num_rows, THREADS, 0, stream>>>(out, logits, vocab, stride);
+  const int chunks = (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+  if (scratch == nullptr || chunks < 4) {
+    argmax_kernel<<<num_rows, THREADS, 0, stream>>>(out, logits, vocab, stride);
+    return le::launched();
+  }
+  if (num_rows > 65535) return le::invalid("le_argmax: too many rows for one launch");
+  float *part_val = scratch;
+  int32_t *part_idx = reinterpret_cast<int32_t *>(scratch + static_cast<int64_t>(num_rows) * chunks);
+  argmax_partial_kernel<<<dim3(chunks, num_rows), 256, 0, stream>>>(part_val, part_idx, logits, vocab, stride, chunks);
+  int rc = le::launched();
+  if (rc != 0) return rc;
+  argmax_final_kernel<<<num_rows, 32, 0, stream>>>(out, part_val, part_idx, chunks);
   return le::launched();
 }
 

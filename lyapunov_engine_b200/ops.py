@@ -63,7 +63,7 @@ _CORE_SIGNATURES = {
                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "le_gemm_simt": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                      c_void_p],
-    "le_argmax": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p],
+    "le_argmax": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p],
     "le_sample": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_void_p, c_void_p],
 }
@@ -316,11 +316,19 @@ def attention_decode_bf16(out, scratch, q, q_stride, k_cache, v_cache, block_tab
                                         _ptr(status), _stream()), "le_attention_decode_bf16", lib)
 
 
-def argmax(out: torch.Tensor, logits: torch.Tensor) -> None:
-    _need_cuda(out, logits)
+def argmax_scratch_floats(num_rows: int, vocab: int) -> int:
+    return 2 * num_rows * ((vocab + 4095) // 4096)
+
+
+def argmax(out: torch.Tensor, logits: torch.Tensor, scratch=None) -> None:
+    """out[r] = index of the first maximum of logits[r].  ``scratch`` (float32,
+    argmax_scratch_floats elements) lets many blocks search one wide row."""
+    _need_cuda(out, logits, scratch)
     n, V = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and logits.stride(1) == 1
-    _check(core().le_argmax(_ptr(out), _ptr(logits), n, V, logits.stride(0), _stream()), "le_argmax")
+    if scratch is not None:
+        assert scratch.dtype == torch.float32 and scratch.numel() >= argmax_scratch_floats(n, V)
+    _check(core().le_argmax(_ptr(out), _ptr(logits), n, V, logits.stride(0), _ptr(scratch), _stream()), "le_argmax")
 
 
 def sample(out, logits, temperature, top_p, top_k, seeds, uniforms=None, probs_out=None) -> None:

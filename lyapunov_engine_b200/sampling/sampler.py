@@ -22,6 +22,7 @@ class Sampler:
         self._host = torch.empty((max_rows, 6), dtype=torch.int32, pin_memory=True)
         self._dev = torch.empty((max_rows, 6), dtype=torch.int32, device=device)
         self._out = torch.empty(max_rows, dtype=torch.int32, device=device)
+        self._scratch = None
 
     def sample(self, logits: torch.Tensor, params: list, token_indices: list[int]) -> torch.Tensor:
         """``logits`` [n, V] float32; ``params[i]`` the SamplingParams of row i;
@@ -30,7 +31,10 @@ class Sampler:
         n = logits.shape[0]
         out = self._out[:n]
         if all(p.temperature < 1e-4 for p in params):
-            ops.argmax(out, logits)
+            need = ops.argmax_scratch_floats(self.max_rows, logits.shape[1])
+            if self._scratch is None or self._scratch.numel() < need:
+                self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+            ops.argmax(out, logits, self._scratch)
             return out
         host = self._host.numpy()
         f = host.view(np.float32)

@@ -163,14 +163,18 @@ def test_linear_bf16(M, N, K):
     torch.testing.assert_close(out16.float().cpu(), want, atol=0.05, rtol=1e-2)
 
 
-def test_argmax_first_of_equal_maxima():
-    logits = torch.randn(6, 1003)
-    logits[2, 17] = logits[2, 900] = 50.0
-    logits[4, 1002] = 60.0
+@pytest.mark.parametrize("vocab,scratch", [(1003, False), (1003, True), (128256, True), (20001, True)])
+def test_argmax_first_of_equal_maxima(vocab, scratch):
+    logits = torch.randn(6, vocab)
+    logits[2, 17] = logits[2, vocab - 103] = 50.0
+    logits[4, vocab - 1] = 60.0
+    edge = 4095 if vocab > 4096 else 500          # a tie across the boundary of two blocks' chunks
+    logits[5, edge + 1] = logits[5, edge] = 55.0
     out = torch.empty(6, dtype=torch.int32, device=DEV)
-    ops().argmax(out, logits.to(DEV))
+    buf = torch.empty(ops().argmax_scratch_floats(6, vocab), device=DEV) if scratch else None
+    ops().argmax(out, logits.to(DEV), buf)
     assert out.cpu().tolist() == [plain_llama.plain_greedy(r) for r in logits]
-    assert out[2].item() == 17
+    assert out[2].item() == 17 and out[5].item() == edge
 
 
 @pytest.mark.parametrize("vocab", [50, 1003, 128256])
