@@ -76,30 +76,58 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t *>(&v);
 }
 
-// Copies keys [k0, k0 + BN) of one kv head into a swizzled tile; rows at or
-// after `k_end` are zero-filled.  `threads` threads take part.
-__device__ __forceinline__ void load_kv_tile(bf16 *k_tile, bf16 *v_tile, const bf16 *__restrict__ k_cache,
-                                             const bf16 *__restrict__ v_cache, const int32_t *__restrict__ table,
-                                             int k0, int k_end, int kvh, int num_kv_heads, int page_size, int num_pages,
-                                             int tid, int threads, int *status) {
-  for (int c = tid; c < BN * CPR; c += threads) {
+// Where the rows of one kv head lie in the paged pools.
+struct KvLayout {
+  const bf16 *k_cache, *v_cache;
+  const int32_t *table;     // this request's row of the block table
+  int64_t page_stride;      // elements between pages
+  int64_t head_offset;      // elements to this kv head inside a page
+  int page_size, page_shift, num_pages;   // page_shift < 0: page_size is no power of two
+};
+
+// Copies keys [k0, k0 + ROWS) into a swizzled tile of ROWS rows; rows at or
+// after `k_end` are zero-filled.  `threads` threads (a block or one warp) share
+// the work; `tid` is the caller's index among them.
+template <int ROWS>
+__device__ __forceinline__ void load_kv_tile(bf16 *k_tile, bf16 *v_tile, const KvLayout &kv, int k0, int k_end, int tid,
+                                             int threads, int *status) {
+#pragma unroll 4
+  for (int c = tid; c < ROWS * CPR; c += threads) {
     const int row = c / CPR, chunk = c % CPR;
     const int pos = k0 + row;
     bool valid = pos < k_end;
     int64_t offset = 0;
     if (valid) {
-      const int page = table[pos / page_size];
-      if (page < 0 || page >= num_pages) {
+      int slot, in_page;
+      if (kv.page_shift >= 0) {
+        slot = pos >> kv.page_shift;
+        in_page = pos & (kv.page_size - 1);
+      } else {
+        slot = pos / kv.page_size;
+        in_page = pos - slot * kv.page_size;
+      }
+      const int page = kv.table[slot];
+      if (page < 0 || page >= kv.num_pages) {
         atomicOr(status, LE_STATUS_BAD_PAGE);
         valid = false;
       } else {
-        offset = ((static_cast<int64_t>(page) * num_kv_heads + kvh) * page_size + pos % page_size) * HD + chunk * 8;
+        offset = page * kv.page_stride + kv.head_offset + in_page * HD + chunk * 8;
       }
     }
     const int dst = swizzled_chunk(row, chunk) * 8;
-    cp_async16(k_tile + dst, k_cache + offset, valid);
-    cp_async16(v_tile + dst, v_cache + offset, valid);
+    cp_async16(k_tile + dst, kv.k_cache + offset, valid);
+    cp_async16(v_tile + dst, kv.v_cache + offset, valid);
   }
+}
+
+__device__ __forceinline__ KvLayout make_kv_layout(const bf16 *k_cache, const bf16 *v_cache, const int32_t *table, int kvh,
+                                                   int num_kv_heads, int page_size, int page_shift, int num_pages) {
+  KvLayout kv;
+  kv.k_cache = k_cache; kv.v_cache = v_cache; kv.table = table;
+  kv.page_stride = static_cast<int64_t>(num_kv_heads) * page_size * HD;
+  kv.head_offset = static_cast<int64_t>(kvh) * page_size * HD;
+  kv.page_size = page_size; kv.page_shift = page_shift; kv.num_pages = num_pages;
+  return kv;
 }
 
 // S[16 x 64] += Q[16 x HD] K^T for one warp: q fragments in registers, keys
@@ -148,7 +176,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
                          const int32_t *__restrict__ block_table, int max_blocks, const int32_t *__restrict__ cu_q,
                          const int32_t *__restrict__ ctx_before, const int32_t *__restrict__ tile_request,
                          const int32_t *__restrict__ tile_q0, int num_heads, int num_kv_heads, int page_size,
-                         int num_pages, int window, float scale, int *__restrict__ status) {
+                         int page_shift, int num_pages, int window, float scale, int *__restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   bf16 *q_tile = reinterpret_cast<bf16 *>(smem_raw);
   bf16 *k_tiles = q_tile + PF_BM * HD;
@@ -179,8 +207,8 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
   const int k_end = p_last + 1;
   const int num_tiles = (k_end - k_begin + BN - 1) / BN;
 
-  load_kv_tile(k_tiles, v_tiles, k_cache, v_cache, table, k_begin, k_end, kvh, num_kv_heads, page_size, num_pages, tid,
-               PF_THREADS, status);
+  const KvLayout kv = make_kv_layout(k_cache, v_cache, table, kvh, num_kv_heads, page_size, page_shift, num_pages);
+  load_kv_tile<BN>(k_tiles, v_tiles, kv, k_begin, k_end, tid, PF_THREADS, status);
   cp_async_commit();
 
   uint32_t qf[KSTEPS][4];
@@ -199,8 +227,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
     const int stage = it % PF_STAGES;
     if (it + 1 < num_tiles) {
       const int next = (it + 1) % PF_STAGES;
-      load_kv_tile(k_tiles + next * BN * HD, v_tiles + next * BN * HD, k_cache, v_cache, table, k0 + BN, k_end, kvh,
-                   num_kv_heads, page_size, num_pages, tid, PF_THREADS, status);
+      load_kv_tile<BN>(k_tiles + next * BN * HD, v_tiles + next * BN * HD, kv, k0 + BN, k_end, tid, PF_THREADS, status);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -289,9 +316,17 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
 }
 
 // ---------------------------------------------------------------- decode
-constexpr int DC_THREADS = 128;
-constexpr int DC_STAGES = 4;
+constexpr int DC_WARPS = 4;
+constexpr int DC_THREADS = DC_WARPS * 32;
+constexpr int DC_TILE = 32;                       // keys per warp and pipeline stage
+constexpr int DC_STAGES = 3;                      // stages per warp
+constexpr int DC_WARP_SMEM = DC_STAGES * 2 * DC_TILE * HD;   // bf16 elements per warp
 
+// One block per (split of the keys, kv head, request).  Its four warps take
+// the split's tiles of 32 keys in turn, each with a cp.async pipeline of its
+// own (no block barrier inside the loop), and keep their own running maximum,
+// sum and output; these are merged through shared memory at the end and
+// written as the split's partial result (or, with one split, as the result).
 // Scratch per (request, head, split): HD floats of unnormalised output, then
 // the maximum (in log2 units) and the sum.
 __global__ void __launch_bounds__(DC_THREADS)
@@ -300,11 +335,8 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
                         const bf16 *__restrict__ v_cache, const int32_t *__restrict__ block_table, int max_blocks,
                         const int32_t *__restrict__ cu_q, const int32_t *__restrict__ ctx_before,
                         const int32_t *__restrict__ requests, int num_heads, int num_kv_heads, int page_size,
-                        int num_pages, int window, float scale, int num_splits, int *__restrict__ status) {
+                        int page_shift, int num_pages, int window, float scale, int num_splits, int *__restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  bf16 *k_tiles = reinterpret_cast<bf16 *>(smem_raw);
-  bf16 *v_tiles = k_tiles + DC_STAGES * BN * HD;
-
   const int split = blockIdx.x;
   const int group = num_heads / num_kv_heads;
   const int row_tiles = (group + 15) / 16;
@@ -316,15 +348,22 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
   const int p = ctx_before[b];                                    // its position; keys 0 .. p
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int32_t *table = block_table + static_cast<int64_t>(b) * max_blocks;
+  const KvLayout kv = make_kv_layout(k_cache, v_cache, block_table + static_cast<int64_t>(b) * max_blocks, kvh,
+                                     num_kv_heads, page_size, page_shift, num_pages);
 
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int total = p + 1 - lo;
   int per_split = (total + num_splits - 1) / num_splits;
-  per_split = (per_split + BN - 1) / BN * BN;
+  per_split = (per_split + DC_TILE - 1) / DC_TILE * DC_TILE;
   const int k_begin = lo + split * per_split;
   const int k_end = min(p + 1, k_begin + per_split);
-  const int num_tiles = k_end > k_begin ? (k_end - k_begin + BN - 1) / BN : 0;
+  const int tiles_in_split = k_end > k_begin ? (k_end - k_begin + DC_TILE - 1) / DC_TILE : 0;
+  const int my_tiles = tiles_in_split > warp ? (tiles_in_split - warp + DC_WARPS - 1) / DC_WARPS : 0;   // tiles warp, warp+4, ...
+
+  bf16 *my_smem = reinterpret_cast<bf16 *>(smem_raw) + warp * DC_WARP_SMEM;
+  auto k_stage = [&](int s) { return my_smem + s * 2 * DC_TILE * HD; };
+  auto v_stage = [&](int s) { return my_smem + s * 2 * DC_TILE * HD + DC_TILE * HD; };
+  auto tile_start = [&](int i) { return k_begin + (warp + i * DC_WARPS) * DC_TILE; };
 
   // query fragments straight from global memory: rows are the group's heads
   uint32_t qf[KSTEPS][4];
@@ -344,39 +383,31 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
   const float sl2 = scale * LOG2E;
 
-  // prologue: fill the pipeline
 #pragma unroll
-  for (int sidx = 0; sidx < DC_STAGES - 1; ++sidx) {
-    if (sidx < num_tiles)
-      load_kv_tile(k_tiles + sidx * BN * HD, v_tiles + sidx * BN * HD, k_cache, v_cache, table, k_begin + sidx * BN, k_end,
-                   kvh, num_kv_heads, page_size, num_pages, tid, DC_THREADS, status);
+  for (int s = 0; s < DC_STAGES - 1; ++s) {
+    if (s < my_tiles) load_kv_tile<DC_TILE>(k_stage(s), v_stage(s), kv, tile_start(s), k_end, lane, 32, status);
     cp_async_commit();
   }
-  for (int it = 0; it < num_tiles; ++it) {
+  for (int it = 0; it < my_tiles; ++it) {
     cp_async_wait<DC_STAGES - 2>();
-    __syncthreads();                       // tile `it` has landed; the stage used by it - 1 is free
+    __syncwarp();                          // tile `it` has landed for every lane; stage of it - 1 is free
     const int nxt = it + DC_STAGES - 1;
-    if (nxt < num_tiles) {
-      const int st = nxt % DC_STAGES;
-      load_kv_tile(k_tiles + st * BN * HD, v_tiles + st * BN * HD, k_cache, v_cache, table, k_begin + nxt * BN, k_end, kvh,
-                   num_kv_heads, page_size, num_pages, tid, DC_THREADS, status);
-    }
+    if (nxt < my_tiles) load_kv_tile<DC_TILE>(k_stage(nxt % DC_STAGES), v_stage(nxt % DC_STAGES), kv, tile_start(nxt), k_end, lane, 32, status);
     cp_async_commit();
-    const int stage = it % DC_STAGES;
-    const bf16 *k_tile = k_tiles + stage * BN * HD, *v_tile = v_tiles + stage * BN * HD;
-    const int k0 = k_begin + it * BN + warp * 16;            // this warp's 16 keys of the tile
-    if (k0 >= k_end) continue;                               // (uniform per warp)
-    float s[2][4];
+    const bf16 *k_tile = k_stage(it % DC_STAGES), *v_tile = v_stage(it % DC_STAGES);
+    const int k0 = tile_start(it);
+    float s[DC_TILE / 8][4];
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
-    scores<2>(s, qf, k_tile, warp * 16, lane);
+    for (int nt = 0; nt < DC_TILE / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+    scores<DC_TILE / 8>(s, qf, k_tile, 0, lane);
     float tile_max[2] = {-INFINITY, -INFINITY};
+    const bool full = k0 + DC_TILE <= k_end;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
+    for (int nt = 0; nt < DC_TILE / 8; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int pos = k0 + nt * 8 + 2 * t + (e & 1);
-        s[nt][e] = pos < k_end ? s[nt][e] * sl2 : -INFINITY;
+        s[nt][e] = (full || pos < k_end) ? s[nt][e] * sl2 : -INFINITY;
         tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[nt][e]);
       }
     }
@@ -391,7 +422,7 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
       l_run[r] *= alpha[r];
     }
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
+    for (int nt = 0; nt < DC_TILE / 8; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float pr = (s[nt][e] == -INFINITY) ? 0.0f : exp2f(s[nt][e] - m_new[e >> 1]);
@@ -399,17 +430,20 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
         l_run[e >> 1] += pr;
       }
     }
-    uint32_t pf[1][4];
-    pf[0][0] = pack_bf16(s[0][0], s[0][1]);
-    pf[0][1] = pack_bf16(s[0][2], s[0][3]);
-    pf[0][2] = pack_bf16(s[1][0], s[1][1]);
-    pf[0][3] = pack_bf16(s[1][2], s[1][3]);
+    uint32_t pf[DC_TILE / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < DC_TILE / 16; ++kk) {
+      pf[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      pf[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      pf[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      pf[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    }
 #pragma unroll
     for (int nt = 0; nt < NT_O; ++nt) {
       o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0];
       o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
     }
-    weighted_values<1>(o, pf, v_tile, warp * 16, lane);
+    weighted_values<DC_TILE / 16>(o, pf, v_tile, 0, lane);
   }
   cp_async_wait<0>();
   __syncthreads();
@@ -420,9 +454,9 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
-  float *sm_o = reinterpret_cast<float *>(smem_raw);            // [4 warps][16 rows][HD]
-  float *sm_m = sm_o + 4 * 16 * HD;                             // [4][16]
-  float *sm_l = sm_m + 4 * 16;
+  float *sm_o = reinterpret_cast<float *>(smem_raw);            // [warps][16 rows][HD]
+  float *sm_m = sm_o + DC_WARPS * 16 * HD;                      // [warps][16]
+  float *sm_l = sm_m + DC_WARPS * 16;
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = g + 8 * r;
@@ -441,10 +475,10 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
     const int row = i / HD, d = i % HD;
     float m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) m = fmaxf(m, sm_m[w * 16 + row]);
+    for (int w = 0; w < DC_WARPS; ++w) m = fmaxf(m, sm_m[w * 16 + row]);
     float acc = 0.0f, l = 0.0f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < DC_WARPS; ++w) {
       const float mw = sm_m[w * 16 + row];
       const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
       acc += f * sm_o[(w * 16 + row) * HD + d];
@@ -491,6 +525,12 @@ __global__ void attention_merge_kernel(bf16 *__restrict__ out, int64_t out_strid
 
 LE_API int le_attention_mma_available() { return 1; }
 
+static int page_shift_of(int page_size) {
+  for (int s = 0; s < 30; ++s)
+    if ((1 << s) == page_size) return s;
+  return -1;
+}
+
 LE_API int le_attention_prefill_bf16(void *out, int64_t out_stride, const void *q, int64_t q_stride, const void *k_cache,
                                      const void *v_cache, const int32_t *block_table, int max_blocks, const int32_t *cu_q,
                                      const int32_t *ctx_before, const int32_t *tile_request, const int32_t *tile_q0,
@@ -508,7 +548,7 @@ LE_API int le_attention_prefill_bf16(void *out, int64_t out_stride, const void *
   attention_prefill_kernel<<<grid, PF_THREADS, smem, stream>>>(
       static_cast<bf16 *>(out), out_stride, static_cast<const bf16 *>(q), q_stride, static_cast<const bf16 *>(k_cache),
       static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before, tile_request, tile_q0, num_heads,
-      num_kv_heads, page_size, num_pages, window, scale, status);
+      num_kv_heads, page_size, page_shift_of(page_size), num_pages, window, scale, status);
   return le::launched();
 }
 
@@ -532,8 +572,8 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
   const int group = num_heads / num_kv_heads;
   const int row_tiles = (group + 15) / 16;
   if (num_kv_heads * row_tiles > 65535 || num_requests > 65535) return le::invalid("le_attention_decode_bf16: the batch is too large for one launch");
-  size_t smem = static_cast<size_t>(2 * DC_STAGES * BN) * HD * sizeof(bf16);
-  const size_t merge = static_cast<size_t>(4 * 16 * HD + 2 * 4 * 16) * sizeof(float);
+  size_t smem = static_cast<size_t>(DC_WARPS) * DC_WARP_SMEM * sizeof(bf16);
+  const size_t merge = static_cast<size_t>(DC_WARPS * 16 * HD + 2 * DC_WARPS * 16) * sizeof(float);
   if (merge > smem) smem = merge;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -545,7 +585,7 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
   attention_decode_kernel<<<grid, DC_THREADS, smem, stream>>>(
       static_cast<bf16 *>(out), out_stride, part_o, part_ml, static_cast<const bf16 *>(q), q_stride,
       static_cast<const bf16 *>(k_cache), static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before,
-      requests, num_heads, num_kv_heads, page_size, num_pages, window, scale, num_splits, status);
+      requests, num_heads, num_kv_heads, page_size, page_shift_of(page_size), num_pages, window, scale, num_splits, status);
   int rc = le::launched();
   if (rc != 0 || num_splits == 1) return rc;
   dim3 mgrid(num_heads, num_requests);
