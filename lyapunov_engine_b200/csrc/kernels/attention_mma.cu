@@ -337,6 +337,7 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
                         const int32_t *__restrict__ requests, int num_heads, int num_kv_heads, int page_size,
                         int page_shift, int num_pages, int window, float scale, int num_splits, int *__restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
+  le::wait_for_predecessor();
   const int split = blockIdx.x;
   const int group = num_heads / num_kv_heads;
   const int row_tiles = (group + 15) / 16;
@@ -447,6 +448,7 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
   }
   cp_async_wait<0>();
   __syncthreads();
+  le::let_successor_start();   // only the merge and the stores are left
 
   // merge the four warps through shared memory (the tiles are no longer needed)
 #pragma unroll
@@ -502,6 +504,8 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
 __global__ void attention_merge_kernel(bf16 *__restrict__ out, int64_t out_stride, const float *__restrict__ part_o,
                                        const float *__restrict__ part_ml, const int32_t *__restrict__ cu_q,
                                        const int32_t *__restrict__ requests, int num_heads, int num_splits) {
+  le::let_successor_start();
+  le::wait_for_predecessor();
   const int head = blockIdx.x, z = blockIdx.y;
   const int b = requests ? requests[z] : z;
   const int tok = cu_q[b];
@@ -582,16 +586,15 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
   float *part_o = scratch;
   float *part_ml = scratch ? scratch + static_cast<int64_t>(num_requests) * num_heads * num_splits * HD : nullptr;
   dim3 grid(num_splits, num_kv_heads * row_tiles, num_requests);
-  attention_decode_kernel<<<grid, DC_THREADS, smem, stream>>>(
-      static_cast<bf16 *>(out), out_stride, part_o, part_ml, static_cast<const bf16 *>(q), q_stride,
-      static_cast<const bf16 *>(k_cache), static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before,
-      requests, num_heads, num_kv_heads, page_size, page_shift_of(page_size), num_pages, window, scale, num_splits, status);
-  int rc = le::launched();
+  int rc = le::launch_chained(attention_decode_kernel, grid, dim3(DC_THREADS), smem, stream, static_cast<bf16 *>(out), out_stride,
+                              part_o, part_ml, static_cast<const bf16 *>(q), q_stride, static_cast<const bf16 *>(k_cache),
+                              static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before, requests, num_heads,
+                              num_kv_heads, page_size, page_shift_of(page_size), num_pages, window, scale, num_splits, status);
   if (rc != 0 || num_splits == 1) return rc;
   dim3 mgrid(num_heads, num_requests);
-  attention_merge_kernel<<<mgrid, HD < 32 ? 32 : (HD > 128 ? 128 : HD), 0, stream>>>(
-      static_cast<bf16 *>(out), out_stride, part_o, part_ml, cu_q, requests, num_heads, num_splits);
-  return le::launched();
+  return le::launch_chained(attention_merge_kernel, mgrid, dim3(HD < 32 ? 32 : (HD > 128 ? 128 : HD)), 0, stream,
+                            static_cast<bf16 *>(out), out_stride, static_cast<const float *>(part_o),
+                            static_cast<const float *>(part_ml), cu_q, requests, num_heads, num_splits);
 }
 
 // ---------------------------------------------------------------- no allocation

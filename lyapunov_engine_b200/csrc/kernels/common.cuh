@@ -16,6 +16,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 
 #define LE_API extern "C" __attribute__((visibility("default")))
 
@@ -49,6 +50,44 @@ inline int launched() {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) snprintf(error_buffer(), 512, "CUDA: %s", cudaGetErrorString(e));
   return static_cast<int>(e);
+}
+
+// Programmatic dependent launch: a kernel launched with launch_chained() may
+// start while its predecessor in the stream still runs.  It must call
+// wait_for_predecessor() before it reads anything the predecessor wrote and
+// before it writes anything the predecessor may still read; what it does
+// before that (address arithmetic, fetching weights) overlaps the predecessor's
+// tail.  let_successor_start() lets the next kernel in the stream begin its own
+// preamble.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void let_successor_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool chaining_enabled() {
+  static const bool on = [] {
+    const char *env = getenv("LYAPUNOV_PDL");
+    return env == nullptr || env[0] != '0';
+  }();
+  return on;
+}
+
+template <typename... KernelArgs, typename... Args>
+inline int launch_chained(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = chaining_enabled() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+  if (e != cudaSuccess) {
+    snprintf(error_buffer(), 512, "CUDA: %s", cudaGetErrorString(e));
+    return static_cast<int>(e);
+  }
+  return launched();
 }
 
 template <typename T> __device__ __forceinline__ float to_f32(T x);

@@ -14,6 +14,8 @@ namespace {
 template <typename T>
 __global__ void embed_kernel(float *__restrict__ out, const T *__restrict__ table, const int32_t *__restrict__ ids,
                              int hidden, int vocab, int *__restrict__ status) {
+  le::let_successor_start();
+  le::wait_for_predecessor();
   const int t = blockIdx.x;
   const int id = ids[t];
   float *dst = out + static_cast<int64_t>(t) * hidden;
@@ -72,8 +74,8 @@ LE_API int le_embed(float *out, const void *table, int table_dtype, const int32_
   if (num_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   LE_DISPATCH_DTYPE(table_dtype, T,
-                    embed_kernel<T><<<num_tokens, threads, 0, stream>>>(out, static_cast<const T *>(table), ids, hidden, vocab, status));
-  return le::launched();
+                    return le::launch_chained(embed_kernel<T>, dim3(num_tokens), dim3(threads), 0, stream, out,
+                                              static_cast<const T *>(table), ids, hidden, vocab, status));
 }
 
 LE_API int le_swiglu(void *out, const void *gate_up, int dtype, int num_tokens, int inter, cudaStream_t stream) {

@@ -1,7 +1,11 @@
 // RMSNorm over the 32-bit residual stream, with the residual addition fused.
 //
-//   resid[r] += delta[r]                      (when delta is given)
+//   resid[r] += delta[0][r] + delta[1][r] + ...   (when delta is given)
 //   out[r]    = resid[r] * rsqrt(mean(resid[r]^2) + eps) * weight
+//
+// delta is the output of the sub-layer before the norm: one tensor in the
+// activations' type, or the float32 partial sums of a split-K product, which
+// are added here in their fixed order.
 //
 // Sum, mean, rsqrt and the product are 32-bit; the output is rounded once.
 // With `rows` given, only those rows are normed, into consecutive rows of
@@ -16,8 +20,11 @@ namespace {
 
 template <typename TO, typename TD, int VEC>
 __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, const TD *__restrict__ delta,
-                               const float *__restrict__ weight, const int32_t *__restrict__ rows, float eps, int hidden) {
+                               int num_partials, int64_t partial_stride, const float *__restrict__ weight,
+                               const int32_t *__restrict__ rows, float eps, int hidden) {
   __shared__ float scratch[33];
+  le::let_successor_start();
+  le::wait_for_predecessor();
   const int64_t src_row = rows ? rows[blockIdx.x] : blockIdx.x;
   float *x = resid + src_row * hidden;
   const TD *d = delta ? delta + src_row * hidden : nullptr;
@@ -29,7 +36,8 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
       float val = x[i + v];
-      if (d) val += le::to_f32(d[i + v]);
+      if (d)
+        for (int p = 0; p < num_partials; ++p) val += le::to_f32(d[p * partial_stride + i + v]);
       if (write_back) x[i + v] = val;
       ss += val * val;
     }
@@ -40,32 +48,40 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
       float val = x[i + v];
-      if (d && !write_back) val += le::to_f32(d[i + v]);
+      if (d && !write_back)
+        for (int p = 0; p < num_partials; ++p) val += le::to_f32(d[p * partial_stride + i + v]);
       o[i + v] = le::from_f32<TO>(val * inv * weight[i + v]);
     }
   }
 }
 
 template <typename TO, typename TD>
-int launch(void *out, float *resid, const void *delta, const float *weight, const int32_t *rows, float eps,
-           int num_rows, int hidden, cudaStream_t stream) {
+int launch(void *out, float *resid, const void *delta, int num_partials, int64_t partial_stride, const float *weight,
+           const int32_t *rows, float eps, int num_rows, int hidden, cudaStream_t stream) {
   int threads = 32;
   while (threads < 512 && threads * 8 < hidden) threads *= 2;
   if (hidden % 4 == 0)
-    rmsnorm_kernel<TO, TD, 4><<<num_rows, threads, 0, stream>>>(static_cast<TO *>(out), resid, static_cast<const TD *>(delta), weight, rows, eps, hidden);
-  else
-    rmsnorm_kernel<TO, TD, 1><<<num_rows, threads, 0, stream>>>(static_cast<TO *>(out), resid, static_cast<const TD *>(delta), weight, rows, eps, hidden);
-  return le::launched();
+    return le::launch_chained(rmsnorm_kernel<TO, TD, 4>, dim3(num_rows), dim3(threads), 0, stream, static_cast<TO *>(out), resid,
+                              static_cast<const TD *>(delta), num_partials, partial_stride, weight, rows, eps, hidden);
+  return le::launch_chained(rmsnorm_kernel<TO, TD, 1>, dim3(num_rows), dim3(threads), 0, stream, static_cast<TO *>(out), resid,
+                            static_cast<const TD *>(delta), num_partials, partial_stride, weight, rows, eps, hidden);
 }
 
 }  // namespace
 
-// `out_dtype` is the type of `out` and of `delta` (the activations' type).
-LE_API int le_rmsnorm(void *out, int out_dtype, float *resid, const void *delta, const float *weight,
-                      const int32_t *rows, float eps, int num_rows, int hidden, cudaStream_t stream) {
+// `out_dtype` is the type of `out`; `delta_dtype` that of `delta`, which holds
+// `num_partials` tensors of the residual stream's shape, `partial_stride`
+// elements apart.
+LE_API int le_rmsnorm(void *out, int out_dtype, float *resid, const void *delta, int delta_dtype, int num_partials,
+                      int64_t partial_stride, const float *weight, const int32_t *rows, float eps, int num_rows, int hidden,
+                      cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (hidden <= 0) return le::invalid("le_rmsnorm: hidden must be positive");
-  if (out_dtype == LE_F32) return launch<float, float>(out, resid, delta, weight, rows, eps, num_rows, hidden, stream);
-  if (out_dtype == LE_BF16) return launch<__nv_bfloat16, __nv_bfloat16>(out, resid, delta, weight, rows, eps, num_rows, hidden, stream);
-  return le::invalid("le_rmsnorm: unknown dtype code %d", out_dtype);
+  if (delta != nullptr && num_partials < 1) return le::invalid("le_rmsnorm: num_partials must be at least 1");
+#define LE_GO(TO, TD) return launch<TO, TD>(out, resid, delta, num_partials, partial_stride, weight, rows, eps, num_rows, hidden, stream)
+  if (out_dtype == LE_F32 && (delta == nullptr || delta_dtype == LE_F32)) LE_GO(float, float);
+  if (out_dtype == LE_BF16 && (delta == nullptr || delta_dtype == LE_BF16)) LE_GO(__nv_bfloat16, __nv_bfloat16);
+  if (out_dtype == LE_BF16 && delta_dtype == LE_F32) LE_GO(__nv_bfloat16, float);
+#undef LE_GO
+  return le::invalid("le_rmsnorm: unsupported types: out %d, delta %d", out_dtype, delta_dtype);
 }

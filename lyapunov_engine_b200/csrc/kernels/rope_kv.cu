@@ -81,6 +81,8 @@ rope_kv_vec_kernel(T *__restrict__ qkv, T *__restrict__ k_cache, T *__restrict__
                    int max_blocks, int num_heads, int num_kv_heads, int head_dim, int rot, int max_pos, int page_size,
                    int num_pages, int write_kv, int *__restrict__ status) {
   constexpr int VEC = Vec16<T>::N;
+  le::let_successor_start();
+  le::wait_for_predecessor();
   const int t = blockIdx.x;
   const int pos = positions[t];
   if (pos < 0 || pos >= max_pos) {
@@ -146,11 +148,10 @@ LE_API int le_rope_kv_write(void *qkv, int dtype, void *k_cache, void *v_cache, 
   const int vec = dtype == LE_BF16 ? 8 : 4;
   if (head_dim % vec == 0 && (rot / 2) % vec == 0) {
     LE_DISPATCH_DTYPE(dtype, T,
-                      rope_kv_vec_kernel<T><<<num_tokens, 256, 0, stream>>>(
-                          static_cast<T *>(qkv), static_cast<T *>(k_cache), static_cast<T *>(v_cache), cos_sin, positions,
-                          request_of_token, block_table, max_blocks, num_heads, num_kv_heads, head_dim, rot, max_pos,
-                          page_size, num_pages, write_kv, status));
-    return le::launched();
+                      return le::launch_chained(rope_kv_vec_kernel<T>, dim3(num_tokens), dim3(256), 0, stream,
+                                                static_cast<T *>(qkv), static_cast<T *>(k_cache), static_cast<T *>(v_cache),
+                                                cos_sin, positions, request_of_token, block_table, max_blocks, num_heads,
+                                                num_kv_heads, head_dim, rot, max_pos, page_size, num_pages, write_kv, status));
   }
   dim3 grid(num_tokens, num_heads + 2 * num_kv_heads);
   int threads = 32;

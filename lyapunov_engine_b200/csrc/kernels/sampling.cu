@@ -102,6 +102,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(float *__restrict__
                                                              int chunks) {
   __shared__ float fs[33];
   __shared__ int is[33];
+  le::let_successor_start();
+  le::wait_for_predecessor();
   const int row = blockIdx.y, chunk = blockIdx.x;
   const int begin = chunk * ARGMAX_CHUNK;
   const int n = min(ARGMAX_CHUNK, vocab - begin);
@@ -114,6 +116,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(float *__restrict__
 
 __global__ void argmax_final_kernel(int32_t *__restrict__ out, const float *__restrict__ part_val,
                                     const int32_t *__restrict__ part_idx, int chunks) {
+  le::let_successor_start();
+  le::wait_for_predecessor();
   const int row = blockIdx.x;
   float best = -INFINITY;
   int idx = 0x7fffffff;
@@ -254,11 +258,11 @@ LE_API int le_argmax(int32_t *out, const float *logits, int num_rows, int vocab,
   if (num_rows > 65535) return le::invalid("le_argmax: too many rows for one launch");
   float *part_val = scratch;
   int32_t *part_idx = reinterpret_cast<int32_t *>(scratch + static_cast<int64_t>(num_rows) * chunks);
-  argmax_partial_kernel<<<dim3(chunks, num_rows), 256, 0, stream>>>(part_val, part_idx, logits, vocab, stride, chunks);
-  int rc = le::launched();
+  int rc = le::launch_chained(argmax_partial_kernel, dim3(chunks, num_rows), dim3(256), 0, stream, part_val, part_idx, logits,
+                              vocab, stride, chunks);
   if (rc != 0) return rc;
-  argmax_final_kernel<<<num_rows, 32, 0, stream>>>(out, part_val, part_idx, chunks);
-  return le::launched();
+  return le::launch_chained(argmax_final_kernel, dim3(num_rows), dim3(32), 0, stream, out, static_cast<const float *>(part_val),
+                            static_cast<const int32_t *>(part_idx), chunks);
 }
 
 // seeds: [rows, 3] = seed low word, seed high word, counter.  `uniforms`

@@ -128,6 +128,7 @@ class LLMEngine:
         self.scheduler = self.host.ContinuousScheduler(sched, self.block_manager)
         self.req_counter = 0
         self.active_sequences: dict[int, tuple] = {}
+        self._prompts: dict[int, list] = {}
         self._tokens_host = torch.empty(config.max_num_seqs + 1, dtype=torch.int32, pin_memory=True)
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -162,9 +163,11 @@ class LLMEngine:
         c = self.host.SamplingParams()
         c.temperature, c.top_p, c.top_k = sampling.temperature, sampling.top_p, sampling.top_k
         c.max_tokens, c.ignore_eos, c.seed = sampling.max_tokens, sampling.ignore_eos, int(sampling.seed) & (2**64 - 1)
-        seq = self.host.Sequence(seq_id, [int(t) for t in prompt_tokens], c)
+        prompt_tokens = [int(t) for t in prompt_tokens]
+        seq = self.host.Sequence(seq_id, prompt_tokens, c)
         self.scheduler.add_sequence(seq)
         self.active_sequences[seq_id] = (seq, sampling, request_id)
+        self._prompts[seq_id] = prompt_tokens     # kept here so that outputs need not copy it out of C++ every step
         return request_id
 
     def abort_request(self, request_id) -> None:
@@ -172,6 +175,7 @@ class LLMEngine:
             if rid == request_id:
                 self.scheduler.abort_sequence(seq_id)
                 del self.active_sequences[seq_id]
+                self._prompts.pop(seq_id, None)
 
     def has_unfinished_requests(self) -> bool:
         return self.scheduler.has_unfinished_sequences()
@@ -214,10 +218,14 @@ class LLMEngine:
         seq_id = seq.get_seq_id()
         _, _, request_id = self.active_sequences.get(seq_id, (None, None, seq_id))
         finished = seq.is_finished()
-        o = RequestOutput(request_id, seq.get_prompt_tokens(), seq.get_output_tokens(), finished,
+        prompt = self._prompts.get(seq_id)
+        if prompt is None:
+            prompt = seq.get_prompt_tokens()
+        o = RequestOutput(request_id, prompt, seq.get_output_tokens(), finished,
                           seq.finish_reason() if finished else None, seq.get_error() or None)
         if finished:
             self.active_sequences.pop(seq_id, None)
+            self._prompts.pop(seq_id, None)
         return o
 
     # ---- convenience

@@ -58,7 +58,10 @@ _CORE_SIGNATURES = {
     "le_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "le_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "le_convert": [c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p],
-    "le_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p],
+    "le_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_float, c_int,
+                   c_int, c_void_p],
+    "le_gemm_skinny_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
+                            c_int64, c_int, c_void_p],
     "le_rope_kv_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "le_gemm_simt": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
@@ -176,20 +179,30 @@ def convert(out: torch.Tensor, src: torch.Tensor) -> None:
 
 def rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, rows=None) -> None:
     """resid += delta (when given and ``rows`` is None); out = rmsnorm(resid) * weight.
-    With ``rows`` (int32 indices) only those rows are normed, into out[0..len(rows))."""
+    ``delta`` has the residual stream's shape [T, H] in the activations' type,
+    or is float32 [S, T, H]: the partial sums of a split-K product, added in
+    order.  With ``rows`` (int32 indices) only those rows are normed, into
+    out[0..len(rows)), and ``resid`` is left as it is."""
     _need_cuda(out, resid, delta, weight, rows)
     H = resid.shape[1]
     n = out.shape[0]
     assert resid.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == H
     assert out.shape[1] == H and out.is_contiguous() and resid.is_contiguous()
+    parts, stride, dcode = 1, 0, dtype_code(out.dtype)
     if delta is not None:
-        assert delta.dtype == out.dtype and delta.shape == resid.shape and delta.is_contiguous()
+        assert delta.is_contiguous() and tuple(delta.shape[-2:]) == tuple(resid.shape)
+        if delta.dim() == 3:
+            assert delta.dtype == torch.float32
+            parts, stride = delta.shape[0], delta.stride(0)
+        else:
+            assert delta.dtype in (out.dtype, torch.float32)
+        dcode = dtype_code(delta.dtype)
     if rows is not None:
         assert rows.dtype == torch.int32 and rows.numel() >= n
     else:
         assert n == resid.shape[0]
-    _check(core().le_rmsnorm(_ptr(out), dtype_code(out.dtype), _ptr(resid), _ptr(delta), _ptr(weight), _ptr(rows),
-                             float(eps), n, H, _stream()), "le_rmsnorm")
+    _check(core().le_rmsnorm(_ptr(out), dtype_code(out.dtype), _ptr(resid), _ptr(delta), dcode, parts, stride,
+                             _ptr(weight), _ptr(rows), float(eps), n, H, _stream()), "le_rmsnorm")
 
 
 def rope_kv_write(qkv, k_cache, v_cache, cos_sin, positions, request_of_token, block_table, num_heads, num_kv_heads,
@@ -224,14 +237,79 @@ def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
                                a.stride(0), w.stride(0), out.stride(0), _stream()), "le_gemm_simt")
 
 
+SKINNY_ROWS = 16          # up to this many rows a product streams weights through the package's own kernel
+SKINNY_BLOCKS = 2 * 148   # blocks worth having in flight on a B200
+
+
+def skinny_applies(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and a.shape[0] <= SKINNY_ROWS and a.shape[1] % 8 == 0 and a.stride(1) == 1
+            and w.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+
+
+def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, splits: int = 1, gated: bool = False) -> None:
+    """The package's weight-streaming product for at most 64 rows (bfloat16
+    inputs).  ``splits`` > 1: ``out`` is float32 [splits, M, N] partial sums.
+    ``gated``: ``w`` is [2 I, K] (gate rows, then up rows), out = silu(gate) * up."""
+    _need_cuda(out, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    if splits > 1:
+        assert out.dtype == torch.float32 and out.shape == (splits, M, N) and out.is_contiguous()
+        ldo, stride = N, out.stride(0)
+    else:
+        assert out.shape[-2:] == (M, N // 2 if gated else N) and out.stride(-1) == 1
+        ldo, stride = out.stride(-2), 0
+    _check(core().le_gemm_skinny_bf16(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0),
+                                      w.stride(0), ldo, splits, stride, 1 if gated else 0, _stream()),
+           "le_gemm_skinny_bf16")
+
+
+def split_k_for(n_out: int, k: int) -> int:
+    """How many slices of K give a product enough blocks to fill the GPU."""
+    blocks = (n_out + 15) // 16
+    return max(1, min((SKINNY_BLOCKS + blocks - 1) // blocks, k // 512, 16))
+
+
+def linear_for_residual(a: torch.Tensor, w: torch.Tensor, workspace, key: str):
+    """a @ w^T for a product whose only use is to be added to the residual
+    stream: returns either the tensor [M, N] in the activations' type or, for
+    few rows, float32 partial sums [S, M, N] that the next norm adds up."""
+    M, N = a.shape[0], w.shape[0]
+    if skinny_applies(a, w):
+        splits = split_k_for(N, a.shape[1])
+        out = workspace.get(key + "_partials", (splits, M, N), torch.float32)
+        if splits == 1:
+            gemm_skinny(out[0], a, w)
+        else:
+            gemm_skinny(out, a, w, splits=splits)
+        return out
+    out = workspace.get(key, (M, N), a.dtype)
+    linear(out, a, w)
+    return out
+
+
+def gated_linear(out: torch.Tensor, a: torch.Tensor, w_gate_up: torch.Tensor, workspace) -> None:
+    """out = silu(a @ w_gate^T) * (a @ w_up^T), w_gate_up = [gate rows; up rows]."""
+    if skinny_applies(a, w_gate_up):
+        gemm_skinny(out, a, w_gate_up, gated=True)
+        return
+    gu = workspace.get("gate_up", (a.shape[0], w_gate_up.shape[0]), a.dtype)
+    linear(gu, a, w_gate_up)
+    swiglu(out, gu)
+
+
 def linear(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
-    """out = a @ w^T.  float32: the package's FP32 kernel.  bfloat16: the
-    library product (cuBLAS), 32-bit accumulation; when ``out`` is float32 the
-    product is written in 32 bits without an intermediate rounding."""
+    """out = a @ w^T.  float32: the package's FP32 kernel.  bfloat16 with at
+    most 64 rows: the package's weight-streaming kernel.  bfloat16 with more
+    rows: the library product (cuBLAS), 32-bit accumulation; when ``out`` is
+    float32 the product is written in 32 bits without an intermediate rounding."""
     if a.dtype == torch.float32:
         gemm_simt(out, a, w)
         return
     _need_cuda(out, a, w)
+    if skinny_applies(a, w):
+        gemm_skinny(out, a, w)
+        return
     if out.dtype == torch.bfloat16:
         counters["library_products"] += 1
         torch.mm(a, w.t(), out=out)

@@ -66,6 +66,4 @@ class AttentionMixer(Mixer):
         self.position.encode_and_store(qkv, (nh, nkv, hd), ctx, cache.kv, cache.write)
         attn = ws.get("attn", (T, nh * hd), rt.dtype)
         attention_kernels.run(attn, qkv, ctx, cache.kv, nh, nkv, hd, self.window, self.scale)
-        y = ws.get("mixer_out", (T, self.hidden_size), rt.dtype)
-        ops.linear(y, attn, self.w_o)
-        return y
+        return ops.linear_for_residual(attn, self.w_o, ws, "mixer_out")

@@ -18,7 +18,7 @@ GENERIC_TILE = 16
 PREFILL_TILE = 64
 DECODE_KEYS_PER_SPLIT = 256     # a split is worth its launch from about four tiles of keys
 DECODE_MAX_SPLITS = 64
-TARGET_BLOCKS = 3 * 148         # blocks of the decode kernel that are resident at once on a B200
+RESIDENT_BLOCKS = 2 * 148       # blocks of the decode kernel that are resident at once on a B200
 
 
 def tile_sizes() -> list[int]:
@@ -32,11 +32,21 @@ def prepare(head_dim: int) -> None:
 
 
 def decode_splits(num_requests: int, num_heads: int, num_kv_heads: int, context_bound: int) -> int:
+    """The fewest splits whose blocks fill the GPU in whole waves (a last wave
+    that is mostly empty costs as much as a full one)."""
     group = num_heads // num_kv_heads
     blocks = num_requests * num_kv_heads * ((group + 15) // 16)
-    by_blocks = (TARGET_BLOCKS + blocks - 1) // blocks
     by_keys = max(1, (context_bound + DECODE_KEYS_PER_SPLIT - 1) // DECODE_KEYS_PER_SPLIT)
-    return max(1, min(by_blocks, by_keys, DECODE_MAX_SPLITS))
+    limit = max(1, min(by_keys, DECODE_MAX_SPLITS))
+    best, best_fill = 1, 0.0
+    for splits in range(1, limit + 1):
+        waves = blocks * splits / RESIDENT_BLOCKS
+        fill = waves / -(-waves // 1)        # waves / ceil(waves)
+        if fill >= 0.85:
+            return splits
+        if fill > best_fill + 1e-9:
+            best, best_fill = splits, fill
+    return best
 
 
 def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, window, scale) -> None:

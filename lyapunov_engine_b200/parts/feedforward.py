@@ -36,10 +36,6 @@ class GatedFeedForward(FeedForward):
         rt = self.runtime
         T = x.shape[0]
         ws = ctx.workspace
-        gu = ws.get("gate_up", (T, 2 * self.intermediate_size), rt.dtype)
-        ops.linear(gu, x, self.w_gate_up)
         act = ws.get("ffn_act", (T, self.intermediate_size), rt.dtype)
-        ops.swiglu(act, gu)
-        y = ws.get("ffn_out", (T, self.hidden_size), rt.dtype)
-        ops.linear(y, act, self.w_down)
-        return y
+        ops.gated_linear(act, x, self.w_gate_up, ws)
+        return ops.linear_for_residual(act, self.w_down, ws, "ffn_out")

@@ -145,8 +145,8 @@ def test_tensor_core_kernels(case):
 
 def test_decode_splits_choice():
     from lyapunov_engine_b200.parts.attention_kernels import decode_splits
-    assert decode_splits(64, 32, 8, 4096) == 1
-    assert decode_splits(8, 32, 8, 4096) == 7
-    assert decode_splits(1, 32, 8, 4096) == 16
+    assert decode_splits(64, 32, 8, 4096) == 1      # 512 blocks: 1.73 waves of 296
+    assert decode_splits(8, 32, 8, 4096) == 4       # 256 blocks: one wave, 86 % full
+    assert decode_splits(1, 32, 8, 4096) == 16      # as many as the keys allow
     assert decode_splits(1, 32, 8, 100) == 1
-    assert decode_splits(1, 32, 8, 131072) == 56
+    assert decode_splits(1, 32, 8, 131072) == 32    # 256 blocks

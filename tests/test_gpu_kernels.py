@@ -225,3 +225,46 @@ def test_sampling_frequencies_and_batch_independence():
     for i in (0, 17, 3999):
         o.sample(one, rows[i:i + 1], *(a[i:i + 1] for a in args), seeds[i:i + 1].to(DEV))
         assert one.item() == out[i].item()
+
+
+@pytest.mark.parametrize("M", [1, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("N,K", [(515, 96), (64, 2048), (1000, 136), (48, 328), (2048, 1024)])
+def test_skinny_product(M, N, K):
+    """The weight-streaming product for few rows: plain, split over K, gated."""
+    o = ops()
+    g = torch.Generator().manual_seed(M * N + K)
+    a = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.5).bfloat16()
+    want = (a.double() @ w.double().t()).float()
+    for dtype, tol in ((torch.float32, dict(atol=2e-3, rtol=1e-4)), (torch.bfloat16, dict(atol=0.1, rtol=1e-2))):
+        out = torch.full((M, N), 9.0, dtype=dtype, device=DEV)
+        o.gemm_skinny(out, a.to(DEV), w.to(DEV))
+        torch.testing.assert_close(out.float().cpu(), want, **tol)
+    for splits in (2, 5):
+        part = torch.full((splits, M, N), 9.0, device=DEV)
+        o.gemm_skinny(part, a.to(DEV), w.to(DEV), splits=splits)
+        torch.testing.assert_close(part.sum(0).cpu(), want, atol=2e-3, rtol=1e-4)
+    if N % 2 == 0:
+        act = torch.full((M, N // 2), 9.0, dtype=torch.bfloat16, device=DEV)
+        o.gemm_skinny(act, a.to(DEV), w.to(DEV), gated=True)
+        torch.testing.assert_close(act.float().cpu(), plain_llama.plain_swiglu(want[:, :N // 2], want[:, N // 2:]),
+                                   atol=0.1, rtol=1e-2)
+
+
+def test_norm_adds_partial_sums_in_order():
+    o = ops()
+    g = torch.Generator().manual_seed(5)
+    resid = torch.randn(7, 264, generator=g)
+    parts = torch.randn(3, 7, 264, generator=g)
+    w = 1 + 0.1 * torch.randn(264, generator=g)
+    r = resid.to(DEV)
+    out = torch.empty(7, 264, dtype=torch.bfloat16, device=DEV)
+    o.rmsnorm(out, r, parts.to(DEV), w.to(DEV), 1e-5)
+    summed = ((resid + parts[0]) + parts[1]) + parts[2]
+    assert torch.equal(r.cpu(), summed)
+    torch.testing.assert_close(out.float().cpu(), plain_llama.plain_rmsnorm(summed, w, 1e-5), atol=2e-2, rtol=2e-2)
+    rows = torch.tensor([6, 2], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, 264, dtype=torch.bfloat16, device=DEV)
+    o.rmsnorm(out2, r, parts.to(DEV), w.to(DEV), 1e-5, rows=rows)
+    want = plain_llama.plain_rmsnorm(summed + parts.sum(0), w, 1e-5)[[6, 2]]
+    torch.testing.assert_close(out2.float().cpu(), want, atol=2e-2, rtol=2e-2)
