@@ -44,7 +44,7 @@ CXX_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-Wall", "-Wextra", "-fvisibility=hid
 
 HOST_SOURCES = ["host/block_manager.cpp", "host/scheduler.cpp", "host/step_pack.cpp", "host/bindings.cpp"]
 CORE_KERNEL_SOURCES = ["kernels/elementwise.cu", "kernels/norm.cu", "kernels/rope_kv.cu",
-                       "kernels/gemm_f32.cu", "kernels/sampling.cu", "kernels/gemm_skinny.cu"
+                       "kernels/gemm_f32.cu", "kernels/sampling.cu", "kernels/gemm_skinny.cu", "kernels/gemm_tc.cu"
                        ]
 ATTENTION_SOURCES = ["kernels/attention_generic.cu", "kernels/attention_mma.cu"]
 

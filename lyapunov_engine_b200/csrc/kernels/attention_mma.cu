@@ -1,6 +1,6 @@
 // Tensor-core attention over the paged cache for bfloat16, head sizes 16..128:
 //   * le_attention_prefill_bf16: portions of prompts (any number of query
-//     tokens per request), FlashAttention-2 style: a block owns 64 query
+//     tokens per request), FlashAttention-2 style: a block owns 128 query
 //     tokens of one head, walks the keys in tiles of 64 with a running maximum
 //     and sum, S = Q K^T and O += P V on mma.sync m16n8k16 with 32-bit
 //     accumulators, softmax in 32 bits (exp2 with the scale folded in);
@@ -166,8 +166,9 @@ __device__ __forceinline__ void weighted_values(float (&o)[NT_O][4], const uint3
 }
 
 // ---------------------------------------------------------------- prefill
-constexpr int PF_BM = 64;
-constexpr int PF_THREADS = 128;
+constexpr int PF_BM = 128;          // query tokens per block
+constexpr int PF_WARPS = PF_BM / 16;
+constexpr int PF_THREADS = PF_WARPS * 32;
 constexpr int PF_STAGES = 2;
 
 __global__ void __launch_bounds__(PF_THREADS)
@@ -195,7 +196,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
   const int g = lane >> 2, t = lane & 3;
   const int32_t *table = block_table + static_cast<int64_t>(b) * max_blocks;
 
-  // queries of this tile (rows beyond the request's tokens are zero)
+  // queries of this tile (rows beyond the request's tokens are zero and are never stored)
   for (int c = tid; c < PF_BM * CPR; c += PF_THREADS) {
     const int row = c / CPR, chunk = c % CPR;
     const bool valid = row < rows;
@@ -215,12 +216,16 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
   float o[NT_O][4];
 #pragma unroll
   for (int nt = 0; nt < NT_O; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};   // rows g and g + 8 of this warp
+  // running maximum in units of the raw score, running sum; rows g and g + 8 of this warp
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
   const float sl2 = scale * LOG2E;
   const int row_lo = warp * 16 + g, row_hi = row_lo + 8;
   const int p_row[2] = {p0 + row_lo, p0 + row_hi};
   const int lo_row[2] = {window > 0 ? max(0, p_row[0] - window + 1) : 0, window > 0 ? max(0, p_row[1] - window + 1) : 0};
-  const bool row_ok[2] = {row_lo < rows, row_hi < rows};
+  // what this warp's 16 rows can see at all
+  const int warp_p_first = p0 + warp * 16, warp_p_last = warp_p_first + 15;
+  const int warp_lo_first = window > 0 ? max(0, warp_p_first - window + 1) : 0;
+  const int warp_lo_last = window > 0 ? max(0, warp_p_last - window + 1) : 0;
 
   for (int it = 0; it < num_tiles; ++it) {
     const int k0 = k_begin + it * BN;
@@ -242,59 +247,68 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
         ldmatrix_x4(qf[ks], q_tile + swizzled_chunk(row, ks * 2 + (j >> 1)) * 8);
       }
     }
-    // a warp whose rows all lie before this tile's first key has nothing to do
-    const bf16 *k_tile = k_tiles + stage * BN * HD, *v_tile = v_tiles + stage * BN * HD;
-    float s[BN / 8][4];
+    // a warp skips tiles none of its rows can see (all keys after its last row, or all before its window)
+    const bool visible = k0 <= warp_p_last && k0 + BN - 1 >= warp_lo_first;
+    if (visible) {
+      const bf16 *k_tile = k_tiles + stage * BN * HD, *v_tile = v_tiles + stage * BN * HD;
+      float s[BN / 8][4];
 #pragma unroll
-    for (int nt = 0; nt < BN / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
-    scores<BN / 8>(s, qf, k_tile, 0, lane);
-
-    float tile_max[2] = {-INFINITY, -INFINITY};
+      for (int nt = 0; nt < BN / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+      scores<BN / 8>(s, qf, k_tile, 0, lane);
+      // only tiles that cross the causal diagonal or the window's edge need the mask
+      const bool needs_mask = k0 + BN - 1 > warp_p_first || k0 < warp_lo_last;
+      if (needs_mask) {
 #pragma unroll
-    for (int nt = 0; nt < BN / 8; ++nt) {
+        for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int r = e >> 1;
-        const int pos = k0 + nt * 8 + 2 * t + (e & 1);
-        const bool seen = row_ok[r] && pos <= p_row[r] && pos >= lo_row[r];
-        s[nt][e] = seen ? s[nt][e] * sl2 : -INFINITY;
-        tile_max[r] = fmaxf(tile_max[r], s[nt][e]);
+          for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int pos = k0 + nt * 8 + 2 * t + (e & 1);
+            if (pos > p_row[r] || pos < lo_row[r]) s[nt][e] = -INFINITY;
+          }
+        }
       }
-    }
-    float alpha[2], m_new[2];
+      float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
-      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-      m_new[r] = fmaxf(m_run[r], tile_max[r]);
-      alpha[r] = (m_new[r] == -INFINITY) ? 1.0f : exp2f(m_run[r] - m_new[r]);
-      m_run[r] = m_new[r];
-      l_run[r] *= alpha[r];
-    }
-    uint32_t pf[BN / 16][4];
-#pragma unroll
-    for (int nt = 0; nt < BN / 8; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int r = e >> 1;
-        const float p = (s[nt][e] == -INFINITY) ? 0.0f : exp2f(s[nt][e] - m_new[r]);
-        s[nt][e] = p;
-        l_run[r] += p;
+      for (int nt = 0; nt < BN / 8; ++nt) {
+        tile_max[0] = fmaxf(tile_max[0], fmaxf(s[nt][0], s[nt][1]));
+        tile_max[1] = fmaxf(tile_max[1], fmaxf(s[nt][2], s[nt][3]));
       }
-    }
+      float alpha[2], neg_m[2];
 #pragma unroll
-    for (int kk = 0; kk < BN / 16; ++kk) {
-      pf[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-      pf[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-      pf[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      pf[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-    }
+      for (int r = 0; r < 2; ++r) {
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+        const float m_new = fmaxf(m_run[r], tile_max[r]);
+        alpha[r] = (m_new == -INFINITY) ? 1.0f : exp2f((m_run[r] - m_new) * sl2);
+        neg_m[r] = (m_new == -INFINITY) ? 0.0f : -m_new * sl2;
+        m_run[r] = m_new;
+        l_run[r] *= alpha[r];
+      }
 #pragma unroll
-    for (int nt = 0; nt < NT_O; ++nt) {
-      o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0];
-      o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
+      for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p = exp2f(fmaf(s[nt][e], sl2, neg_m[e >> 1]));   // exp2(-inf) = 0 for masked keys
+          s[nt][e] = p;
+          l_run[e >> 1] += p;
+        }
+      }
+      uint32_t pf[BN / 16][4];
+#pragma unroll
+      for (int kk = 0; kk < BN / 16; ++kk) {
+        pf[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        pf[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        pf[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pf[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < NT_O; ++nt) {
+        o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0];
+        o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
+      }
+      weighted_values<BN / 16>(o, pf, v_tile, 0, lane);
     }
-    weighted_values<BN / 16>(o, pf, v_tile, 0, lane);
     __syncthreads();   // everyone is done with this stage before it is filled again
   }
 
@@ -306,7 +320,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
   const float inv[2] = {l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f};
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    if (!row_ok[r]) continue;
+    if ((r ? row_hi : row_lo) >= rows) continue;
     bf16 *dst = out + (tok0 + (r ? row_hi : row_lo)) * out_stride + head * HD;
 #pragma unroll
     for (int nt = 0; nt < NT_O; ++nt) {

@@ -1,0 +1,358 @@
+// out[M, N] = x[M, K] W[N, K]^T in bfloat16 on the fifth-generation tensor
+// cores: the matrix products of prompt portions (many rows).
+//
+// One block computes a 128 x BN tile of the output (BN = 128 or 256).  Warp 0
+// is the producer: one thread issues TMA tile loads (cp.async.bulk.tensor, 128
+// byte swizzle) of x and W into a ring of shared-memory stages and arms each
+// stage's mbarrier with the bytes to expect.  Warp 1 owns tensor memory: it
+// allocates BN columns, and one thread issues tcgen05.mma (128 x BN x 16,
+// operands straight from shared memory through matrix descriptors,
+// accumulator in tensor memory) four times per stage and commits the stage's
+// "empty" barrier, so the producer may refill it while the tensor core still
+// works on later stages.  Warps 2-5 are the epilogue: after the last commit
+// they read the accumulator with tcgen05.ld (each warp its own 32 lanes = 32
+// output rows), convert and store.  Forms: plain (bfloat16 or float32 output)
+// and gated (W = [gate rows; up rows]; a block loads 128 gate rows and the 128
+// up rows that belong to them as one 256-row operand and writes
+// silu(gate) * up), which removes the separate activation pass over 2 I
+// columns.
+//
+// Every wait on an mbarrier is bounded: when a limit runs out the block sets
+// the status word (LE_STATUS_WAIT_TIMEOUT), stops issuing work, lets what is in
+// flight land (again bounded), frees its tensor memory and returns.
+//
+// The reference's projections are nn.Linear calls into the vendor library
+// (python/lyapunov_engine/models/llama.py:45-48,112-117,177).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int BM = 128;
+constexpr int BK = 64;                 // 128 bytes of bfloat16: one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;           // producer warp, MMA warp, four epilogue warps
+constexpr unsigned long long WAIT_LIMIT_NS = 200ull * 1000 * 1000;   // no wait inside the kernel lasts longer
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait for the phase with the given parity.  False when the time limit
+// ran out or another role of the block has already given up (`failed`).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *failed) {
+  const uint32_t addr = smem_u32(bar);
+  unsigned long long start = 0;
+  for (uint32_t i = 0;; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+    if (*failed) return false;
+    if ((i & 63) == 63) {
+      const unsigned long long t = now_ns();
+      if (start == 0) start = t;
+      else if (t - start > WAIT_LIMIT_NS) return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void *smem, const CUtensorMap *map, uint64_t *bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_load32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Matrix descriptor of a K-major tile with 128-byte rows in the 128-byte
+// swizzle: start address / 16, leading offset 1 (unused with a swizzle),
+// stride between groups of eight rows 1024 bytes, version 1, layout type 2.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  const uint64_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);
+  const uint64_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return lo | (hi << 32);
+}
+
+// BN: output columns of the tile (the N of the MMA).  GATED: the 256-row
+// operand is 128 gate rows and their 128 up rows; the tile has 128 output
+// columns.  STAGES: shared-memory stages.
+template <int BN, bool GATED, typename TO, int STAGES>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO *__restrict__ out,
+               int M, int N, int K, int64_t ldo, int up_row_offset, int *__restrict__ status) {
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+  uint64_t *empty = full + STAGES;
+  uint64_t *acc_ready = empty + STAGES;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
+  volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM;
+  const int n_out_tile = GATED ? BN / 2 : BN;        // output columns per tile
+  const int n0 = blockIdx.x * n_out_tile;            // first output column (and first gate / weight row)
+  const int num_k_tiles = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    mbar_init(acc_ready, 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- producer
+    if (lane == 0) {
+      int issued = 0;
+      for (int kt = 0; kt < num_k_tiles; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t phase = (kt / STAGES) & 1;
+        if (*failed || !mbar_wait(empty + s, phase ^ 1, failed)) { *failed = 1; break; }
+        unsigned char *a_dst = smem + s * STAGE_BYTES, *b_dst = a_dst + A_BYTES;
+        mbar_expect_tx(full + s, STAGE_BYTES);
+        tma_load_2d(a_dst, &map_a, full + s, kt * BK, m0);
+        if (GATED) {
+          tma_load_2d(b_dst, &map_b, full + s, kt * BK, n0);
+          tma_load_2d(b_dst + B_BYTES / 2, &map_b, full + s, kt * BK, up_row_offset + n0);
+        } else {
+          tma_load_2d(b_dst, &map_b, full + s, kt * BK, n0);
+        }
+        issued = kt + 1;
+      }
+      if (*failed) {
+        // let the copies already issued land before the block goes away
+        atomicOr(status, LE_STATUS_WAIT_TIMEOUT);
+        volatile int never = 0;
+        for (int kt = max(0, issued - STAGES); kt < issued; ++kt) mbar_wait(full + kt % STAGES, (kt / STAGES) & 1, &never);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- tensor-core issue
+    if (lane == 0) {
+      // instruction descriptor: F32 accumulate, BF16 x BF16, both K-major, N >> 3, M >> 4
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                 (static_cast<uint32_t>(BM >> 4) << 24);
+      bool ok = true;
+      for (int kt = 0; kt < num_k_tiles && ok; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t phase = (kt / STAGES) & 1;
+        if (*failed || !mbar_wait(full + s, phase, failed)) { *failed = 1; ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint64_t da = smem_desc(a_addr + k * UMMA_K * 2), db = smem_desc(b_addr + k * UMMA_K * 2);
+          tc_mma(tmem_base, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(empty + s);          // arrives when the MMAs above have read the stage
+      }
+      if (ok) tc_commit(acc_ready);    // arrives when the accumulator is complete
+      else atomicOr(status, LE_STATUS_WAIT_TIMEOUT);
+    }
+  } else {
+    // ---- epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. + 31, i.e. those rows of the tile
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    bool ok = num_k_tiles > 0 && mbar_wait(acc_ready, 0, failed);
+    if (!ok && lane == 0 && num_k_tiles > 0) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (ok) {
+      tc_fence_after();
+      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      TO *dst = out + static_cast<int64_t>(row) * ldo;
+#pragma unroll 1
+      for (int c = 0; c < n_out_tile; c += 32) {
+        uint32_t v[32], u[32];
+        tc_load32(lane_addr + c, v);
+        if (GATED) tc_load32(lane_addr + BN / 2 + c, u);
+        if (row < M) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            const int col = n0 + c + j;
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              f[i] = __uint_as_float(v[j + i]);
+              if (GATED) f[i] = f[i] / (1.0f + __expf(-f[i])) * __uint_as_float(u[j + i]);
+            }
+            const int n_limit = GATED ? N / 2 : N;
+            if (col + 8 <= n_limit && (reinterpret_cast<uintptr_t>(dst + col) & 15) == 0) {
+              if constexpr (sizeof(TO) == 2) {
+                uint4 pack;
+                __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pack);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                *reinterpret_cast<uint4 *>(dst + col) = pack;
+              } else {
+                *reinterpret_cast<float4 *>(dst + col) = make_float4(f[0], f[1], f[2], f[3]);
+                *reinterpret_cast<float4 *>(dst + col + 4) = make_float4(f[4], f[5], f[6], f[7]);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                if (col + i < n_limit) dst[col + i] = le::from_f32<TO>(f[i]);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+  }
+}
+
+// ---- tensor maps (host)
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &res) != cudaSuccess || res != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void *ptr; int rows, cols, box_rows; int64_t ld;
+  bool operator==(const MapKey &o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && ld == o.ld; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey &k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h = h * 1000003u ^ static_cast<size_t>(k.rows);
+    h = h * 1000003u ^ static_cast<size_t>(k.cols);
+    h = h * 1000003u ^ static_cast<size_t>(k.box_rows);
+    return h * 1000003u ^ static_cast<size_t>(k.ld);
+  }
+};
+
+// A [rows, cols] bfloat16 matrix with `ld` elements between rows, fetched in
+// boxes of box_rows x 64 columns with the 128-byte swizzle; outside the matrix
+// a box reads zeros.
+int tensor_map(CUtensorMap *out, const void *ptr, int rows, int cols, int64_t ld, int box_rows) {
+  static std::mutex guard;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{ptr, rows, cols, box_rows, ld};
+  std::lock_guard<std::mutex> lock(guard);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return le::invalid("le_gemm_tc_bf16: the driver does not export cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  CUtensorMap map;
+  const CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return le::invalid("le_gemm_tc_bf16: cuTensorMapEncodeTiled failed (%d) for a %d x %d matrix, ld %lld", static_cast<int>(r), rows, cols, static_cast<long long>(ld));
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, map);
+  *out = map;
+  return 0;
+}
+
+template <int BN, bool GATED, typename TO>
+int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int *status,
+           cudaStream_t stream) {
+  constexpr int STAGES = BN == 256 ? 4 : 3;   // 192 KB: one block per SM; 96 KB: two
+  constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
+  const size_t smem = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024 + 256;
+  CUtensorMap map_a, map_b;
+  int rc = tensor_map(&map_a, x, M, K, ldx, BM);
+  if (rc != 0) return rc;
+  rc = tensor_map(&map_b, w, N, K, ldw, GATED ? BN / 2 : BN);
+  if (rc != 0) return rc;
+  auto kernel = gemm_tc_kernel<BN, GATED, TO, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return le::invalid("le_gemm_tc_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+  const int n_out = GATED ? N / 2 : N;
+  const int n_tile = GATED ? BN / 2 : BN;
+  dim3 grid((n_out + n_tile - 1) / n_tile, (M + BM - 1) / BM);
+  kernel<<<grid, THREADS, smem, stream>>>(map_a, map_b, static_cast<TO *>(out), M, N, K, ldo, GATED ? N / 2 : 0, status);
+  return le::launched();
+}
+
+}  // namespace
+
+// gated = 0: out[M, N] (bfloat16 or float32) = x W^T.  gated = 1: W is
+// [N = 2 I, K] (gate rows, then up rows), out is bfloat16 [M, I] =
+// silu(x Wg^T) * (x Wu^T).  Needs K and the leading dimensions of x and W to
+// be multiples of 8 and their base addresses 16-byte aligned (TMA).
+LE_API int le_gemm_tc_bf16(void *out, int out_dtype, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw,
+                           int64_t ldo, int gated, int *status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) return le::invalid("le_gemm_tc_bf16: K (%d) and the leading dimensions must be multiples of 8", K);
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return le::invalid("le_gemm_tc_bf16: x and W must be 16-byte aligned");
+  if (gated) {
+    if (out_dtype != LE_BF16 || N % 2) return le::invalid("le_gemm_tc_bf16: the gated form has bfloat16 output and an even N");
+    return launch<256, true, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);
+  }
+  const int64_t tiles256 = static_cast<int64_t>((M + BM - 1) / BM) * ((N + 255) / 256);
+  const bool wide = tiles256 >= 2 * 148;
+  if (out_dtype == LE_BF16)
+    return wide ? launch<256, false, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream)
+                : launch<128, false, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);
+  if (out_dtype == LE_F32)
+    return wide ? launch<256, false, float>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream)
+                : launch<128, false, float>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);
+  return le::invalid("le_gemm_tc_bf16: unknown dtype code %d", out_dtype);
+}

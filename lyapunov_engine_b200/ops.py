@@ -60,6 +60,8 @@ _CORE_SIGNATURES = {
     "le_convert": [c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p],
     "le_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_float, c_int,
                    c_int, c_void_p],
+    "le_gemm_tc_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
+                        c_void_p, c_void_p],
     "le_gemm_skinny_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
                             c_int64, c_int, c_void_p],
     "le_rope_kv_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -264,6 +266,38 @@ def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, splits: int
            "le_gemm_skinny_bf16")
 
 
+_tc_status = {}
+
+
+def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = False) -> None:
+    """The package's tcgen05 / TMA product for many rows (bfloat16 inputs):
+    out = a @ w^T (bfloat16 or float32), or with ``gated`` out = silu(a Wg^T) *
+    (a Wu^T) for w = [Wg; Wu]."""
+    _need_cuda(out, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+    assert out.shape == (M, N // 2 if gated else N) and out.stride(1) == 1 and a.stride(1) == 1 and w.stride(1) == 1
+    status = _tc_status.get(a.device)
+    if status is None:
+        status = _tc_status[a.device] = new_status(a.device)
+    _check(core().le_gemm_tc_bf16(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0),
+                                  out.stride(0), 1 if gated else 0, _ptr(status), _stream()), "le_gemm_tc_bf16")
+
+
+def tc_status(device) -> torch.Tensor:
+    """The status word of the tensor-core product (a bounded wait that ran out sets it)."""
+    status = _tc_status.get(torch.device(device))
+    if status is None:
+        status = _tc_status[torch.device(device)] = new_status(device)
+    return status
+
+
+def tc_applies(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 def split_k_for(n_out: int, k: int) -> int:
     """How many slices of K give a product enough blocks to fill the GPU."""
     blocks = (n_out + 15) // 16
@@ -359,7 +393,7 @@ def attention_mma_available(head_dim: int) -> bool:
 def attention_prefill_bf16(out, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, tile_request, tile_q0,
                            num_tiles, num_heads, num_kv_heads, head_dim, page_size, window, scale, status) -> None:
     """Tensor-core attention for requests that bring several tokens; the tiles
-    list 64 query tokens each."""
+    list 128 query tokens each."""
     _need_cuda(out, q, k_cache, v_cache, block_table)
     lib = attention_lib(head_dim)
     assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[1] == num_heads * head_dim

@@ -15,7 +15,7 @@ import torch
 from .. import ops
 
 GENERIC_TILE = 16
-PREFILL_TILE = 64
+PREFILL_TILE = 128
 DECODE_KEYS_PER_SPLIT = 256     # a split is worth its launch from about four tiles of keys
 DECODE_MAX_SPLITS = 64
 RESIDENT_BLOCKS = 2 * 148       # blocks of the decode kernel that are resident at once on a B200

@@ -126,7 +126,7 @@ def test_tensor_core_kernels(case):
         if multi:
             req, q0 = [], []
             for b in multi:
-                for s in range(0, q_lens[b], 64):
+                for s in range(0, q_lens[b], 128):
                     req.append(b); q0.append(s)
             ops.attention_prefill_bf16(out, c["q"], c["q"].stride(0), c["k"], c["v"], c["table"], c["cu"], c["ctx"],
                                        torch.tensor(req, dtype=torch.int32, device=DEV),

@@ -268,3 +268,41 @@ def test_norm_adds_partial_sums_in_order():
     o.rmsnorm(out2, r, parts.to(DEV), w.to(DEV), 1e-5, rows=rows)
     want = plain_llama.plain_rmsnorm(summed + parts.sum(0), w, 1e-5)[[6, 2]]
     torch.testing.assert_close(out2.float().cpu(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 256), (200, 384, 136), (17, 515 - 3, 96), (1000, 1000, 328),
+                                   (2048, 3072, 2048), (130, 8, 8)])
+def test_tensor_core_product(M, N, K):
+    """The tcgen05 / TMA product against a float64 product of the same bfloat16 inputs."""
+    o = ops()
+    g = torch.Generator().manual_seed(M + N + K)
+    a = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.5).bfloat16()
+    want = (a.double() @ w.double().t()).float()
+    scale = float(want.abs().max())
+    for dtype, tol in ((torch.float32, dict(atol=1e-4 * scale + 1e-4, rtol=1e-4)), (torch.bfloat16, dict(atol=1e-2 * scale, rtol=1e-2))):
+        out = torch.full((M, N), 9.0, dtype=dtype, device=DEV)
+        o.gemm_tc(out, a.to(DEV), w.to(DEV))
+        torch.cuda.synchronize()
+        o.check_status(o.tc_status(DEV))
+        torch.testing.assert_close(out.float().cpu(), want, **tol)
+    if N % 2 == 0:
+        act = torch.full((M, N // 2), 9.0, dtype=torch.bfloat16, device=DEV)
+        o.gemm_tc(act, a.to(DEV), w.to(DEV), gated=True)
+        torch.cuda.synchronize()
+        o.check_status(o.tc_status(DEV))
+        ref = plain_llama.plain_swiglu(want[:, :N // 2], want[:, N // 2:])
+        torch.testing.assert_close(act.float().cpu(), ref, atol=1e-2 * float(ref.abs().max()) + 1e-3, rtol=2e-2)
+
+
+def test_tensor_core_product_on_a_strided_input():
+    """Rows of x that are wider than K (a slice of a fused buffer)."""
+    o = ops()
+    g = torch.Generator().manual_seed(1)
+    big = (torch.randn(300, 256, generator=g) * 0.5).bfloat16().to(DEV)
+    a = big[:, 64:192]
+    w = (torch.randn(72, 128, generator=g) * 0.5).bfloat16().to(DEV)
+    out = torch.empty(300, 72, dtype=torch.float32, device=DEV)
+    o.gemm_tc(out, a, w)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.cpu(), (a.double().cpu() @ w.double().cpu().t()).float(), atol=1e-3, rtol=1e-4)
