@@ -183,7 +183,8 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
   bf16 *k_tiles = q_tile + PF_BM * HD;
   bf16 *v_tiles = k_tiles + PF_STAGES * BN * HD;
 
-  const int tile = blockIdx.x, head = blockIdx.y;
+  // later tiles of a prompt see more keys and take longer: start them first
+  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
   const int kvh = head / (num_heads / num_kv_heads);
   const int b = tile_request[tile];
   const int q0 = tile_q0[tile];

@@ -17,6 +17,10 @@
 // silu(gate) * up), which removes the separate activation pass over 2 I
 // columns.
 //
+// The kernel is persistent (one block per SM walks a list of tiles) and keeps
+// two accumulators in tensor memory, so the epilogue of a tile overlaps the
+// products of the next.
+//
 // Every wait on an mbarrier is bounded: when a limit runs out the block sets
 // the status word (LE_STATUS_WAIT_TIMEOUT), stops issuing work, lets what is in
 // flight land (again bounded), frees its tensor memory and returns.
@@ -111,36 +115,42 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
   return lo | (hi << 32);
 }
 
-// BN: output columns of the tile (the N of the MMA).  GATED: the 256-row
-// operand is 128 gate rows and their 128 up rows; the tile has 128 output
-// columns.  STAGES: shared-memory stages.
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// BN: output columns of the MMA.  GATED: the BN-row operand is BN/2 gate rows
+// and their BN/2 up rows; a tile then has BN/2 output columns.  STAGES:
+// shared-memory stages.  The kernel is persistent: block b takes tiles b,
+// b + gridDim.x, ...; two accumulators in tensor memory alternate, so the
+// epilogue of one tile runs while the tensor core works on the next.
 template <int BN, bool GATED, typename TO, int STAGES>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO *__restrict__ out,
-               int M, int N, int K, int64_t ldo, int up_row_offset, int *__restrict__ status) {
+               int M, int N, int K, int64_t ldo, int up_row_offset, int tiles_m, int tiles_n, int *__restrict__ status) {
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int N_TILE = GATED ? BN / 2 : BN;        // output columns per tile
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
   uint64_t *empty = full + STAGES;
-  uint64_t *acc_ready = empty + STAGES;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
+  uint64_t *acc_full = empty + STAGES;               // [2]
+  uint64_t *acc_empty = acc_full + 2;                // [2]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
   volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM;
-  const int n_out_tile = GATED ? BN / 2 : BN;        // output columns per tile
-  const int n0 = blockIdx.x * n_out_tile;            // first output column (and first gate / weight row)
   const int num_k_tiles = (K + BK - 1) / BK;
+  const int num_tiles = tiles_m * tiles_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
-    mbar_init(acc_ready, 1);
+    for (int a = 0; a < 2; ++a) { mbar_init(acc_full + a, 1); mbar_init(acc_empty + a, 4); }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -149,29 +159,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---- producer
+    // ---- producer: one thread keeps the ring of stages full across all of this block's tiles
     if (lane == 0) {
       int issued = 0;
-      for (int kt = 0; kt < num_k_tiles; ++kt) {
-        const int s = kt % STAGES;
-        const uint32_t phase = (kt / STAGES) & 1;
-        if (*failed || !mbar_wait(empty + s, phase ^ 1, failed)) { *failed = 1; break; }
-        unsigned char *a_dst = smem + s * STAGE_BYTES, *b_dst = a_dst + A_BYTES;
-        mbar_expect_tx(full + s, STAGE_BYTES);
-        tma_load_2d(a_dst, &map_a, full + s, kt * BK, m0);
-        if (GATED) {
-          tma_load_2d(b_dst, &map_b, full + s, kt * BK, n0);
-          tma_load_2d(b_dst + B_BYTES / 2, &map_b, full + s, kt * BK, up_row_offset + n0);
-        } else {
-          tma_load_2d(b_dst, &map_b, full + s, kt * BK, n0);
+      for (int tile = blockIdx.x; tile < num_tiles && !*failed; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * N_TILE;
+        for (int kt = 0; kt < num_k_tiles; ++kt, ++issued) {
+          const int s = issued % STAGES;
+          const uint32_t phase = (issued / STAGES) & 1;
+          if (*failed || !mbar_wait(empty + s, phase ^ 1, failed)) { *failed = 1; break; }
+          unsigned char *a_dst = smem + s * STAGE_BYTES, *b_dst = a_dst + A_BYTES;
+          mbar_expect_tx(full + s, STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, full + s, kt * BK, m0);
+          if (GATED) {
+            tma_load_2d(b_dst, &map_b, full + s, kt * BK, n0);
+            tma_load_2d(b_dst + B_BYTES / 2, &map_b, full + s, kt * BK, up_row_offset + n0);
+          } else {
+            tma_load_2d(b_dst, &map_b, full + s, kt * BK, n0);
+          }
         }
-        issued = kt + 1;
       }
       if (*failed) {
         // let the copies already issued land before the block goes away
         atomicOr(status, LE_STATUS_WAIT_TIMEOUT);
         volatile int never = 0;
-        for (int kt = max(0, issued - STAGES); kt < issued; ++kt) mbar_wait(full + kt % STAGES, (kt / STAGES) & 1, &never);
+        for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(full + i % STAGES, (i / STAGES) & 1, &never);
       }
     }
   } else if (warp == 1) {
@@ -180,36 +192,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // instruction descriptor: F32 accumulate, BF16 x BF16, both K-major, N >> 3, M >> 4
       constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                                  (static_cast<uint32_t>(BM >> 4) << 24);
+      int consumed = 0, local = 0;
       bool ok = true;
-      for (int kt = 0; kt < num_k_tiles && ok; ++kt) {
-        const int s = kt % STAGES;
-        const uint32_t phase = (kt / STAGES) & 1;
-        if (*failed || !mbar_wait(full + s, phase, failed)) { *failed = 1; ok = false; break; }
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        // the epilogue must have drained this accumulator (two tiles ago)
+        if (*failed || !mbar_wait(acc_empty + acc, ((local >> 1) & 1) ^ 1, failed)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+        const uint32_t tmem_acc = tmem_base + acc * BN;
+        for (int kt = 0; kt < num_k_tiles; ++kt, ++consumed) {
+          const int s = consumed % STAGES;
+          const uint32_t phase = (consumed / STAGES) & 1;
+          if (*failed || !mbar_wait(full + s, phase, failed)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          const uint64_t da = smem_desc(a_addr + k * UMMA_K * 2), db = smem_desc(b_addr + k * UMMA_K * 2);
-          tc_mma(tmem_base, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = smem_desc(a_addr + k * UMMA_K * 2), db = smem_desc(b_addr + k * UMMA_K * 2);
+            tc_mma(tmem_acc, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(empty + s);          // arrives when the MMAs above have read the stage
         }
-        tc_commit(empty + s);          // arrives when the MMAs above have read the stage
+        if (ok) tc_commit(acc_full + acc);   // arrives when this tile's accumulator is complete
       }
-      if (ok) tc_commit(acc_ready);    // arrives when the accumulator is complete
-      else atomicOr(status, LE_STATUS_WAIT_TIMEOUT);
+      if (!ok) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
     }
   } else {
     // ---- epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. + 31, i.e. those rows of the tile
     const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
-    bool ok = num_k_tiles > 0 && mbar_wait(acc_ready, 0, failed);
-    if (!ok && lane == 0 && num_k_tiles > 0) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
-    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-    if (ok) {
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * N_TILE;
+      const int acc = local & 1;
+      const int row = m0 + quarter * 32 + lane;
+      bool ok = mbar_wait(acc_full + acc, (local >> 1) & 1, failed);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) {
+        if (lane == 0) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
+        break;
+      }
       tc_fence_after();
-      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t lane_addr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       TO *dst = out + static_cast<int64_t>(row) * ldo;
+      const int n_limit = GATED ? N / 2 : N;
 #pragma unroll 1
-      for (int c = 0; c < n_out_tile; c += 32) {
+      for (int c = 0; c < N_TILE; c += 32) {
         uint32_t v[32], u[32];
         tc_load32(lane_addr + c, v);
         if (GATED) tc_load32(lane_addr + BN / 2 + c, u);
@@ -223,7 +250,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               f[i] = __uint_as_float(v[j + i]);
               if (GATED) f[i] = f[i] / (1.0f + __expf(-f[i])) * __uint_as_float(u[j + i]);
             }
-            const int n_limit = GATED ? N / 2 : N;
             if (col + 8 <= n_limit && (reinterpret_cast<uintptr_t>(dst + col) & 15) == 0) {
               if constexpr (sizeof(TO) == 2) {
                 uint4 pack;
@@ -243,13 +269,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
       }
+      // this warp has read its part of the accumulator: hand it back to the tensor core
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty + acc);
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
   }
 }
 
@@ -313,7 +343,7 @@ int tensor_map(CUtensorMap *out, const void *ptr, int rows, int cols, int64_t ld
 template <int BN, bool GATED, typename TO>
 int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int *status,
            cudaStream_t stream) {
-  constexpr int STAGES = BN == 256 ? 4 : 3;   // 192 KB: one block per SM; 96 KB: two
+  constexpr int STAGES = BN == 256 ? 4 : 6;   // 192 KB either way: one persistent block per SM
   constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
   const size_t smem = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024 + 256;
   CUtensorMap map_a, map_b;
@@ -326,8 +356,21 @@ int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t
   if (e != cudaSuccess) return le::invalid("le_gemm_tc_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   const int n_out = GATED ? N / 2 : N;
   const int n_tile = GATED ? BN / 2 : BN;
-  dim3 grid((n_out + n_tile - 1) / n_tile, (M + BM - 1) / BM);
-  kernel<<<grid, THREADS, smem, stream>>>(map_a, map_b, static_cast<TO *>(out), M, N, K, ldo, GATED ? N / 2 : 0, status);
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (n_out + n_tile - 1) / n_tile;
+  int sms = 148;
+  {
+    static int cached = 0;
+    if (cached == 0) {
+      int dev = 0, count = 0;
+      if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && count > 0) cached = count;
+      else cached = 148;
+    }
+    sms = cached;
+  }
+  const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
+  const int blocks = static_cast<int>(tiles < sms ? tiles : sms);
+  kernel<<<blocks, THREADS, smem, stream>>>(map_a, map_b, static_cast<TO *>(out), M, N, K, ldo, GATED ? N / 2 : 0, tiles_m,
+                                             tiles_n, status);
   return le::launched();
 }
 
@@ -346,8 +389,10 @@ LE_API int le_gemm_tc_bf16(void *out, int out_dtype, const void *x, const void *
     if (out_dtype != LE_BF16 || N % 2) return le::invalid("le_gemm_tc_bf16: the gated form has bfloat16 output and an even N");
     return launch<256, true, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);
   }
-  const int64_t tiles256 = static_cast<int64_t>((M + BM - 1) / BM) * ((N + 255) / 256);
-  const bool wide = tiles256 >= 2 * 148;
+  // 128 x 256 tiles unless their last round of tiles over the SMs would be emptier than with 128 x 128
+  const int64_t tiles_m = (M + BM - 1) / BM;
+  const int64_t rounds256 = (tiles_m * ((N + 255) / 256) + 147) / 148, rounds128 = (tiles_m * ((N + 127) / 128) + 147) / 148;
+  const bool wide = 2 * rounds256 <= rounds128;
   if (out_dtype == LE_BF16)
     return wide ? launch<256, false, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream)
                 : launch<128, false, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);

@@ -14,6 +14,7 @@ reference's do (nn.Linear, python/lyapunov_engine/models/llama.py:45-48,112-117,
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_int64, c_void_p
 
 import torch
@@ -269,7 +270,7 @@ def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, splits: int
 _tc_status = {}
 
 
-def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = False) -> None:
+def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = False, status=None) -> None:
     """The package's tcgen05 / TMA product for many rows (bfloat16 inputs):
     out = a @ w^T (bfloat16 or float32), or with ``gated`` out = silu(a Wg^T) *
     (a Wu^T) for w = [Wg; Wu]."""
@@ -278,9 +279,8 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = F
     N = w.shape[0]
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
     assert out.shape == (M, N // 2 if gated else N) and out.stride(1) == 1 and a.stride(1) == 1 and w.stride(1) == 1
-    status = _tc_status.get(a.device)
     if status is None:
-        status = _tc_status[a.device] = new_status(a.device)
+        status = tc_status(a.device)
     _check(core().le_gemm_tc_bf16(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0),
                                   out.stride(0), 1 if gated else 0, _ptr(status), _stream()), "le_gemm_tc_bf16")
 
@@ -298,13 +298,29 @@ def tc_applies(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+# Plain products with many rows: the package's tcgen05 kernel (one block per SM, 128 x 256 tiles) measures 7-18 %
+# behind the library's two-SM kernels on this model's shapes, so they go to the library unless this is set; the
+# gated product, where the fused activation more than pays for it, always uses the package's kernel.
+TC_PLAIN_PRODUCTS = os.environ.get("LYAPUNOV_TC_PLAIN", "0") not in ("0", "")
+
+
+def tc_fills_the_gpu(m: int, n: int) -> bool:
+    """Whether 128 x 256 tiles of an [m, n] product fill the 148 SMs in whole
+    rounds.  The package's kernel has that one tile shape; where it leaves the
+    last round mostly empty the library, which picks among many shapes, is
+    faster, and a plain product may go to it."""
+    tiles = ((m + 127) // 128) * ((n + 255) // 256)
+    rounds = (tiles + 147) // 148
+    return tiles >= 0.8 * rounds * 148
+
+
 def split_k_for(n_out: int, k: int) -> int:
     """How many slices of K give a product enough blocks to fill the GPU."""
     blocks = (n_out + 15) // 16
     return max(1, min((SKINNY_BLOCKS + blocks - 1) // blocks, k // 512, 16))
 
 
-def linear_for_residual(a: torch.Tensor, w: torch.Tensor, workspace, key: str):
+def linear_for_residual(a: torch.Tensor, w: torch.Tensor, workspace, key: str, status=None):
     """a @ w^T for a product whose only use is to be added to the residual
     stream: returns either the tensor [M, N] in the activations' type or, for
     few rows, float32 partial sums [S, M, N] that the next norm adds up."""
@@ -318,31 +334,40 @@ def linear_for_residual(a: torch.Tensor, w: torch.Tensor, workspace, key: str):
             gemm_skinny(out, a, w, splits=splits)
         return out
     out = workspace.get(key, (M, N), a.dtype)
-    linear(out, a, w)
+    linear(out, a, w, status)
     return out
 
 
-def gated_linear(out: torch.Tensor, a: torch.Tensor, w_gate_up: torch.Tensor, workspace) -> None:
-    """out = silu(a @ w_gate^T) * (a @ w_up^T), w_gate_up = [gate rows; up rows]."""
+def gated_linear(out: torch.Tensor, a: torch.Tensor, w_gate_up: torch.Tensor, workspace, status=None) -> None:
+    """out = silu(a @ w_gate^T) * (a @ w_up^T), w_gate_up = [gate rows; up rows].
+    bfloat16: one kernel of the package (weight-streaming for few rows, tcgen05
+    for many) with the activation in its epilogue."""
     if skinny_applies(a, w_gate_up):
         gemm_skinny(out, a, w_gate_up, gated=True)
         return
+    if tc_applies(a, w_gate_up):
+        gemm_tc(out, a, w_gate_up, gated=True, status=status)
+        return
     gu = workspace.get("gate_up", (a.shape[0], w_gate_up.shape[0]), a.dtype)
-    linear(gu, a, w_gate_up)
+    linear(gu, a, w_gate_up, status)
     swiglu(out, gu)
 
 
-def linear(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
-    """out = a @ w^T.  float32: the package's FP32 kernel.  bfloat16 with at
-    most 64 rows: the package's weight-streaming kernel.  bfloat16 with more
-    rows: the library product (cuBLAS), 32-bit accumulation; when ``out`` is
-    float32 the product is written in 32 bits without an intermediate rounding."""
+def linear(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status=None) -> None:
+    """out = a @ w^T.  float32: the package's FP32 kernel.  bfloat16 with few
+    rows: the package's weight-streaming kernel.  bfloat16 with many rows: the
+    package's tcgen05 kernel where its tiles fill the GPU, else the library
+    product (cuBLAS); 32-bit accumulation everywhere, and a float32 ``out`` is
+    written without an intermediate rounding."""
     if a.dtype == torch.float32:
         gemm_simt(out, a, w)
         return
     _need_cuda(out, a, w)
     if skinny_applies(a, w):
         gemm_skinny(out, a, w)
+        return
+    if TC_PLAIN_PRODUCTS and tc_applies(a, w) and tc_fills_the_gpu(a.shape[0], w.shape[0]):
+        gemm_tc(out, a, w, status=status)
         return
     if out.dtype == torch.bfloat16:
         counters["library_products"] += 1

@@ -52,5 +52,5 @@ class LinearHead(Part):
 
     def forward(self, normed, ctx):
         logits = ctx.workspace.get("logits", (normed.shape[0], self.vocab_size), torch.float32)
-        ops.linear(logits, normed, self.weight)
+        ops.linear(logits, normed, self.weight, ctx.status)
         return logits

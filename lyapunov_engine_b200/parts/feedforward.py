@@ -37,5 +37,5 @@ class GatedFeedForward(FeedForward):
         T = x.shape[0]
         ws = ctx.workspace
         act = ws.get("ffn_act", (T, self.intermediate_size), rt.dtype)
-        ops.gated_linear(act, x, self.w_gate_up, ws)
-        return ops.linear_for_residual(act, self.w_down, ws, "ffn_out")
+        ops.gated_linear(act, x, self.w_gate_up, ws, ctx.status)
+        return ops.linear_for_residual(act, self.w_down, ws, "ffn_out", ctx.status)

@@ -140,6 +140,7 @@ def test_parts_alone(dtype):
         return t.to("cuda:0", torch.float32 if name == "n" else dtype)
     ctx = _Ctx()
     ctx.workspace = rt.workspace
+    ctx.status = rt.status
     tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
     rounded = {k: (v if k == "n" else v.to(dtype).float()) for k, v in tensors.items()}
 
