@@ -120,6 +120,33 @@ __device__ __forceinline__ void load_kv_tile(bf16 *k_tile, bf16 *v_tile, const K
   }
 }
 
+// One warp copies 32 keys whose first key starts a page (pages of 1..32 keys,
+// a power of two): each lane looks one page of the tile up and the others get
+// it by shuffle, so a tile costs one block-table read per lane.
+__device__ __forceinline__ void load_kv_tile_warp32(bf16 *k_tile, bf16 *v_tile, const KvLayout &kv, int k0, int k_end,
+                                                    int lane, int *status) {
+  const int pages_in_tile = 32 >> kv.page_shift;
+  int my_page = -1;
+  if (lane < pages_in_tile && k0 + (lane << kv.page_shift) < k_end) {
+    my_page = kv.table[(k0 >> kv.page_shift) + lane];
+    if (my_page < 0 || my_page >= kv.num_pages) {
+      atomicOr(status, LE_STATUS_BAD_PAGE);
+      my_page = -1;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < CPR; ++i) {
+    const int c = lane + 32 * i;
+    const int row = c / CPR, chunk = c % CPR;
+    const int page = __shfl_sync(0xffffffffu, my_page, row >> kv.page_shift);
+    const bool valid = page >= 0 && k0 + row < k_end;
+    const int64_t offset = valid ? page * kv.page_stride + kv.head_offset + (row & (kv.page_size - 1)) * HD + chunk * 8 : 0;
+    const int dst = swizzled_chunk(row, chunk) * 8;
+    cp_async16(k_tile + dst, kv.k_cache + offset, valid);
+    cp_async16(v_tile + dst, kv.v_cache + offset, valid);
+  }
+}
+
 __device__ __forceinline__ KvLayout make_kv_layout(const bf16 *k_cache, const bf16 *v_cache, const int32_t *table, int kvh,
                                                    int num_kv_heads, int page_size, int page_shift, int num_pages) {
   KvLayout kv;
@@ -130,37 +157,67 @@ __device__ __forceinline__ KvLayout make_kv_layout(const bf16 *k_cache, const bf
   return kv;
 }
 
-// S[16 x 64] += Q[16 x HD] K^T for one warp: q fragments in registers, keys
-// rows [key0, key0 + 8 * NT) of the tile.
+// Where each lane's ldmatrix rows lie in a swizzled tile does not change from
+// tile to tile: the element offsets are computed once per kernel.
+// S = Q K^T reads, per k-step and pair of 8-key n-tiles, one x4 of K.
 template <int NT>
-__device__ __forceinline__ void scores(float (&s)[NT][4], const uint32_t (&qf)[KSTEPS][4], const bf16 *k_tile, int key0, int lane) {
+struct ScoreOffsets {
+  int off[KSTEPS][NT / 2];
+  __device__ __forceinline__ void init(int lane) {
+    const int j = lane >> 3;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+      for (int np = 0; np < NT / 2; ++np) {
+        const int row = np * 16 + (j >> 1) * 8 + (lane & 7);
+        off[ks][np] = swizzled_chunk(row, ks * 2 + (j & 1)) * 8;
+      }
+  }
+};
+// O += P V reads, per 16 keys and pair of 8-dim n-tiles, one transposed x4 of V.
+template <int KK>
+struct ValueOffsets {
+  int off[KK][NT_O / 2];
+  __device__ __forceinline__ void init(int lane) {
+    const int j = lane >> 3;
+#pragma unroll
+    for (int kk = 0; kk < KK; ++kk)
+#pragma unroll
+      for (int np = 0; np < NT_O / 2; ++np) {
+        const int row = kk * 16 + (j & 1) * 8 + (lane & 7);
+        off[kk][np] = swizzled_chunk(row, np * 2 + (j >> 1)) * 8;
+      }
+  }
+};
+
+// S[16 x 8 NT] += Q[16 x HD] K^T for one warp: q fragments in registers.
+template <int NT>
+__device__ __forceinline__ void scores(float (&s)[NT][4], const uint32_t (&qf)[KSTEPS][4], const bf16 *k_tile,
+                                       const ScoreOffsets<NT> &at) {
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
 #pragma unroll
-    for (int nt = 0; nt < NT; nt += 2) {
+    for (int np = 0; np < NT / 2; ++np) {
       uint32_t b[4];
-      const int j = lane >> 3;
-      const int row = key0 + nt * 8 + (j >> 1) * 8 + (lane & 7);
-      ldmatrix_x4(b, k_tile + swizzled_chunk(row, ks * 2 + (j & 1)) * 8);
-      mma_bf16(s[nt], qf[ks], b[0], b[1]);
-      mma_bf16(s[nt + 1], qf[ks], b[2], b[3]);
+      ldmatrix_x4(b, k_tile + at.off[ks][np]);
+      mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
+      mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
     }
   }
 }
 
-// O[16 x HD] += P[16 x 16*KK] V for one warp: probabilities as A fragments.
+// O[16 x HD] += P[16 x 16 KK] V for one warp: probabilities as A fragments.
 template <int KK>
-__device__ __forceinline__ void weighted_values(float (&o)[NT_O][4], const uint32_t (&pf)[KK][4], const bf16 *v_tile, int key0, int lane) {
+__device__ __forceinline__ void weighted_values(float (&o)[NT_O][4], const uint32_t (&pf)[KK][4], const bf16 *v_tile,
+                                                const ValueOffsets<KK> &at) {
 #pragma unroll
   for (int kk = 0; kk < KK; ++kk) {
 #pragma unroll
-    for (int nt = 0; nt < NT_O; nt += 2) {
+    for (int np = 0; np < NT_O / 2; ++np) {
       uint32_t b[4];
-      const int j = lane >> 3;
-      const int row = key0 + kk * 16 + (j & 1) * 8 + (lane & 7);
-      ldmatrix_x4_trans(b, v_tile + swizzled_chunk(row, nt + (j >> 1)) * 8);
-      mma_bf16(o[nt], pf[kk], b[0], b[1]);
-      mma_bf16(o[nt + 1], pf[kk], b[2], b[3]);
+      ldmatrix_x4_trans(b, v_tile + at.off[kk][np]);
+      mma_bf16(o[2 * np], pf[kk], b[0], b[1]);
+      mma_bf16(o[2 * np + 1], pf[kk], b[2], b[3]);
     }
   }
 }
@@ -214,6 +271,10 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
   cp_async_commit();
 
   uint32_t qf[KSTEPS][4];
+  ScoreOffsets<BN / 8> k_at;
+  ValueOffsets<BN / 16> v_at;
+  k_at.init(lane);
+  v_at.init(lane);
   float o[NT_O][4];
 #pragma unroll
   for (int nt = 0; nt < NT_O; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
@@ -255,7 +316,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
       float s[BN / 8][4];
 #pragma unroll
       for (int nt = 0; nt < BN / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
-      scores<BN / 8>(s, qf, k_tile, 0, lane);
+      scores<BN / 8>(s, qf, k_tile, k_at);
       // only tiles that cross the causal diagonal or the window's edge need the mask
       const bool needs_mask = k0 + BN - 1 > warp_p_first || k0 < warp_lo_last;
       if (needs_mask) {
@@ -308,7 +369,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
         o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0];
         o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
       }
-      weighted_values<BN / 16>(o, pf, v_tile, 0, lane);
+      weighted_values<BN / 16>(o, pf, v_tile, v_at);
     }
     __syncthreads();   // everyone is done with this stage before it is filled again
   }
@@ -393,58 +454,75 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
     }
   }
 
+  ScoreOffsets<DC_TILE / 8> k_at;
+  ValueOffsets<DC_TILE / 16> v_at;
+  k_at.init(lane);
+  v_at.init(lane);
   float o[NT_O][4];
 #pragma unroll
   for (int nt = 0; nt < NT_O; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
   const float sl2 = scale * LOG2E;
+  const bool upper_rows = heads_here > 8;     // rows 8..15 of the MMA are padding for small groups
 
+  // pages that divide a tile and tiles that start on a page boundary take the cheap loader
+  const bool paged_tiles = page_shift >= 0 && page_size <= DC_TILE && (k_begin & (page_size - 1)) == 0;
+  auto load_tile = [&](int stage, int i) {
+    if (paged_tiles) load_kv_tile_warp32(k_stage(stage), v_stage(stage), kv, tile_start(i), k_end, lane, status);
+    else load_kv_tile<DC_TILE>(k_stage(stage), v_stage(stage), kv, tile_start(i), k_end, lane, 32, status);
+  };
 #pragma unroll
   for (int s = 0; s < DC_STAGES - 1; ++s) {
-    if (s < my_tiles) load_kv_tile<DC_TILE>(k_stage(s), v_stage(s), kv, tile_start(s), k_end, lane, 32, status);
+    if (s < my_tiles) load_tile(s, s);
     cp_async_commit();
   }
   for (int it = 0; it < my_tiles; ++it) {
     cp_async_wait<DC_STAGES - 2>();
     __syncwarp();                          // tile `it` has landed for every lane; stage of it - 1 is free
     const int nxt = it + DC_STAGES - 1;
-    if (nxt < my_tiles) load_kv_tile<DC_TILE>(k_stage(nxt % DC_STAGES), v_stage(nxt % DC_STAGES), kv, tile_start(nxt), k_end, lane, 32, status);
+    if (nxt < my_tiles) load_tile(nxt % DC_STAGES, nxt);
     cp_async_commit();
     const bf16 *k_tile = k_stage(it % DC_STAGES), *v_tile = v_stage(it % DC_STAGES);
     const int k0 = tile_start(it);
     float s[DC_TILE / 8][4];
 #pragma unroll
     for (int nt = 0; nt < DC_TILE / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
-    scores<DC_TILE / 8>(s, qf, k_tile, 0, lane);
-    float tile_max[2] = {-INFINITY, -INFINITY};
+    scores<DC_TILE / 8>(s, qf, k_tile, k_at);
     const bool full = k0 + DC_TILE <= k_end;
+    if (!full) {
 #pragma unroll
-    for (int nt = 0; nt < DC_TILE / 8; ++nt) {
+      for (int nt = 0; nt < DC_TILE / 8; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int pos = k0 + nt * 8 + 2 * t + (e & 1);
-        s[nt][e] = (full || pos < k_end) ? s[nt][e] * sl2 : -INFINITY;
-        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[nt][e]);
-      }
+        for (int e = 0; e < 4; ++e)
+          if (k0 + nt * 8 + 2 * t + (e & 1) >= k_end) s[nt][e] = -INFINITY;
     }
-    float alpha[2], m_new[2];
+    // softmax per row in units of the raw score; rows 8..15 only when they hold heads
+    float alpha[2] = {1.0f, 1.0f};
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
-      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-      m_new[r] = fmaxf(m_run[r], tile_max[r]);
-      alpha[r] = (m_new[r] == -INFINITY) ? 1.0f : exp2f(m_run[r] - m_new[r]);
-      m_run[r] = m_new[r];
-      l_run[r] *= alpha[r];
-    }
+      if (r == 1 && !upper_rows) {
 #pragma unroll
-    for (int nt = 0; nt < DC_TILE / 8; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float pr = (s[nt][e] == -INFINITY) ? 0.0f : exp2f(s[nt][e] - m_new[e >> 1]);
-        s[nt][e] = pr;
-        l_run[e >> 1] += pr;
+        for (int nt = 0; nt < DC_TILE / 8; ++nt) s[nt][2] = s[nt][3] = 0.0f;
+        continue;
       }
+      float tile_max = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < DC_TILE / 8; ++nt) tile_max = fmaxf(tile_max, fmaxf(s[nt][2 * r], s[nt][2 * r + 1]));
+      tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+      tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+      const float m_new = fmaxf(m_run[r], tile_max);
+      alpha[r] = (m_new == -INFINITY) ? 1.0f : exp2f((m_run[r] - m_new) * sl2);
+      const float neg_m = (m_new == -INFINITY) ? 0.0f : -m_new * sl2;
+      m_run[r] = m_new;
+      float sum = 0.0f;
+#pragma unroll
+      for (int nt = 0; nt < DC_TILE / 8; ++nt) {
+        const float p0 = exp2f(fmaf(s[nt][2 * r], sl2, neg_m)), p1 = exp2f(fmaf(s[nt][2 * r + 1], sl2, neg_m));
+        s[nt][2 * r] = p0;
+        s[nt][2 * r + 1] = p1;
+        sum += p0 + p1;
+      }
+      l_run[r] = l_run[r] * alpha[r] + sum;
     }
     uint32_t pf[DC_TILE / 16][4];
 #pragma unroll
@@ -459,7 +537,7 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
       o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0];
       o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
     }
-    weighted_values<DC_TILE / 16>(o, pf, v_tile, 0, lane);
+    weighted_values<DC_TILE / 16>(o, pf, v_tile, v_at);
   }
   cp_async_wait<0>();
   __syncthreads();
@@ -497,7 +575,7 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
 #pragma unroll
     for (int w = 0; w < DC_WARPS; ++w) {
       const float mw = sm_m[w * 16 + row];
-      const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
+      const float f = (mw == -INFINITY) ? 0.0f : exp2f((mw - m) * sl2);
       acc += f * sm_o[(w * 16 + row) * HD + d];
       l += f * sm_l[w * 16 + row];
     }
@@ -508,7 +586,7 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
       const int64_t slot = (static_cast<int64_t>(blockIdx.z) * num_heads + head) * num_splits + split;
       part_o[slot * HD + d] = acc;
       if (d == 0) {
-        part_ml[slot * 2] = m;
+        part_ml[slot * 2] = m * sl2;          // in log2 units, as the merge kernel reads it (-inf stays -inf)
         part_ml[slot * 2 + 1] = l;
       }
     }
