@@ -317,8 +317,20 @@ def run_ours(args):
 
 
 def run_reference(args):
+    """The unmodified reference (installed under baseline/_ref with its own
+    setup.py, CUDA extension built for sm_100 through its TORCH_CUDA_ARCH_LIST
+    switch) through its own public API: LlamaForCausalLM with random weights,
+    LLMEngine.add_request / step.  Same shapes, batch, context and greedy
+    sampling as the other arm; float16, the only type its kernels take."""
     why = reference_unavailable()
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if why:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    try:
+        line = _reference_line(args)
+    except Exception as e:  # the reference's own failure is a result, not a crash of the benchmark
+        line = {"impl": "reference", "unavailable": f"the reference failed while running: {type(e).__name__}: {str(e)[:200]}"}
+    print(json.dumps(line))
     return 0
 
 
@@ -326,8 +338,87 @@ def reference_unavailable() -> str:
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "lyapunov_engine")):
         return "IanConery/lyapunov-engine is not installed under baseline/_ref (see DESIGN.md, reference arm)"
-    return ("the reference's generation loop cannot produce this metric: its model never writes the KV cache and "
-            "its engine needs a CUDA extension built for sm_86/89/90 only")
+    if not any(f.startswith("_C") and f.endswith(".so") for f in os.listdir(os.path.join(ref, "lyapunov_engine"))):
+        return "the reference was installed without its CUDA extension; its engine then returns nothing from step()"
+    return ""
+
+
+def _reference_line(args):
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+    from lyapunov_engine.engine.llm_engine import EngineConfig, LLMEngine
+    from lyapunov_engine.engine.sampling import SamplingParams
+    from lyapunov_engine.models.llama import LlamaConfig, LlamaForCausalLM
+
+    c = LLAMA_1B
+    torch.manual_seed(0)
+    torch.cuda.set_device(0)
+    config = LlamaConfig(vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], intermediate_size=c["intermediate_size"],
+                         num_hidden_layers=c["num_hidden_layers"], num_attention_heads=c["num_attention_heads"],
+                         num_key_value_heads=c["num_key_value_heads"], head_dim=c["head_dim"],
+                         max_position_embeddings=c["max_position_embeddings"], rms_norm_eps=c["rms_norm_eps"],
+                         rope_theta=c["rope_theta"])
+    model = LlamaForCausalLM(config)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() == 2:
+                p.normal_(0.0, 0.02)
+    model = model.to(dtype=torch.float16, device="cuda:0").eval()
+    batch = 8
+    steps, warmup = args.steps, max(args.warmup, 3)
+    prompt_len = CONTEXT - (steps + warmup) - 1
+    engine = LLMEngine(model, EngineConfig(model_config=config, num_blocks=batch * (CONTEXT // BLOCK_SIZE + 2),
+                                           block_size=BLOCK_SIZE, max_num_seqs=64,
+                                           max_num_batched_tokens=batch * CONTEXT + 64, dtype=torch.float16,
+                                           device="cuda:0"))
+    gen = torch.Generator().manual_seed(0)
+    sp = SamplingParams(temperature=0.0, max_tokens=steps + warmup + 1, ignore_eos=True)
+    for i in range(batch):
+        engine.add_request(f"bench-{i}", torch.randint(0, c["vocab_size"], (prompt_len,), generator=gen).tolist(), sp)
+    clocks = ClockSampler()
+    clocks.start()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    engine.step()                                   # the reference runs every waiting prompt whole in one step
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    m0 = clocks.mark()
+    t0 = time.perf_counter()
+    begin.record()
+    produced = 0
+    for _ in range(steps):
+        produced += len(engine.step())
+    end.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    m1 = clocks.mark()
+    clocks.stop()
+    ms = begin.elapsed_time(end) / steps
+    nbytes = decode_bytes(c, batch, CONTEXT)
+    pk = peaks()
+    return {
+        "impl": "reference",
+        "metric": "decode tokens/s, Llama-3.2-1B shapes, batch 8, context 4096",
+        "value": round(batch * 1000.0 / ms, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp16", "data": "synthetic: random weights N(0,0.02), token ids uniform over the vocabulary",
+        "config": {"model": "Llama-3.2-1B shapes", "layers": c["num_hidden_layers"], "layers_of_model": c["num_hidden_layers"],
+                   "global_batch": batch, "seq_len": CONTEXT, "page": BLOCK_SIZE, "parallelism": "single GPU",
+                   "timing": "CUDA events around LLMEngine.step(); working set per step > L2",
+                   "note": "the reference's model never writes its KV cache, so its decode reads pages it never filled"},
+        "clocks": clocks.summary(m0, m1),
+        "e2e": {"value": round(produced / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
+                "ms_per_step": round(wall * 1000 / steps, 4)},
+        "gpu_launches": None,
+        "prefill": {"value": round(batch * prompt_len / prefill_s, 1), "tokens": batch * prompt_len, "ms": round(prefill_s * 1000, 2)},
+        "roofline": {"bound": "hbm", "achieved": round(nbytes / (ms * 1e-3) / 1e9, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
+    }
 
 
 def main():
