@@ -68,7 +68,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -252,7 +252,7 @@ def run_ours(args):
         ms, _, _ = timed_decode(b, args.steps, args.warmup, CONTEXT)
         points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
         points[f"decode_b{b}_ms"] = round(ms, 4)
-        points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(cfg, b, CONTEXT) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(cfg, b, CONTEXT - (args.steps - 1) // 2) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
 
     # ---- prefill of 2,048 tokens
     pre_ms = timed_prefill(PREFILL_TOKENS, 5, 3)
@@ -289,7 +289,9 @@ def run_ours(args):
            "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_s * 1000 / e2e_steps, 4)}
     clocks.stop()
 
-    nbytes = decode_bytes(cfg, batch, CONTEXT)
+    # the timed steps run at contexts CONTEXT - steps + 1 .. CONTEXT: count the bytes of their mean
+    mean_context = CONTEXT - (args.steps - 1) // 2
+    nbytes = decode_bytes(cfg, batch, mean_context)
     achieved = nbytes / (ms8 * 1e-3) / 1e9
     line = {
         "metric": "decode tokens/s, Llama-3.2-1B shapes, batch 8, context 4096",
@@ -309,7 +311,7 @@ def run_ours(args):
         "library_products": kernels_per_step["library_products"] * args.steps,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": nbytes},
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": nbytes, "mean_context": mean_context},
         "points": points,
     }
     print(json.dumps(line))
@@ -424,8 +426,8 @@ def _reference_line(args):
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=64)
-    p.add_argument("--warmup", type=int, default=8)
+    p.add_argument("--steps", type=int, default=256)
+    p.add_argument("--warmup", type=int, default=16)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     p.add_argument("--only", choices=["decode", "prefill"], default=None, help="run one kind of step and exit (for profilers)")

@@ -200,9 +200,9 @@ class LLMEngine:
                 params = [self.active_sequences[s.get_seq_id()][1] for s in sampled]
                 indices = [s.get_total_len() for s in sampled]
                 ids = self.sampler.sample(logits, params, indices)
-                # one transfer: the chosen ids and the kernels' status word
-                both = torch.cat([ids, self.runtime.status[:1]])
-                self._tokens_host[:n + 1].copy_(both, non_blocking=True)
+                # two small transfers, one wait: the chosen ids and the kernels' status word
+                self._tokens_host[:n].copy_(ids, non_blocking=True)
+                self._tokens_host[n:n + 1].copy_(self.runtime.status[:1], non_blocking=True)
                 torch.cuda.current_stream().synchronize()
                 host = self._tokens_host[:n + 1].tolist()
                 tokens, status = host[:n], host[n]
