@@ -46,7 +46,7 @@ HOST_SOURCES = ["host/block_manager.cpp", "host/scheduler.cpp", "host/step_pack.
 CORE_KERNEL_SOURCES = ["kernels/elementwise.cu", "kernels/norm.cu", "kernels/rope_kv.cu",
                        "kernels/gemm_f32.cu", "kernels/sampling.cu", "kernels/gemm_skinny.cu", "kernels/gemm_tc.cu"
                        ]
-ATTENTION_SOURCES = ["kernels/attention_generic.cu", "kernels/attention_mma.cu"]
+ATTENTION_SOURCES = ["kernels/attention_generic.cu", "kernels/attention_mma.cu", "kernels/attention_tc.cu"]
 
 _lock = threading.Lock()
 _loaded: dict[str, object] = {}

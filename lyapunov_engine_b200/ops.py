@@ -109,6 +109,8 @@ def attention_lib(head_dim: int):
         _declare(lib, _EXTRA_ATTENTION_SIGNATURES)
         lib.le_attention_mma_available.restype = c_int
         lib.le_attention_mma_available.argtypes = []
+        lib.le_attention_tc_available.restype = c_int
+        lib.le_attention_tc_available.argtypes = [c_int]
         _attention[head_dim] = lib
     return lib
 
@@ -117,6 +119,9 @@ _EXTRA_ATTENTION_SIGNATURES: dict[str, list] = {
     "le_attention_prefill_bf16": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                   c_void_p, c_void_p],
+    "le_attention_prefill_tc_bf16": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_float, c_void_p, c_void_p],
     "le_attention_decode_bf16": [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                  c_int, c_void_p, c_void_p],
@@ -428,6 +433,28 @@ def attention_prefill_bf16(out, q, q_stride, k_cache, v_cache, block_table, cu_q
                                          _ptr(tile_request), _ptr(tile_q0), num_tiles, num_heads, num_kv_heads,
                                          page_size, k_cache.shape[0], int(window or 0), float(scale), _ptr(status),
                                          _stream()), "le_attention_prefill_bf16", lib)
+
+
+def attention_tc_available(head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 prefill attention exists for this head and page size."""
+    return bool(attention_lib(head_dim).le_attention_tc_available(int(page_size)))
+
+
+def attention_prefill_tc_bf16(out, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, tile_request, tile_q0,
+                              num_tiles, num_heads, num_kv_heads, head_dim, page_size, window, scale, status) -> None:
+    """tcgen05 / TMA attention for requests that bring several tokens (head
+    sizes 64 and 128, pages of 8..128 keys); the tiles list 128 query tokens
+    each.  ``q`` is the [T, width] buffer whose rows start with the query heads."""
+    _need_cuda(out, q, k_cache, v_cache, block_table)
+    lib = attention_lib(head_dim)
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[1] == num_heads * head_dim
+    assert k_cache.dtype == torch.bfloat16 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.shape[1:] == (num_kv_heads, page_size, head_dim) and q.dim() == 2 and q.stride(1) == 1
+    _check(lib.le_attention_prefill_tc_bf16(_ptr(out), out.stride(0), _ptr(q), q_stride, q.shape[0], q.shape[1],
+                                            _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+                                            _ptr(cu_q), _ptr(ctx_before), _ptr(tile_request), _ptr(tile_q0), num_tiles,
+                                            num_heads, num_kv_heads, page_size, k_cache.shape[0], int(window or 0),
+                                            float(scale), _ptr(status), _stream()), "le_attention_prefill_tc_bf16", lib)
 
 
 def attention_decode_scratch_floats(head_dim: int, num_requests: int, num_heads: int, num_splits: int) -> int:

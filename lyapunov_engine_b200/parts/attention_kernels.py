@@ -2,13 +2,17 @@
 
 float32: the FP32-pipe kernel for every shape.  bfloat16 with head sizes up to
 128: the tensor-core kernels, one for the requests that bring several tokens
-(portions of prompts) and a split-key one for the requests that bring a single
-decoded token; in a mixed step both run, each on its own requests.  Other
+(portions of prompts: the tcgen05 / TMA kernel for head sizes 64 and 128 and
+pages of 8..128 keys, else the mma.sync kernel) and a split-key one for the
+requests that bring a single decoded token; in a mixed step both run, each on
+its own requests.  Other
 cases (bfloat16 with larger heads) use the generic kernel.  All of them read
 keys and values through the block table and give the same result up to
 rounding.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -18,6 +22,7 @@ GENERIC_TILE = 16
 PREFILL_TILE = 128
 DECODE_KEYS_PER_SPLIT = 256     # a split is worth its launch from about four tiles of keys
 DECODE_MAX_SPLITS = 64
+USE_TC_ATTENTION = os.environ.get("LYAPUNOV_TC_ATTENTION", "1") not in ("0", "")
 RESIDENT_BLOCKS = 2 * 148       # blocks of the decode kernel that are resident at once on a B200
 
 
@@ -54,9 +59,10 @@ def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, window, scale) -> 
     if out.dtype == torch.bfloat16 and ops.attention_mma_available(head_dim):
         req, q0, n_tiles, n_multi = ctx.tiles[PREFILL_TILE]
         if n_multi:
-            ops.attention_prefill_bf16(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0,
-                                       n_multi, num_heads, num_kv_heads, head_dim, kv.page_size, window, scale,
-                                       ctx.status)
+            prefill = (ops.attention_prefill_tc_bf16 if USE_TC_ATTENTION and ops.attention_tc_available(head_dim, kv.page_size)
+                       else ops.attention_prefill_bf16)
+            prefill(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0, n_multi, num_heads,
+                    num_kv_heads, head_dim, kv.page_size, window, scale, ctx.status)
         if ctx.num_decode:
             splits = decode_splits(ctx.num_decode, num_heads, num_kv_heads, ctx.context_bound)
             floats = ops.attention_decode_scratch_floats(head_dim, ctx.num_decode, num_heads, splits)

@@ -106,6 +106,10 @@ MMA_CASES = CASES[:6] + [
     (32, 1, 32, 8, [1, 1, 3], [77, 300, 10], None),                            # 32 query heads on one kv head: two row tiles
     (4, 4, 96, 16, [130], [700], 256),
     (2, 1, 112, 4, [1, 1], [511, 40], 100),
+    (8, 2, 64, 16, [300, 1, 128, 129], [0, 50, 128, 1000], None),               # tcgen05 prefill: several tiles, edges
+    (4, 4, 128, 8, [257, 5], [31, 0], None),
+    (4, 1, 64, 32, [200, 130], [500, 3], 160),
+    (2, 2, 128, 128, [140], [120], None),
 ]
 
 
@@ -121,17 +125,19 @@ def test_tensor_core_kernels(case):
     status = ops.new_status(DEV)
     multi = [b for b, n in enumerate(q_lens) if n > 1]
     single = [b for b, n in enumerate(q_lens) if n == 1]
-    for splits in (1, 3, 16):
+    variants = [(1, ops.attention_prefill_bf16), (3, ops.attention_prefill_bf16), (16, ops.attention_prefill_bf16)]
+    if ops.attention_tc_available(hd, page):
+        variants.append((2, ops.attention_prefill_tc_bf16))      # the tcgen05 kernel for the requests with several tokens
+    for splits, prefill in variants:
         out = torch.full((c["T"], nh * hd), 7.0, dtype=dtype, device=DEV)
         if multi:
             req, q0 = [], []
             for b in multi:
                 for s in range(0, q_lens[b], 128):
                     req.append(b); q0.append(s)
-            ops.attention_prefill_bf16(out, c["q"], c["q"].stride(0), c["k"], c["v"], c["table"], c["cu"], c["ctx"],
-                                       torch.tensor(req, dtype=torch.int32, device=DEV),
-                                       torch.tensor(q0, dtype=torch.int32, device=DEV), len(req), nh, nkv, hd, page,
-                                       window, 1.0 / hd ** 0.5, status)
+            prefill(out, c["q"], c["q"].stride(0), c["k"], c["v"], c["table"], c["cu"], c["ctx"],
+                    torch.tensor(req, dtype=torch.int32, device=DEV), torch.tensor(q0, dtype=torch.int32, device=DEV),
+                    len(req), nh, nkv, hd, page, window, 1.0 / hd ** 0.5, status)
         if single:
             floats = ops.attention_decode_scratch_floats(hd, len(single), nh, splits)
             scratch = torch.full((max(floats, 1),), float("nan"), device=DEV)
