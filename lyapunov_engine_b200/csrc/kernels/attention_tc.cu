@@ -10,11 +10,14 @@
 //   warp 1      tensor core: one thread issues S = Q K^T (128 x 128 x head
 //               size) into one of two score buffers in tensor memory and, when
 //               the probabilities are ready, O += P V (128 x head size x 128);
-//   warps 2..5  softmax: thread r owns query row r.  It reads its 128 scores
-//               from tensor memory, masks what the row may not see, keeps the
-//               running maximum and sum in 32 bits (exp2 with the scale folded
-//               in), writes the probabilities as bfloat16 into shared memory in
-//               the operand layout of the next product, and rescales the
+//   warps 2..9  softmax: two threads share query row r, each with 64 of the
+//               tile's 128 keys.  A thread reads its scores from tensor memory,
+//               masks what the row may not see, agrees with its partner on the
+//               row's maximum, keeps the running maximum and its share of the
+//               sum in 32 bits (exp2 with the scale folded in), writes the
+//               probabilities as bfloat16 into shared memory in the operand
+//               layout of the next product (two buffers, so this overlaps the
+//               product of the tile before), and rescales its half of the
 //               output accumulator in tensor memory when a row's maximum grew.
 // Scores of tile j + 1 are issued before the product of tile j, so the softmax
 // of one tile overlaps the tensor core's work on its neighbours.  At the end
@@ -43,8 +46,9 @@ constexpr int HD = LE_HEAD_DIM;
 constexpr int DB = HD / 64;                 // 64-wide blocks of the head size
 constexpr int BM = 128, BN = 128;           // query rows, keys per tile
 constexpr int STAGES = HD == 64 ? 3 : 2;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;               // producer warp, tensor-core warp, eight softmax warps
 constexpr int Q_BYTES = BM * HD * 2, K_BYTES = BN * HD * 2, V_BYTES = BN * HD * 2, P_BYTES = BM * BN * 2;
+constexpr int P_BUFFERS = HD == 64 ? 2 : 1;   // probabilities double-buffered where shared memory allows
 constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
 constexpr uint32_t TMEM_COLS = 512;         // scores 0..127 and 128..255, output from 256
 constexpr uint32_t O_COL = 256;
@@ -62,14 +66,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   unsigned char *q_smem = smem;
   unsigned char *kv_smem = q_smem + Q_BYTES;
   unsigned char *p_smem = kv_smem + STAGES * STAGE_BYTES;
-  uint64_t *q_full = reinterpret_cast<uint64_t *>(p_smem + P_BYTES);
+  float *pair_max = reinterpret_cast<float *>(p_smem + P_BUFFERS * P_BYTES);   // [2 tile parities][2 halves][BM]
+  float *pair_sum = pair_max + 4 * BM;                                         // [2 halves][BM]
+  uint64_t *q_full = reinterpret_cast<uint64_t *>(pair_sum + 2 * BM);
   uint64_t *kv_full = q_full + 1;            // [STAGES]
   uint64_t *kv_empty = kv_full + STAGES;     // [STAGES]
   uint64_t *s_full = kv_empty + STAGES;      // [2]
   uint64_t *s_free = s_full + 2;             // [2]
   uint64_t *p_full = s_free + 2;
   uint64_t *o_done = p_full + 1;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_done + 1);
+  uint64_t *p_free = o_done + 1;             // [2]
+  uint64_t *pair_bar = p_free + 2;           // [4]: the two warps that share 32 rows meet here
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(pair_bar + 4);
   volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,9 +99,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(s_full + a, 1); mbar_init(s_free + a, 4); }
-    mbar_init(p_full, 4);
+    for (int a = 0; a < 2; ++a) { mbar_init(s_full + a, 1); mbar_init(s_free + a, 8); mbar_init(p_free + a, 1); }
+    mbar_init(p_full, 8);
     mbar_init(o_done, 1);
+    for (int a = 0; a < 4; ++a) mbar_init(pair_bar + a, 64);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -183,43 +192,54 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k) {
           // P: K-major, keys in two 64-wide blocks; V: rows are keys, 16 keys = 2048 bytes, 64-wide dim blocks BN * 128 apart
-          const uint64_t da = smem_desc(p_addr + (k / 4) * (BM * 128) + (k % 4) * 32);
+          const uint64_t da = smem_desc(p_addr + (j % P_BUFFERS) * P_BYTES + (k / 4) * (BM * 128) + (k % 4) * 32);
           const uint64_t db = smem_desc_mn(v_addr + k * 16 * 128, BN * 128);
           tc_mma(tmem_base + O_COL, da, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(kv_empty + j % STAGES);     // the stage's keys and values have been read
+        tc_commit(p_free + (j & 1));          // ... and this tile's probabilities
         tc_commit(o_done);                    // the output accumulator holds tiles 0..j
       }
       if (!ok) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
     }
   } else {
-    // ---- softmax: thread = query row
-    const int quarter = warp & 3;
+    // ---- softmax: threads (quarter, lane) of the two halves share query row r; each takes 64 of the 128 keys
+    const int quarter = warp & 3;               // the tensor-memory lanes this warp may touch
+    const int half = (warp - 2) >> 2;           // which 64 keys of a tile, which half of the output columns
     const int r = quarter * 32 + lane;
     const int p_row = p0 + r;
     const int lo_row = window > 0 ? max(0, p_row - window + 1) : 0;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const float sl2 = scale * LOG2E;
+    constexpr int OC = HD / 2;                  // output columns per thread
     float m_run = -INFINITY, l_run = 0.0f;
     bool ok = true;
+    uint32_t pair_phase = 0;
+    // the two threads of a row exchange a value through shared memory: arrive, then a bounded wait for all 64
+    auto pair_sync = [&]() {
+      mbar_arrive(pair_bar + quarter);
+      const bool met = mbar_wait(pair_bar + quarter, pair_phase, failed);
+      pair_phase ^= 1;
+      return met;
+    };
     for (int j = 0; j < num_tiles; ++j) {
-      const int k0 = k_begin + j * BN;
+      const int k0 = k_begin + j * BN + half * 64;
       ok = mbar_wait(s_full + (j & 1), (j >> 1) & 1, failed);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       tc_fence_after();
-      uint32_t v[4][32];
+      uint32_t v[2][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tc_load32_async(lane_base + (j & 1) * BN + c * 32, v[c]);
+      for (int c = 0; c < 2; ++c) tc_load32_async(lane_base + (j & 1) * BN + half * 64 + c * 32, v[c]);
       tc_wait_loads();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free + (j & 1));          // the tensor core may overwrite this score buffer
-      // mask what this row may not see, find the tile's maximum
-      const bool edge = k0 + BN - 1 > p_row || k0 < lo_row;
+      // mask what this row may not see, find the maximum of this half, then of the row
+      const bool edge = k0 + 63 > p_row || k0 < lo_row;
       float tile_max = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float x = __uint_as_float(v[c][i]);
@@ -230,20 +250,32 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           v[c][i] = __float_as_uint(x);
           tile_max = fmaxf(tile_max, x);
         }
+      float *mine = pair_max + ((j & 1) * 2 + half) * BM, *theirs = pair_max + ((j & 1) * 2 + (half ^ 1)) * BM;
+      mine[r] = tile_max;
+      ok = pair_sync();
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      tile_max = fmaxf(tile_max, theirs[r]);
       const float m_new = fmaxf(m_run, tile_max);
       const float alpha = (m_new == -INFINITY) ? 1.0f : exp2f((m_run - m_new) * sl2);
       const float neg_m = (m_new == -INFINITY) ? 0.0f : -m_new * sl2;
       m_run = m_new;
-      if (j > 0) {
-        // the product of the tile before has read the probabilities and updated the output
+      if (P_BUFFERS == 2) {
+        if (j >= 2) {                            // the product two tiles back has read this buffer
+          ok = mbar_wait(p_free + (j & 1), ((j >> 1) - 1) & 1, failed);
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
+        }
+      } else if (j > 0) {                        // one buffer: the product of the tile before must be through
         ok = mbar_wait(o_done, (j - 1) & 1, failed);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
         tc_fence_after();
       }
+      unsigned char *p_tile = p_smem + (j % P_BUFFERS) * P_BYTES + half * (BM * 128) + r * 128;
       float sum = 0.0f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
           float p[8];
@@ -256,21 +288,26 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&packed);
 #pragma unroll
           for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
-          const int chunk = c * 4 + i / 8;                   // 16-byte chunk 0..15 of the row's 128 keys
-          unsigned char *dst = p_smem + (chunk >> 3) * (BM * 128) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
-          *reinterpret_cast<uint4 *>(dst) = packed;
+          const int chunk = c * 4 + i / 8;                   // 16-byte chunk 0..7 of this half's 64 keys
+          *reinterpret_cast<uint4 *>(p_tile + ((chunk ^ (r & 7)) << 4)) = packed;
         }
       }
       l_run = l_run * alpha + sum;
-      // rescale the output accumulator when some row of this warp moved its maximum
+      if (P_BUFFERS == 2 && j > 0) {             // the output accumulator holds every tile before this one
+        ok = mbar_wait(o_done, (j - 1) & 1, failed);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        tc_fence_after();
+      }
+      // rescale this thread's half of the output accumulator when some row of the warp moved its maximum
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < OC / 32; ++c) {
           uint32_t o[32];
-          tc_load32(lane_base + O_COL + c * 32, o);
+          tc_load32(lane_base + O_COL + half * OC + c * 32, o);
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tc_store32(lane_base + O_COL + c * 32, o);
+          tc_store32(lane_base + O_COL + half * OC + c * 32, o);
         }
         tc_wait_stores();
       }
@@ -287,12 +324,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (lane == 0) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
     } else {
       tc_fence_after();
-      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-      bf16 *dst = out + (tok0 + r) * out_stride + head * HD;
+      pair_sum[half * BM + r] = l_run;
+      if (!pair_sync()) atomicOr(status, LE_STATUS_WAIT_TIMEOUT);   // the row is then stored with its own share only
+      const float l = l_run + pair_sum[(half ^ 1) * BM + r];
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      bf16 *dst = out + (tok0 + r) * out_stride + head * HD + half * OC;
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < OC / 32; ++c) {
         uint32_t o[32];
-        tc_load32(lane_base + O_COL + c * 32, o);
+        tc_load32(lane_base + O_COL + half * OC + c * 32, o);
         if (r < rows) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
@@ -352,7 +392,7 @@ LE_API int le_attention_prefill_tc_bf16(void *out, int64_t out_stride, const voi
   if (rc != 0) return rc;
   rc = tensor_map(&map_v, v_cache, cache_rows, HD, HD, page_size);
   if (rc != 0) return rc;
-  const size_t smem = Q_BYTES + STAGES * STAGE_BYTES + P_BYTES + 1024 + 256;
+  const size_t smem = Q_BYTES + STAGES * STAGE_BYTES + P_BUFFERS * P_BYTES + 6 * BM * sizeof(float) + 1024 + 256;
   cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return le::invalid("le_attention_prefill_tc_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   dim3 grid(num_tiles, num_heads);
