@@ -342,7 +342,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
         const float m_new = fmaxf(m_run[r], tile_max[r]);
-        alpha[r] = (m_new == -INFINITY) ? 1.0f : exp2f((m_run[r] - m_new) * sl2);
+        alpha[r] = (m_new == -INFINITY) ? 1.0f : le::fast_exp2((m_run[r] - m_new) * sl2);
         neg_m[r] = (m_new == -INFINITY) ? 0.0f : -m_new * sl2;
         m_run[r] = m_new;
         l_run[r] *= alpha[r];
@@ -351,7 +351,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
       for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p = exp2f(fmaf(s[nt][e], sl2, neg_m[e >> 1]));   // exp2(-inf) = 0 for masked keys
+          const float p = le::fast_exp2(fmaf(s[nt][e], sl2, neg_m[e >> 1]));   // exp2(-inf) = 0 for masked keys
           s[nt][e] = p;
           l_run[e >> 1] += p;
         }
@@ -511,13 +511,13 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
       tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
       tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
       const float m_new = fmaxf(m_run[r], tile_max);
-      alpha[r] = (m_new == -INFINITY) ? 1.0f : exp2f((m_run[r] - m_new) * sl2);
+      alpha[r] = (m_new == -INFINITY) ? 1.0f : le::fast_exp2((m_run[r] - m_new) * sl2);
       const float neg_m = (m_new == -INFINITY) ? 0.0f : -m_new * sl2;
       m_run[r] = m_new;
       float sum = 0.0f;
 #pragma unroll
       for (int nt = 0; nt < DC_TILE / 8; ++nt) {
-        const float p0 = exp2f(fmaf(s[nt][2 * r], sl2, neg_m)), p1 = exp2f(fmaf(s[nt][2 * r + 1], sl2, neg_m));
+        const float p0 = le::fast_exp2(fmaf(s[nt][2 * r], sl2, neg_m)), p1 = le::fast_exp2(fmaf(s[nt][2 * r + 1], sl2, neg_m));
         s[nt][2 * r] = p0;
         s[nt][2 * r + 1] = p1;
         sum += p0 + p1;
@@ -575,7 +575,7 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
 #pragma unroll
     for (int w = 0; w < DC_WARPS; ++w) {
       const float mw = sm_m[w * 16 + row];
-      const float f = (mw == -INFINITY) ? 0.0f : exp2f((mw - m) * sl2);
+      const float f = (mw == -INFINITY) ? 0.0f : le::fast_exp2((mw - m) * sl2);
       acc += f * sm_o[(w * 16 + row) * HD + d];
       l += f * sm_l[w * 16 + row];
     }
@@ -610,7 +610,7 @@ __global__ void attention_merge_kernel(bf16 *__restrict__ out, int64_t out_strid
     for (int s = 0; s < num_splits; ++s) {
       const float ms = part_ml[(base + s) * 2];
       if (ms == -INFINITY) continue;
-      const float f = exp2f(ms - m);
+      const float f = le::fast_exp2(ms - m);
       acc += f * part_o[(base + s) * HD + d];
       l += f * part_ml[(base + s) * 2 + 1];
     }

@@ -5,23 +5,28 @@
 // One block owns 128 query tokens of one head and walks the keys in tiles of
 // 128.  Roles:
 //   warp 0      producer: its lanes look the tile's pages up in the block table
-//               and each issues the TMA copies of one page's keys and values
-//               (128-byte swizzle) into a ring of stages;
+//               and each issues the TMA copies of one page's keys or values
+//               (128-byte swizzle) into a ring of key stages and one of value
+//               stages;
 //   warp 1      tensor core: one thread issues S = Q K^T (128 x 128 x head
 //               size) into one of two score buffers in tensor memory and, when
 //               the probabilities are ready, O += P V (128 x head size x 128);
-//   warps 2..9  softmax: two threads share query row r, each with 64 of the
-//               tile's 128 keys.  A thread reads its scores from tensor memory,
-//               masks what the row may not see, agrees with its partner on the
-//               row's maximum, keeps the running maximum and its share of the
-//               sum in 32 bits (exp2 with the scale folded in), writes the
-//               probabilities as bfloat16 into shared memory in the operand
-//               layout of the next product (two buffers, so this overlaps the
-//               product of the tile before), and rescales its half of the
-//               output accumulator in tensor memory when a row's maximum grew.
-// Scores of tile j + 1 are issued before the product of tile j, so the softmax
-// of one tile overlaps the tensor core's work on its neighbours.  At the end
-// the softmax threads normalise their rows and store them.
+//   warps 2..9  softmax, in two groups of four warps.  Group g takes the tiles
+//               j = g, g + 2, ... and keeps a running maximum, a sum and an
+//               output accumulator of its own for them, so the two groups never
+//               wait for each other: while one computes exponentials the other
+//               waits for its scores.  Thread (quarter, lane) of a group owns
+//               query row r with all 128 keys of the tile: it reads the scores
+//               from tensor memory (once for the maximum, once more for the
+//               exponentials), masks what the row may not see, and writes the
+//               probabilities as bfloat16 into the group's buffer in shared
+//               memory in the operand layout of the next product.
+// The running maximum only moves when the tile's maximum exceeds it by more
+// than 2^8 in the exponent; until then probabilities up to 256 go into the
+// product and the sum (both 32-bit accumulations), which the final division
+// takes out again.  The accumulator in tensor memory is therefore rescaled
+// rarely.  At the end the two groups' partial results are merged like the
+// splits of a decode: each thread combines half of the columns of its row.
 //
 // Every wait on an mbarrier is bounded in time; a block that gives up sets the
 // status word, lets copies in flight land, frees its tensor memory and returns.
@@ -45,14 +50,23 @@ using bf16 = __nv_bfloat16;
 constexpr int HD = LE_HEAD_DIM;
 constexpr int DB = HD / 64;                 // 64-wide blocks of the head size
 constexpr int BM = 128, BN = 128;           // query rows, keys per tile
-constexpr int STAGES = HD == 64 ? 3 : 2;
-constexpr int THREADS = 320;               // producer warp, tensor-core warp, eight softmax warps
+constexpr int KS = HD == 64 ? 4 : 2;        // key stages
+constexpr int VS = HD == 64 ? 4 : 2;        // value stages
+constexpr int THREADS = 320;                // producer warp, tensor-core warp, two softmax groups of four warps
 constexpr int Q_BYTES = BM * HD * 2, K_BYTES = BN * HD * 2, V_BYTES = BN * HD * 2, P_BYTES = BM * BN * 2;
-constexpr int P_BUFFERS = HD == 64 ? 2 : 1;   // probabilities double-buffered where shared memory allows
-constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
-constexpr uint32_t TMEM_COLS = 512;         // scores 0..127 and 128..255, output from 256
+constexpr uint32_t TMEM_COLS = 512;         // scores at 0 and 128, the groups' outputs at 256 and 256 + head size
 constexpr uint32_t O_COL = 256;
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr float MAX_SLACK = 8.0f;           // the running maximum may lag the true one by this much (base-2 exponent)
+
+// 32 scores of a row from tensor memory, masked where the row may not see the key.
+__device__ __forceinline__ void mask32(uint32_t (&v)[32], int first_key, int p_row, int lo_row) {
+  if (first_key + 31 > p_row || first_key < lo_row) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (first_key + i > p_row || first_key + i < lo_row) v[i] = 0xff800000u;   // -inf
+  }
+}
 
 __global__ void __launch_bounds__(THREADS)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -64,20 +78,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   unsigned char *q_smem = smem;
-  unsigned char *kv_smem = q_smem + Q_BYTES;
-  unsigned char *p_smem = kv_smem + STAGES * STAGE_BYTES;
-  float *pair_max = reinterpret_cast<float *>(p_smem + P_BUFFERS * P_BYTES);   // [2 tile parities][2 halves][BM]
-  float *pair_sum = pair_max + 4 * BM;                                         // [2 halves][BM]
-  uint64_t *q_full = reinterpret_cast<uint64_t *>(pair_sum + 2 * BM);
-  uint64_t *kv_full = q_full + 1;            // [STAGES]
-  uint64_t *kv_empty = kv_full + STAGES;     // [STAGES]
-  uint64_t *s_full = kv_empty + STAGES;      // [2]
-  uint64_t *s_free = s_full + 2;             // [2]
-  uint64_t *p_full = s_free + 2;
-  uint64_t *o_done = p_full + 1;
-  uint64_t *p_free = o_done + 1;             // [2]
-  uint64_t *pair_bar = p_free + 2;           // [4]: the two warps that share 32 rows meet here
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(pair_bar + 4);
+  unsigned char *k_smem = q_smem + Q_BYTES;
+  unsigned char *v_smem = k_smem + KS * K_BYTES;
+  unsigned char *p_smem = v_smem + VS * V_BYTES;                               // one buffer per softmax group
+  uint64_t *q_full = reinterpret_cast<uint64_t *>(p_smem + 2 * P_BYTES);
+  uint64_t *k_full = q_full + 1;             // [KS]
+  uint64_t *k_empty = k_full + KS;           // [KS]
+  uint64_t *v_full = k_empty + KS;           // [VS]
+  uint64_t *v_empty = v_full + VS;           // [VS]
+  uint64_t *s_full = v_empty + VS;           // [2]: scores of the group's next tile are in tensor memory
+  uint64_t *p_full = s_full + 2;             // [2]: the group's probabilities are in shared memory
+  uint64_t *o_done = p_full + 2;             // [2]: the group's accumulator holds all its tiles so far
+  uint64_t *merge_bar = o_done + 2;          // both groups have their final sums
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(merge_bar + 1);
   volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -98,11 +111,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(s_full + a, 1); mbar_init(s_free + a, 8); mbar_init(p_free + a, 1); }
-    mbar_init(p_full, 8);
-    mbar_init(o_done, 1);
-    for (int a = 0; a < 4; ++a) mbar_init(pair_bar + a, 64);
+    for (int s = 0; s < KS; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
+    for (int s = 0; s < VS; ++s) { mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1); }
+    for (int g = 0; g < 2; ++g) { mbar_init(s_full + g, 1); mbar_init(p_full + g, 4); mbar_init(o_done + g, 1); }
+    mbar_init(merge_bar, 8);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -116,22 +128,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---- producer
+    // ---- producer: keys run one tile ahead of values, the order in which the tensor core wants them
     if (lane == 0) {
       mbar_expect_tx(q_full, Q_BYTES);
       for (int d = 0; d < DB; ++d) tma_load_2d(q_smem + d * BM * 128, &map_q, q_full, head * HD + d * 64, tok0);
     }
     const int pages_per_tile = BN >> page_shift;            // at most 16: one lane per page
-    int issued = 0;
-    bool ok = true;
-    for (int j = 0; j < num_tiles && ok; ++j, ++issued) {
-      const int s = j % STAGES;
+    int keys_issued = 0, values_issued = 0;
+    // one tile's keys or values: lane 0 waits for the stage and announces the bytes, then one lane per page copies
+    auto load_tile = [&](int j, const CUtensorMap *map, unsigned char *ring, int stages, uint64_t *full, uint64_t *empty) {
+      const int s = j % stages;
+      bool ok = true;
       if (lane == 0) {
-        ok = !*failed && mbar_wait(kv_empty + s, ((j / STAGES) & 1) ^ 1, failed);
-        if (ok) mbar_expect_tx(kv_full + s, STAGE_BYTES);
+        ok = mbar_wait(empty + s, ((j / stages) & 1) ^ 1, failed);
+        if (ok) mbar_expect_tx(full + s, K_BYTES);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
+      if (!ok) return false;
       if (lane < pages_per_tile) {
         const int slot = ((k_begin + j * BN) >> page_shift) + lane;
         int page = slot < max_blocks ? table[slot] : num_pages - 1;
@@ -140,19 +153,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           page = num_pages - 1;                              // the page nobody owns: finite values, masked anyway
         }
         const int row = (page * num_kv_heads + kvh) * page_size;
-        unsigned char *k_dst = kv_smem + s * STAGE_BYTES + lane * page_size * 128;
-        unsigned char *v_dst = k_dst + K_BYTES;
-        for (int d = 0; d < DB; ++d) {
-          tma_load_2d(k_dst + d * BN * 128, &map_k, kv_full + s, d * 64, row);
-          tma_load_2d(v_dst + d * BN * 128, &map_v, kv_full + s, d * 64, row);
-        }
+        unsigned char *dst = ring + s * K_BYTES + lane * page_size * 128;
+        for (int d = 0; d < DB; ++d) tma_load_2d(dst + d * BN * 128, map, full + s, d * 64, row);
       }
+      return true;
+    };
+    bool ok = load_tile(0, &map_k, k_smem, KS, k_full, k_empty);
+    if (ok) keys_issued = 1;
+    for (int j = 0; j < num_tiles && ok; ++j) {
+      if (j + 1 < num_tiles) {
+        ok = load_tile(j + 1, &map_k, k_smem, KS, k_full, k_empty);
+        if (!ok) break;
+        ++keys_issued;
+      }
+      ok = load_tile(j, &map_v, v_smem, VS, v_full, v_empty);
+      if (ok) ++values_issued;
     }
     if (!ok && lane == 0) {
       *failed = 1;
       atomicOr(status, LE_STATUS_WAIT_TIMEOUT);
-      volatile int never = 0;
-      for (int j = max(0, issued - STAGES); j < issued; ++j) mbar_wait(kv_full + j % STAGES, (j / STAGES) & 1, &never);
+      volatile int never = 0;                                // copies in flight must land before the block may end
+      for (int j = max(0, keys_issued - KS); j < keys_issued; ++j) mbar_wait(k_full + j % KS, (j / KS) & 1, &never);
+      for (int j = max(0, values_issued - VS); j < values_issued; ++j) mbar_wait(v_full + j % VS, (j / VS) & 1, &never);
     }
   } else if (warp == 1) {
     // ---- tensor-core issue
@@ -161,8 +183,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
       constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(HD >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
       const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
+      // scores of tile j into the buffer of group j & 1; frees the key stage when they are through
       auto issue_scores = [&](int j) {
-        const uint32_t k_addr = smem_u32(kv_smem + (j % STAGES) * STAGE_BYTES);
+        if (!mbar_wait(k_full + j % KS, (j / KS) & 1, failed)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(k_smem + (j % KS) * K_BYTES);
         const uint32_t tmem_s = tmem_base + (j & 1) * BN;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
@@ -171,176 +196,169 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           tc_mma(tmem_s, smem_desc(q_addr + off), smem_desc(k_addr + off), idesc_s, k > 0 ? 1u : 0u);
         }
         tc_commit(s_full + (j & 1));
+        tc_commit(k_empty + j % KS);
+        return true;
       };
-      bool ok = mbar_wait(q_full, 0, failed) && mbar_wait(kv_full, 0, failed);
-      if (ok) {
-        tc_fence_after();
-        issue_scores(0);
-      }
+      bool ok = mbar_wait(q_full, 0, failed) && issue_scores(0);
+      if (ok && num_tiles > 1) ok = issue_scores(1);
       for (int j = 0; j < num_tiles && ok; ++j) {
-        if (j + 1 < num_tiles) {
-          ok = mbar_wait(kv_full + (j + 1) % STAGES, ((j + 1) / STAGES) & 1, failed);
-          if (ok && j + 1 >= 2) ok = mbar_wait(s_free + ((j + 1) & 1), (((j + 1) >> 1) - 1) & 1, failed);
-          if (!ok) break;
-          tc_fence_after();
-          issue_scores(j + 1);
-        }
-        ok = mbar_wait(p_full, j & 1, failed);
+        const int g = j & 1;
+        ok = mbar_wait(p_full + g, (j >> 1) & 1, failed) && mbar_wait(v_full + j % VS, (j / VS) & 1, failed);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(kv_smem + (j % STAGES) * STAGE_BYTES + K_BYTES);
+        const uint32_t v_addr = smem_u32(v_smem + (j % VS) * V_BYTES);
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k) {
           // P: K-major, keys in two 64-wide blocks; V: rows are keys, 16 keys = 2048 bytes, 64-wide dim blocks BN * 128 apart
-          const uint64_t da = smem_desc(p_addr + (j % P_BUFFERS) * P_BYTES + (k / 4) * (BM * 128) + (k % 4) * 32);
+          const uint64_t da = smem_desc(p_addr + g * P_BYTES + (k / 4) * (BM * 128) + (k % 4) * 32);
           const uint64_t db = smem_desc_mn(v_addr + k * 16 * 128, BN * 128);
-          tc_mma(tmem_base + O_COL, da, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+          tc_mma(tmem_base + O_COL + g * HD, da, db, idesc_o, (j >= 2 || k > 0) ? 1u : 0u);
         }
-        tc_commit(kv_empty + j % STAGES);     // the stage's keys and values have been read
-        tc_commit(p_free + (j & 1));          // ... and this tile's probabilities
-        tc_commit(o_done);                    // the output accumulator holds tiles 0..j
+        tc_commit(v_empty + j % VS);          // the stage's values have been read
+        tc_commit(o_done + g);                // the group's accumulator holds its tiles up to j; its probabilities are free
+        // the group has read the scores of tile j (it said so with its probabilities): the buffer takes tile j + 2
+        if (j + 2 < num_tiles) ok = issue_scores(j + 2);
       }
       if (!ok) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
     }
   } else {
-    // ---- softmax: threads (quarter, lane) of the two halves share query row r; each takes 64 of the 128 keys
+    // ---- softmax: thread (quarter, lane) of group g owns query row r for the tiles g, g + 2, ...
     const int quarter = warp & 3;               // the tensor-memory lanes this warp may touch
-    const int half = (warp - 2) >> 2;           // which 64 keys of a tile, which half of the output columns
+    const int g = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const int p_row = p0 + r;
     const int lo_row = window > 0 ? max(0, p_row - window + 1) : 0;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t s_col = lane_base + g * BN, o_col = lane_base + O_COL + g * HD;
     const float sl2 = scale * LOG2E;
-    constexpr int OC = HD / 2;                  // output columns per thread
-    float m_run = -INFINITY, l_run = 0.0f;
+    const float2 sl2_2 = make_float2(sl2, sl2);
+    unsigned char *p_row_smem = p_smem + g * P_BYTES + r * 128;
+    const uint32_t swz = (r & 7) << 4;
+    float m_run = -INFINITY, l_run = 0.0f;      // m_run in exponent units (score * scale * log2 e)
     bool ok = true;
-    uint32_t pair_phase = 0;
-    // the two threads of a row exchange a value through shared memory: arrive, then a bounded wait for all 64
-    auto pair_sync = [&]() {
-      mbar_arrive(pair_bar + quarter);
-      const bool met = mbar_wait(pair_bar + quarter, pair_phase, failed);
-      pair_phase ^= 1;
-      return met;
-    };
-    for (int j = 0; j < num_tiles; ++j) {
-      const int k0 = k_begin + j * BN + half * 64;
-      ok = mbar_wait(s_full + (j & 1), (j >> 1) & 1, failed);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
+    int t = 0;                                  // how many tiles this group has done
+    for (int j = g; j < num_tiles; j += 2, ++t) {
+      const int k0 = k_begin + j * BN;
+      ok = mbar_wait(s_full + g, t & 1, failed) && ok;
       tc_fence_after();
-      uint32_t v[2][32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) tc_load32_async(lane_base + (j & 1) * BN + half * 64 + c * 32, v[c]);
-      tc_wait_loads();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_free + (j & 1));          // the tensor core may overwrite this score buffer
-      // mask what this row may not see, find the maximum of this half, then of the row
-      const bool edge = k0 + 63 > p_row || k0 < lo_row;
+      // first pass over the scores: the row's maximum
       float tile_max = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+      for (int h = 0; h < 2; ++h) {
+        uint32_t v[2][32];
+        tc_load32_async(s_col + h * 64, v[0]);
+        tc_load32_async(s_col + h * 64 + 32, v[1]);
+        tc_wait_loads();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[c][i]);
-          if (edge) {
-            const int pos = k0 + c * 32 + i;
-            if (pos > p_row || pos < lo_row) x = -INFINITY;
-          }
-          v[c][i] = __float_as_uint(x);
-          tile_max = fmaxf(tile_max, x);
+        for (int c = 0; c < 2; ++c) {
+          mask32(v[c], k0 + h * 64 + c * 32, p_row, lo_row);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, __uint_as_float(v[c][i]));
         }
-      float *mine = pair_max + ((j & 1) * 2 + half) * BM, *theirs = pair_max + ((j & 1) * 2 + (half ^ 1)) * BM;
-      mine[r] = tile_max;
-      ok = pair_sync();
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      tile_max = fmaxf(tile_max, theirs[r]);
-      const float m_new = fmaxf(m_run, tile_max);
-      const float alpha = (m_new == -INFINITY) ? 1.0f : exp2f((m_run - m_new) * sl2);
-      const float neg_m = (m_new == -INFINITY) ? 0.0f : -m_new * sl2;
-      m_run = m_new;
-      if (P_BUFFERS == 2) {
-        if (j >= 2) {                            // the product two tiles back has read this buffer
-          ok = mbar_wait(p_free + (j & 1), ((j >> 1) - 1) & 1, failed);
-          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-          if (!ok) break;
-        }
-      } else if (j > 0) {                        // one buffer: the product of the tile before must be through
-        ok = mbar_wait(o_done, (j - 1) & 1, failed);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
+      }
+      tile_max *= sl2;
+      float alpha = 1.0f;
+      if (tile_max > m_run + MAX_SLACK) {        // also the first keys a row sees (m_run is -inf until then)
+        alpha = le::fast_exp2(m_run - tile_max);
+        m_run = tile_max;
+      }
+      const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;
+      const float2 neg_m2 = make_float2(neg_m, neg_m);
+      if (t > 0) {                               // the product of this group's tile before has read the probabilities
+        ok = mbar_wait(o_done + g, (t - 1) & 1, failed) && ok;
         tc_fence_after();
-      }
-      unsigned char *p_tile = p_smem + (j % P_BUFFERS) * P_BYTES + half * (BM * 128) + r * 128;
-      float sum = 0.0f;
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tc_load32(o_col + c * 32, o);
 #pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          float p[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            p[e] = exp2f(fmaf(__uint_as_float(v[c][i + e]), sl2, neg_m));
-            sum += p[e];
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tc_store32(o_col + c * 32, o);
           }
-          uint4 packed;
-          __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&packed);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
-          const int chunk = c * 4 + i / 8;                   // 16-byte chunk 0..7 of this half's 64 keys
-          *reinterpret_cast<uint4 *>(p_tile + ((chunk ^ (r & 7)) << 4)) = packed;
+          tc_wait_stores();
         }
       }
-      l_run = l_run * alpha + sum;
-      if (P_BUFFERS == 2 && j > 0) {             // the output accumulator holds every tile before this one
-        ok = mbar_wait(o_done, (j - 1) & 1, failed);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-        tc_fence_after();
-      }
-      // rescale this thread's half of the output accumulator when some row of the warp moved its maximum
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+      // second pass: exponentials, the row's sum, probabilities into shared memory
+      float2 sum2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-        for (int c = 0; c < OC / 32; ++c) {
-          uint32_t o[32];
-          tc_load32(lane_base + O_COL + half * OC + c * 32, o);
+      for (int h = 0; h < 2; ++h) {
+        uint32_t v[2][32];
+        tc_load32_async(s_col + h * 64, v[0]);
+        tc_load32_async(s_col + h * 64 + 32, v[1]);
+        tc_wait_loads();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tc_store32(lane_base + O_COL + half * OC + c * 32, o);
+        for (int c = 0; c < 2; ++c) {
+          mask32(v[c], k0 + h * 64 + c * 32, p_row, lo_row);
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 packed;
+            __nv_bfloat162 *pk = reinterpret_cast<__nv_bfloat162 *>(&packed);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float2 x = __ffma2_rn(make_float2(__uint_as_float(v[c][i + 2 * e]), __uint_as_float(v[c][i + 2 * e + 1])), sl2_2, neg_m2);
+              x.x = le::fast_exp2(x.x);
+              x.y = le::fast_exp2(x.y);
+              sum2 = __fadd2_rn(sum2, x);
+              pk[e] = __floats2bfloat162_rn(x.x, x.y);
+            }
+            // keys h * 64 ...: 64-key block h of the operand; 16-byte chunk c * 4 + i / 8 of the row, swizzled
+            *reinterpret_cast<uint4 *>(p_row_smem + h * (BM * 128) + ((static_cast<uint32_t>(c * 4 + i / 8) << 4) ^ swz)) = packed;
+          }
         }
-        tc_wait_stores();
       }
+      l_run = l_run * alpha + (sum2.x + sum2.y);
       fence_async_proxy();
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+      if (lane == 0) mbar_arrive(p_full + g);
     }
-    if (ok) {
-      ok = mbar_wait(o_done, (num_tiles - 1) & 1, failed);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-    }
+    if (ok && t > 0) ok = mbar_wait(o_done + g, (t - 1) & 1, failed);
+    // ---- merge the two groups: each thread takes half of the columns of its row
+    // (the groups' final maxima and sums travel through their probability buffers, which are free by now)
+    float *mine = reinterpret_cast<float *>(p_smem + g * P_BYTES), *theirs = reinterpret_cast<float *>(p_smem + (g ^ 1) * P_BYTES);
+    mine[r] = m_run;
+    mine[BM + r] = l_run;
+    tc_fence_before();
+    ok = __all_sync(0xffffffffu, ok);
+    if (lane == 0) mbar_arrive(merge_bar);
+    if (ok) ok = mbar_wait(merge_bar, 0, failed);
+    ok = __all_sync(0xffffffffu, ok);
     if (!ok) {
       if (lane == 0) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
     } else {
       tc_fence_after();
-      pair_sum[half * BM + r] = l_run;
-      if (!pair_sync()) atomicOr(status, LE_STATUS_WAIT_TIMEOUT);   // the row is then stored with its own share only
-      const float l = l_run + pair_sum[(half ^ 1) * BM + r];
+      const float m0 = g == 0 ? m_run : theirs[r], m1 = g == 0 ? theirs[r] : m_run;
+      const float l0 = g == 0 ? l_run : theirs[BM + r], l1 = g == 0 ? theirs[BM + r] : l_run;
+      const float m = fmaxf(m0, m1);
+      const float w0 = m0 == -INFINITY ? 0.0f : le::fast_exp2(m0 - m);
+      const float w1 = m1 == -INFINITY ? 0.0f : le::fast_exp2(m1 - m);
+      const float l = l0 * w0 + l1 * w1;
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      bf16 *dst = out + (tok0 + r) * out_stride + head * HD + half * OC;
+      const float f0 = w0 * inv, f1 = w1 * inv;
+      constexpr int OC = HD / 2;                 // output columns per thread
+      bf16 *dst = out + (tok0 + r) * out_stride + head * HD + g * OC;
+      const uint32_t col = lane_base + O_COL + g * OC;
 #pragma unroll
       for (int c = 0; c < OC / 32; ++c) {
-        uint32_t o[32];
-        tc_load32(lane_base + O_COL + half * OC + c * 32, o);
+        uint32_t a[32], bb[32];
+        tc_load32_async(col + c * 32, a);
+        if (num_tiles > 1) tc_load32_async(col + HD + c * 32, bb);     // the second group had no tile otherwise
+        tc_wait_loads();
         if (r < rows) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 packed;
-            __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&packed);
+            __nv_bfloat162 *pk = reinterpret_cast<__nv_bfloat162 *>(&packed);
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              h[e] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * e]) * inv, __uint_as_float(o[i + 2 * e + 1]) * inv);
+            for (int e = 0; e < 4; ++e) {
+              float x = __uint_as_float(a[i + 2 * e]) * f0, y = __uint_as_float(a[i + 2 * e + 1]) * f0;
+              if (num_tiles > 1) {
+                x = fmaf(__uint_as_float(bb[i + 2 * e]), f1, x);
+                y = fmaf(__uint_as_float(bb[i + 2 * e + 1]), f1, y);
+              }
+              pk[e] = __floats2bfloat162_rn(x, y);
+            }
             *reinterpret_cast<uint4 *>(dst + c * 32 + i) = packed;
           }
         }
@@ -392,7 +410,7 @@ LE_API int le_attention_prefill_tc_bf16(void *out, int64_t out_stride, const voi
   if (rc != 0) return rc;
   rc = tensor_map(&map_v, v_cache, cache_rows, HD, HD, page_size);
   if (rc != 0) return rc;
-  const size_t smem = Q_BYTES + STAGES * STAGE_BYTES + P_BUFFERS * P_BYTES + 6 * BM * sizeof(float) + 1024 + 256;
+  const size_t smem = Q_BYTES + KS * K_BYTES + VS * V_BYTES + 2 * P_BYTES + 1024 + 256;   // 1024 to align, 256 for the barriers
   cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return le::invalid("le_attention_prefill_tc_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   dim3 grid(num_tiles, num_heads);

@@ -28,11 +28,13 @@ __device__ __forceinline__ unsigned long long now_ns() {
   return t;
 }
 // Bounded wait for the phase with the given parity.  False when the time limit
-// ran out or another role of the block has already given up (`failed`).
+// ran out (the waiter then raises `failed` itself) or another role of the block
+// has already given up.  try_wait suspends the thread for a while by itself, so
+// the flag and the clock are looked at only now and then.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *failed) {
   const uint32_t addr = smem_u32(bar);
   unsigned long long start = 0;
-  for (uint32_t i = 0;; ++i) {
+  for (uint32_t i = 1;; ++i) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -40,11 +42,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
     if (done) return true;
-    if (*failed) return false;
-    if ((i & 63) == 63) {
-      const unsigned long long t = now_ns();
-      if (start == 0) start = t;
-      else if (t - start > WAIT_LIMIT_NS) return false;
+    if ((i & 15) == 0) {
+      if (*failed) return false;
+      if ((i & 255) == 0) {
+        const unsigned long long t = now_ns();
+        if (start == 0) start = t;
+        else if (t - start > WAIT_LIMIT_NS) { *failed = 1; return false; }
+      }
     }
   }
 }
