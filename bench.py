@@ -216,8 +216,8 @@ def run_ours(args):
         # that every kernel shows as its own launch.
         runner.use_cuda_graphs = not args.no_cuda_graphs
         if args.only == "decode":
-            ms, _, _ = timed_decode(args.batch, args.steps, args.warmup, CONTEXT)
-            print(json.dumps({"only": "decode", "batch": args.batch, "context": CONTEXT, "ms_per_step": round(ms, 4),
+            ms, _, _ = timed_decode(args.batch, args.steps, args.warmup, args.context or CONTEXT)
+            print(json.dumps({"only": "decode", "batch": args.batch, "context": args.context or CONTEXT, "ms_per_step": round(ms, 4),
                               "layers": cfg["num_hidden_layers"], "cuda_graph": runner.use_cuda_graphs}))
         else:
             ms = timed_prefill(PREFILL_TOKENS, args.steps, args.warmup)
@@ -432,6 +432,7 @@ def main():
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     p.add_argument("--only", choices=["decode", "prefill"], default=None, help="run one kind of step and exit (for profilers)")
     p.add_argument("--batch", type=int, default=8, help="batch of --only decode")
+    p.add_argument("--context", type=int, default=0, help="with --only decode: the context the last step ends at")
     p.add_argument("--no-cuda-graphs", action="store_true", help="with --only decode: launch every kernel by itself")
     args = p.parse_args()
     if args.gpus != 1:

@@ -17,8 +17,7 @@
 //               wait for each other: while one computes exponentials the other
 //               waits for its scores.  Thread (quarter, lane) of a group owns
 //               query row r with all 128 keys of the tile: it reads the scores
-//               from tensor memory (once for the maximum, once more for the
-//               exponentials), masks what the row may not see, and writes the
+//               from tensor memory, masks what the row may not see, and writes the
 //               probabilities as bfloat16 into the group's buffer in shared
 //               memory in the operand layout of the next product.
 // The running maximum only moves when the tile's maximum exceeds it by more
@@ -68,7 +67,7 @@ __device__ __forceinline__ void mask32(uint32_t (&v)[32], int first_key, int p_r
   }
 }
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, bf16 *__restrict__ out, int64_t out_stride,
                     const int32_t *__restrict__ block_table, int max_blocks, const int32_t *__restrict__ cu_q,
@@ -241,20 +240,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int k0 = k_begin + j * BN;
       ok = mbar_wait(s_full + g, t & 1, failed) && ok;
       tc_fence_after();
-      // first pass over the scores: the row's maximum
+      // the row's 128 scores stay in registers from here to the exponentials
+      uint32_t v[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc_load32_async(s_col + c * 32, v[c]);
+      tc_wait_loads();
       float tile_max = -INFINITY;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t v[2][32];
-        tc_load32_async(s_col + h * 64, v[0]);
-        tc_load32_async(s_col + h * 64 + 32, v[1]);
-        tc_wait_loads();
+      for (int c = 0; c < 4; ++c) {
+        mask32(v[c], k0 + c * 32, p_row, lo_row);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          mask32(v[c], k0 + h * 64 + c * 32, p_row, lo_row);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, __uint_as_float(v[c][i]));
-        }
+        for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, __uint_as_float(v[c][i]));
       }
       tile_max *= sl2;
       float alpha = 1.0f;
@@ -267,47 +263,40 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (t > 0) {                               // the product of this group's tile before has read the probabilities
         ok = mbar_wait(o_done + g, (t - 1) & 1, failed) && ok;
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll
-          for (int c = 0; c < HD / 32; ++c) {
-            uint32_t o[32];
-            tc_load32(o_col + c * 32, o);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tc_store32(o_col + c * 32, o);
-          }
-          tc_wait_stores();
-        }
       }
-      // second pass: exponentials, the row's sum, probabilities into shared memory
+      // exponentials, the row's sum, probabilities into shared memory
       float2 sum2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t v[2][32];
-        tc_load32_async(s_col + h * 64, v[0]);
-        tc_load32_async(s_col + h * 64 + 32, v[1]);
-        tc_wait_loads();
+      for (int c = 0; c < 4; ++c) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          mask32(v[c], k0 + h * 64 + c * 32, p_row, lo_row);
+        for (int i = 0; i < 32; i += 8) {
+          uint4 packed;
+          __nv_bfloat162 *pk = reinterpret_cast<__nv_bfloat162 *>(&packed);
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 packed;
-            __nv_bfloat162 *pk = reinterpret_cast<__nv_bfloat162 *>(&packed);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float2 x = __ffma2_rn(make_float2(__uint_as_float(v[c][i + 2 * e]), __uint_as_float(v[c][i + 2 * e + 1])), sl2_2, neg_m2);
-              x.x = le::fast_exp2(x.x);
-              x.y = le::fast_exp2(x.y);
-              sum2 = __fadd2_rn(sum2, x);
-              pk[e] = __floats2bfloat162_rn(x.x, x.y);
-            }
-            // keys h * 64 ...: 64-key block h of the operand; 16-byte chunk c * 4 + i / 8 of the row, swizzled
-            *reinterpret_cast<uint4 *>(p_row_smem + h * (BM * 128) + ((static_cast<uint32_t>(c * 4 + i / 8) << 4) ^ swz)) = packed;
+          for (int e = 0; e < 4; ++e) {
+            float2 x = __ffma2_rn(make_float2(__uint_as_float(v[c][i + 2 * e]), __uint_as_float(v[c][i + 2 * e + 1])), sl2_2, neg_m2);
+            x.x = le::fast_exp2(x.x);
+            x.y = le::fast_exp2(x.y);
+            sum2 = __fadd2_rn(sum2, x);
+            pk[e] = __floats2bfloat162_rn(x.x, x.y);
           }
+          // keys c * 32 ...: 64-key block c / 2 of the operand; 16-byte chunk (c % 2) * 4 + i / 8 of the row, swizzled
+          *reinterpret_cast<uint4 *>(p_row_smem + (c / 2) * (BM * 128) + ((static_cast<uint32_t>((c % 2) * 4 + i / 8) << 4) ^ swz)) = packed;
         }
       }
       l_run = l_run * alpha + (sum2.x + sum2.y);
+      // (rarely) some row of the warp moved its maximum: rescale the group's accumulator before the next product
+      if (t > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tc_load32(o_col + c * 32, o);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tc_store32(o_col + c * 32, o);
+        }
+        tc_wait_stores();
+      }
       fence_async_proxy();
       tc_fence_before();
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
