@@ -122,7 +122,9 @@ def prefill_flops(cfg, tokens):
 
 
 def run_ours(args):
+    global BLOCK_SIZE
     import torch
+    BLOCK_SIZE = args.page
 
     from lyapunov_engine_b200 import EngineConfig, LLMEngine, SamplingParams, build, load_model, ops
 
@@ -432,6 +434,7 @@ def main():
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     p.add_argument("--only", choices=["decode", "prefill"], default=None, help="run one kind of step and exit (for profilers)")
     p.add_argument("--batch", type=int, default=8, help="batch of --only decode")
+    p.add_argument("--page", type=int, default=BLOCK_SIZE, help="tokens per page of the cache")
     p.add_argument("--context", type=int, default=0, help="with --only decode: the context the last step ends at")
     p.add_argument("--no-cuda-graphs", action="store_true", help="with --only decode: launch every kernel by itself")
     args = p.parse_args()
