@@ -2,35 +2,36 @@
 // memory, TMA), for bfloat16 with head sizes 64 and 128 and pages of 8..128
 // keys (a power of two): portions of prompts against the paged cache.
 //
-// One block owns 128 query tokens of one head and walks the keys in tiles of
-// 128.  Roles:
+// One block owns 128 query tokens of TWO query heads that share a key/value
+// head (one head where the group has an odd one left) and walks the keys in
+// tiles of 128; every tile of keys and values is fetched once for both heads.
+// Roles:
 //   warp 0      producer: its lanes look the tile's pages up in the block table
 //               and each issues the TMA copies of one page's keys or values
 //               (128-byte swizzle) into a ring of key stages and one of value
 //               stages;
-//   warp 1      tensor core: one thread issues S = Q K^T (128 x 128 x head
-//               size) into one of two score buffers in tensor memory and, when
-//               the probabilities are ready, O += P V (128 x head size x 128);
-//   warp 10     where tensor memory has room for the probabilities beside the
-//               scores (head size 64), a thread of its own issues the scores
-//               from tile 2 on, so that they never wait behind a product;
-//   warps 2..9  softmax, in two groups of four warps.  Group g takes the tiles
-//               j = g, g + 2, ... and keeps a running maximum, a sum and an
-//               output accumulator of its own for them, so the two groups never
-//               wait for each other: while one computes exponentials the other
-//               waits for its scores.  Thread (quarter, lane) of a group owns
-//               query row r with all 128 keys of the tile: it reads the scores
-//               from tensor memory, masks what the row may not see, and writes the
-//               probabilities as bfloat16 into the group's buffer in shared
-//               memory in the operand layout of the next product.
+//   warp 1      tensor core: one thread issues the products O += P V (128 x
+//               head size x 128) of both heads when their probabilities are
+//               ready;
+//   warp 10     tensor core: one thread issues the scores S = Q K^T (128 x 128
+//               x head size) of both heads, each as soon as the head's softmax
+//               group has taken the scores of the tile before into registers.
+//               (Where tensor memory has no room for the probabilities beside
+//               the scores - head size 128 - they overwrite the scores they
+//               came from, the next scores must follow the product that reads
+//               them, and warp 1 issues everything in that order.)
+//   warps 2..9  softmax, a group of four warps per head.  Thread (quarter,
+//               lane) owns query row r with all 128 keys of the tile: it reads
+//               the scores from tensor memory into registers, masks what the
+//               row may not see, keeps the running maximum and the sum in 32
+//               bits (exp2 with the scale folded in) and writes the
+//               probabilities as bfloat16 pairs back into tensor memory, the A
+//               operand of the next product.
 // The running maximum only moves when the tile's maximum exceeds it by more
 // than 2^8 in the exponent; until then probabilities up to 256 go into the
 // product and the sum (both 32-bit accumulations), which the final division
 // takes out again.  The accumulator in tensor memory is therefore rescaled
-// rarely.  A group frees its score buffer as soon as the scores are in its
-// registers, and the tensor core fills it with the scores of the group's next
-// tile while the group still works on this one.  At the end the two groups' partial results are merged like the
-// splits of a decode: each thread combines half of the columns of its row.
+// rarely.  At the end every thread normalises its row and stores it.
 //
 // Every wait on an mbarrier is bounded in time; a block that gives up sets the
 // status word, lets copies in flight land, frees its tensor memory and returns.
@@ -56,14 +57,13 @@ constexpr int DB = HD / 64;                 // 64-wide blocks of the head size
 constexpr int BM = 128, BN = 128;           // query rows, keys per tile
 constexpr int KS = HD == 64 ? 4 : 3;        // key stages
 constexpr int VS = HD == 64 ? 4 : 2;        // value stages
-constexpr int THREADS = 352;                // producer warp, tensor-core warp, two softmax groups of four warps, score-issue warp
+constexpr int THREADS = 352;                // producer, products, two softmax groups of four warps, scores
 constexpr int SCORE_WARP = 10;
 constexpr int Q_BYTES = BM * HD * 2, K_BYTES = BN * HD * 2, V_BYTES = BN * HD * 2;
-constexpr uint32_t TMEM_COLS = 512;         // scores at 0 and 128, the groups' outputs at 256 and 256 + head size
+constexpr uint32_t TMEM_COLS = 512;         // head g: scores at g * 128, output at 256 + g * head size
 constexpr uint32_t O_COL = 256;
 // The probabilities (bfloat16, two to a column: 64 columns) have columns of their own where tensor memory has
-// room (head size 64); else they take the place of the scores they were made from, and the scores of the
-// group's next tile can only follow the product that reads them.
+// room (head size 64); else they take the place of the scores they were made from.
 constexpr bool OWN_P_COLUMNS = 256 + 2 * HD + 2 * 64 <= 512;
 __device__ __forceinline__ uint32_t p_col(int g) { return OWN_P_COLUMNS ? 256 + 2 * HD + g * 64 : g * BN; }
 constexpr float LOG2E = 1.4426950408889634f;
@@ -87,27 +87,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     int num_pages, int window, float scale, int *__restrict__ status) {
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
-  unsigned char *q_smem = smem;
-  unsigned char *k_smem = q_smem + Q_BYTES;
+  unsigned char *q_smem = smem;                // [2 heads]
+  unsigned char *k_smem = q_smem + 2 * Q_BYTES;
   unsigned char *v_smem = k_smem + KS * K_BYTES;
-  float *group_stats = reinterpret_cast<float *>(v_smem + VS * V_BYTES);      // [2 groups][maximum, sum][BM]
-  uint64_t *q_full = reinterpret_cast<uint64_t *>(group_stats + 4 * BM);
+  uint64_t *q_full = reinterpret_cast<uint64_t *>(v_smem + VS * V_BYTES);
   uint64_t *k_full = q_full + 1;             // [KS]
   uint64_t *k_empty = k_full + KS;           // [KS]
   uint64_t *v_full = k_empty + KS;           // [VS]
   uint64_t *v_empty = v_full + VS;           // [VS]
-  uint64_t *s_full = v_empty + VS;           // [2]: scores of the group's next tile are in tensor memory
-  uint64_t *s_free = s_full + 2;             // [2]: the group has the scores in registers, the buffer may be overwritten
-  uint64_t *p_full = s_free + 2;             // [2]: the group's probabilities are in shared memory
-  uint64_t *o_done = p_full + 2;             // [2]: the group's accumulator holds all its tiles so far
-  uint64_t *merge_bar = o_done + 2;          // both groups have their final sums
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(merge_bar + 1);
+  uint64_t *s_full = v_empty + VS;           // [2]: the head's scores of the next tile are in tensor memory
+  uint64_t *s_free = s_full + 2;             // [2]: the head's group has them in registers, the buffer may be overwritten
+  uint64_t *p_full = s_free + 2;             // [2]: the head's probabilities are in tensor memory
+  uint64_t *o_done = p_full + 2;             // [2]: the head's accumulator holds all tiles so far
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_done + 2);
   volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // later tiles of a prompt see more keys and take longer: start them first
-  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
-  const int kvh = head / (num_heads / num_kv_heads);
+  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int group = num_heads / num_kv_heads, pairs = (group + 1) / 2;
+  const int kvh = blockIdx.y / pairs, pair = blockIdx.y % pairs;
+  const int head0 = kvh * group + 2 * pair;
+  const int heads_here = min(2, group - 2 * pair);
   const int b = tile_request[tile];
   const int q0 = tile_q0[tile];
   const int q_len = cu_q[b + 1] - cu_q[b];
@@ -162,7 +163,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int s = 0; s < KS; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
       for (int s = 0; s < VS; ++s) { mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1); }
       for (int g = 0; g < 2; ++g) { mbar_init(s_full + g, 1); mbar_init(s_free + g, 4); mbar_init(p_full + g, 4); mbar_init(o_done + g, 1); }
-      mbar_init(merge_bar, 8);
       *failed = 0;
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       fence_async_proxy();
@@ -171,8 +171,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // The first copies need nothing but the barriers: they start before tensor memory is set up and the block
     // meets, so the scores of tile 0 can follow the block's start closely.
     if (lane == 0) {
-      mbar_expect_tx(q_full, Q_BYTES);
-      for (int d = 0; d < DB; ++d) tma_load_2d(q_smem + d * BM * 128, &map_q, q_full, head * HD + d * 64, tok0);
+      mbar_expect_tx(q_full, heads_here * Q_BYTES);
+      for (int g = 0; g < heads_here; ++g)
+        for (int d = 0; d < DB; ++d) tma_load_2d(q_smem + g * Q_BYTES + d * BM * 128, &map_q, q_full, (head0 + g) * HD + d * 64, tok0);
     }
     page_now = page_of(0);
     page_next = page_of(1);
@@ -199,22 +200,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   // F32 accumulate, BF16 operands, M = 128; S: both K-major, N = 128; PV: B is MN-major (bit 16), N = head size
   constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
   constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(HD >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
-  // scores of tile j into the buffer of group j & 1; frees the key stage when they are through
-  auto issue_scores = [&](int j) {
-    if (!mbar_wait(k_full + j % KS, (j / KS) & 1, failed)) return false;
-    tc_fence_after();
-    const uint32_t q_addr = smem_u32(q_smem);
+  // head g's scores of tile j (whose keys have landed) into the head's score buffer
+  auto issue_scores = [&](int j, int g) {
+    const uint32_t q_addr = smem_u32(q_smem + g * Q_BYTES);
     const uint32_t k_addr = smem_u32(k_smem + (j % KS) * K_BYTES);
-    const uint32_t tmem_s = tmem_base + (j & 1) * BN;
 #pragma unroll
     for (int k = 0; k < HD / 16; ++k) {
       // k-step k lies in 64-wide block k / 4 of the head size, 32 bytes per step inside it
       const uint32_t off = (k / 4) * (BM * 128) + (k % 4) * 32;
-      tc_mma(tmem_s, smem_desc(q_addr + off), smem_desc(k_addr + off), idesc_s, k > 0 ? 1u : 0u);
+      tc_mma(tmem_base + g * BN, smem_desc(q_addr + off), smem_desc(k_addr + off), idesc_s, k > 0 ? 1u : 0u);
     }
-    tc_commit(s_full + (j & 1));
-    tc_commit(k_empty + j % KS);
-    return true;
+    tc_commit(s_full + g);
+  };
+  // head g's product of tile j (whose values have landed): P from tensor memory, 16 keys = 8 columns; V: rows
+  // are keys, 16 keys = 2048 bytes, 64-wide blocks of the head size BN * 128 apart
+  auto issue_product = [&](int j, int g) {
+    const uint32_t v_addr = smem_u32(v_smem + (j % VS) * V_BYTES);
+#pragma unroll
+    for (int k = 0; k < BN / 16; ++k)
+      tc_mma_ts(tmem_base + O_COL + g * HD, tmem_base + p_col(g) + k * 8, smem_desc_mn(v_addr + k * 16 * 128, BN * 128), idesc_o,
+                (j > 0 || k > 0) ? 1u : 0u);
+    tc_commit(o_done + g);                    // the head's accumulator holds tiles 0..j; its probabilities are free
   };
 
   if (warp == 0) {
@@ -242,45 +248,58 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int j = max(0, values_issued - VS); j < values_issued; ++j) mbar_wait(v_full + j % VS, (j / VS) & 1, &never);
     }
   } else if (warp == 1) {
-    // ---- tensor-core issue: the first scores and every product O += P V
+    // ---- tensor-core issue: the products; and the scores too where they have to follow the products
     if (lane == 0) {
-      bool ok = mbar_wait(q_full, 0, failed) && issue_scores(0);
-      if (ok && num_tiles > 1) ok = issue_scores(1);
-      for (int j = 0; j < num_tiles && ok; ++j) {
-        const int g = j & 1;
-        ok = mbar_wait(p_full + g, (j >> 1) & 1, failed) && mbar_wait(v_full + j % VS, (j / VS) & 1, failed);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t v_addr = smem_u32(v_smem + (j % VS) * V_BYTES);
-#pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
-          // P: in tensor memory, 16 keys = 8 columns; V: rows are keys, 16 keys = 2048 bytes, 64-wide dim blocks BN * 128 apart
-          const uint64_t db = smem_desc_mn(v_addr + k * 16 * 128, BN * 128);
-          tc_mma_ts(tmem_base + O_COL + g * HD, tmem_base + p_col(g) + k * 8, db, idesc_o, (j >= 2 || k > 0) ? 1u : 0u);
+      bool ok = true;
+      if (!OWN_P_COLUMNS) {
+        ok = mbar_wait(q_full, 0, failed) && mbar_wait(k_full, 0, failed);
+        if (ok) {
+          tc_fence_after();
+          for (int g = 0; g < heads_here; ++g) issue_scores(0, g);
+          tc_commit(k_empty);
         }
+      }
+      for (int j = 0; j < num_tiles && ok; ++j) {
+        ok = mbar_wait(v_full + j % VS, (j / VS) & 1, failed);
+        const bool more = !OWN_P_COLUMNS && j + 1 < num_tiles;
+        for (int g = 0; g < heads_here && ok; ++g) {
+          ok = mbar_wait(p_full + g, j & 1, failed);
+          if (!ok) break;
+          tc_fence_after();
+          issue_product(j, g);
+          if (more) {                         // the head's next scores overwrite the probabilities just read
+            if (g == 0) ok = mbar_wait(k_full + (j + 1) % KS, ((j + 1) / KS) & 1, failed);
+            if (!ok) break;
+            tc_fence_after();
+            issue_scores(j + 1, g);
+          }
+        }
+        if (!ok) break;
         tc_commit(v_empty + j % VS);          // the stage's values have been read
-        tc_commit(o_done + g);                // the group's accumulator holds its tiles up to j; its probabilities are free
-        // without columns of their own the probabilities sat where the next scores go: those follow the product
-        if (!OWN_P_COLUMNS && j + 2 < num_tiles) ok = issue_scores(j + 2);
+        if (more) tc_commit(k_empty + (j + 1) % KS);
       }
       if (!ok) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
     }
   } else if (warp == SCORE_WARP) {
-    // ---- tensor-core issue: the scores from tile 2 on, where they do not have to follow a product.  As soon
-    // as a group has taken the scores of tile j into registers its buffer takes tile j + 2, from a thread of
-    // its own so that this never waits behind the products' thread (which waits for probabilities).
+    // ---- tensor-core issue: the scores, from a thread of their own where they need not follow a product, so
+    // that they never wait behind the products' thread (which waits for probabilities)
     if (OWN_P_COLUMNS && lane == 0) {
-      bool ok = true;
-      for (int j = 2; j < num_tiles && ok; ++j) {
-        ok = mbar_wait(s_free + (j & 1), ((j - 2) >> 1) & 1, failed);
+      bool ok = mbar_wait(q_full, 0, failed);
+      for (int j = 0; j < num_tiles && ok; ++j) {
+        ok = mbar_wait(k_full + j % KS, (j / KS) & 1, failed);
+        for (int g = 0; g < heads_here && ok; ++g) {
+          if (j > 0) ok = mbar_wait(s_free + g, (j - 1) & 1, failed);   // the group has read the tile before
+          if (!ok) break;
+          tc_fence_after();
+          issue_scores(j, g);
+        }
         if (!ok) break;
-        tc_fence_after();
-        ok = issue_scores(j);
+        tc_commit(k_empty + j % KS);          // the stage's keys have been read
       }
       if (!ok) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
     }
-  } else {
-    // ---- softmax: thread (quarter, lane) of group g owns query row r for the tiles g, g + 2, ...
+  } else if (((warp - 2) >> 2) < heads_here) {
+    // ---- softmax: thread (quarter, lane) of group g owns query row r of head head0 + g
     const int quarter = warp & 3;               // the tensor-memory lanes this warp may touch
     const int g = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
@@ -288,15 +307,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int lo_row = window > 0 ? max(0, p_row - window + 1) : 0;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t s_col = lane_base + g * BN, o_col = lane_base + O_COL + g * HD;
+    const uint32_t p_tmem = lane_base + p_col(g);
     const float sl2 = scale * LOG2E;
     const float2 sl2_2 = make_float2(sl2, sl2);
-    const uint32_t p_tmem = lane_base + p_col(g);
     float m_run = -INFINITY, l_run = 0.0f;      // m_run in exponent units (score * scale * log2 e)
     bool ok = true;
-    int t = 0;                                  // how many tiles this group has done
-    for (int j = g; j < num_tiles; j += 2, ++t) {
+    for (int j = 0; j < num_tiles; ++j) {
       const int k0 = k_begin + j * BN;
-      ok = mbar_wait(s_full + g, t & 1, failed) && ok;
+      ok = mbar_wait(s_full + g, j & 1, failed) && ok;
       tc_fence_after();
       // the row's 128 scores stay in registers from here to the exponentials
       uint32_t v[4][32];
@@ -316,8 +334,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int i = 0; i < 32; ++i)
 #pragma unroll
         for (int c = 0; c < 4; ++c) chunk_max[c] = fmaxf(chunk_max[c], __uint_as_float(v[c][i]));   // four chains side by side
-      float tile_max = fmaxf(fmaxf(chunk_max[0], chunk_max[1]), fmaxf(chunk_max[2], chunk_max[3]));
-      tile_max *= sl2;
+      const float tile_max = fmaxf(fmaxf(chunk_max[0], chunk_max[1]), fmaxf(chunk_max[2], chunk_max[3])) * sl2;
       float alpha = 1.0f;
       if (tile_max > m_run + MAX_SLACK) {        // also the first keys a row sees (m_run is -inf until then)
         alpha = le::fast_exp2(m_run - tile_max);
@@ -325,8 +342,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;
       const float2 neg_m2 = make_float2(neg_m, neg_m);
-      if (t > 0) {                               // the product of this group's tile before has read the probabilities
-        ok = mbar_wait(o_done + g, (t - 1) & 1, failed) && ok;
+      if (j > 0) {                               // the product of the tile before has read the probabilities
+        ok = mbar_wait(o_done + g, (j - 1) & 1, failed) && ok;
         tc_fence_after();
       }
       // exponentials, the row's sum, probabilities as bfloat16 pairs into tensor memory (the next product's A operand)
@@ -340,14 +357,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           x.x = le::fast_exp2(x.x);
           x.y = le::fast_exp2(x.y);
           sum2 = __fadd2_rn(sum2, x);
-          const __nv_bfloat162 pair = __floats2bfloat162_rn(x.x, x.y);
-          packed[i / 2] = *reinterpret_cast<const uint32_t *>(&pair);
+          const __nv_bfloat162 both = __floats2bfloat162_rn(x.x, x.y);
+          packed[i / 2] = *reinterpret_cast<const uint32_t *>(&both);
         }
         tc_store16(p_tmem + c * 16, packed);
       }
       l_run = l_run * alpha + (sum2.x + sum2.y);
-      // (rarely) some row of the warp moved its maximum: rescale the group's accumulator before the next product
-      if (t > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+      // (rarely) some row of the warp moved its maximum: rescale the head's accumulator before the next product
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t o[32];
@@ -356,58 +373,32 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
           tc_store32(o_col + c * 32, o);
         }
-        tc_wait_stores();
       }
       tc_wait_stores();
       tc_fence_before();
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       if (lane == 0) mbar_arrive(p_full + g);
     }
-    if (ok && t > 0) ok = mbar_wait(o_done + g, (t - 1) & 1, failed);
-    // ---- merge the two groups: each thread takes half of the columns of its row
-    float *mine = group_stats + g * 2 * BM, *theirs = group_stats + (g ^ 1) * 2 * BM;
-    mine[r] = m_run;
-    mine[BM + r] = l_run;
-    tc_fence_before();
-    ok = __all_sync(0xffffffffu, ok);
-    if (lane == 0) mbar_arrive(merge_bar);
-    if (ok) ok = mbar_wait(merge_bar, 0, failed);
+    if (ok) ok = mbar_wait(o_done + g, (num_tiles - 1) & 1, failed);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) {
       if (lane == 0) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
     } else {
       tc_fence_after();
-      const float m0 = g == 0 ? m_run : theirs[r], m1 = g == 0 ? theirs[r] : m_run;
-      const float l0 = g == 0 ? l_run : theirs[BM + r], l1 = g == 0 ? theirs[BM + r] : l_run;
-      const float m = fmaxf(m0, m1);
-      const float w0 = m0 == -INFINITY ? 0.0f : le::fast_exp2(m0 - m);
-      const float w1 = m1 == -INFINITY ? 0.0f : le::fast_exp2(m1 - m);
-      const float l = l0 * w0 + l1 * w1;
-      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      const float f0 = w0 * inv, f1 = w1 * inv;
-      constexpr int OC = HD / 2;                 // output columns per thread
-      bf16 *dst = out + (tok0 + r) * out_stride + head * HD + g * OC;
-      const uint32_t col = lane_base + O_COL + g * OC;
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      bf16 *dst = out + (tok0 + r) * out_stride + (head0 + g) * HD;
 #pragma unroll
-      for (int c = 0; c < OC / 32; ++c) {
-        uint32_t a[32], bb[32];
-        tc_load32_async(col + c * 32, a);
-        if (num_tiles > 1) tc_load32_async(col + HD + c * 32, bb);     // the second group had no tile otherwise
-        tc_wait_loads();
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tc_load32(o_col + c * 32, o);
         if (r < rows) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 packed;
             __nv_bfloat162 *pk = reinterpret_cast<__nv_bfloat162 *>(&packed);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float x = __uint_as_float(a[i + 2 * e]) * f0, y = __uint_as_float(a[i + 2 * e + 1]) * f0;
-              if (num_tiles > 1) {
-                x = fmaf(__uint_as_float(bb[i + 2 * e]), f1, x);
-                y = fmaf(__uint_as_float(bb[i + 2 * e + 1]), f1, y);
-              }
-              pk[e] = __floats2bfloat162_rn(x, y);
-            }
+            for (int e = 0; e < 4; ++e)
+              pk[e] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * e]) * inv, __uint_as_float(o[i + 2 * e + 1]) * inv);
             *reinterpret_cast<uint4 *>(dst + c * 32 + i) = packed;
           }
         }
@@ -459,10 +450,11 @@ LE_API int le_attention_prefill_tc_bf16(void *out, int64_t out_stride, const voi
   if (rc != 0) return rc;
   rc = tensor_map(&map_v, v_cache, cache_rows, HD, HD, page_size);
   if (rc != 0) return rc;
-  const size_t smem = Q_BYTES + KS * K_BYTES + VS * V_BYTES + 4 * BM * sizeof(float) + 1024 + 256;   // 1024 to align, 256 for the barriers
+  const size_t smem = 2 * Q_BYTES + KS * K_BYTES + VS * V_BYTES + 1024 + 256;   // 1024 to align, 256 for the barriers
   cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return le::invalid("le_attention_prefill_tc_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-  dim3 grid(num_tiles, num_heads);
+  const int group = num_heads / num_kv_heads;
+  dim3 grid(num_tiles, num_kv_heads * ((group + 1) / 2));   // two heads of a group per block
   attention_tc_kernel<<<grid, THREADS, smem, stream>>>(map_q, map_k, map_v, static_cast<bf16 *>(out), out_stride, block_table,
                                                        max_blocks, cu_q, ctx_before, tile_request, tile_q0, num_heads,
                                                        num_kv_heads, page_size, tc_page_shift_of(page_size), num_pages, window,
