@@ -8,6 +8,8 @@
 // are added here in their fixed order.
 //
 // Sum, mean, rsqrt and the product are 32-bit; the output is rounded once.
+// Rows of up to 8192 values are read once and kept in registers between the
+// sum of squares and the scaling.
 // With `rows` given, only those rows are normed, into consecutive rows of
 // `out`, and the residual stream is left as it is (the final norm before the
 // output head runs on the wanted rows alone).
@@ -18,7 +20,40 @@
 
 namespace {
 
-template <typename TO, typename TD, int VEC>
+// VEC values at p (aligned to VEC elements) as floats, in one memory access where VEC is 4.
+template <typename T, int VEC>
+__device__ __forceinline__ void load_vec(float (&dst)[VEC], const T *p) {
+  if constexpr (VEC == 4 && sizeof(T) == 4) {
+    const float4 v = *reinterpret_cast<const float4 *>(p);
+    dst[0] = v.x, dst[1] = v.y, dst[2] = v.z, dst[3] = v.w;
+  } else if constexpr (VEC == 4 && sizeof(T) == 2) {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+    dst[0] = a.x, dst[1] = a.y, dst[2] = b.x, dst[3] = b.y;
+  } else {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) dst[v] = le::to_f32(p[v]);
+  }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void store_vec(T *p, const float (&src)[VEC]) {
+  if constexpr (VEC == 4 && sizeof(T) == 4) {
+    *reinterpret_cast<float4 *>(p) = make_float4(src[0], src[1], src[2], src[3]);
+  } else if constexpr (VEC == 4 && sizeof(T) == 2) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162 *>(&raw.x) = __floats2bfloat162_rn(src[0], src[1]);
+    *reinterpret_cast<__nv_bfloat162 *>(&raw.y) = __floats2bfloat162_rn(src[2], src[3]);
+    *reinterpret_cast<uint2 *>(p) = raw;
+  } else {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) p[v] = le::from_f32<T>(src[v]);
+  }
+}
+
+// PER_THREAD > 0: the row fits in PER_THREAD vectors of VEC values per thread, which stay in registers
+// between the sum of squares and the scaling (one pass over memory).  0: any width, two passes.
+template <typename TO, typename TD, int VEC, int PER_THREAD>
 __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, const TD *__restrict__ delta,
                                int num_partials, int64_t partial_stride, const float *__restrict__ weight,
                                const int32_t *__restrict__ rows, float eps, int hidden) {
@@ -30,6 +65,42 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
   const TD *d = delta ? delta + src_row * hidden : nullptr;
   TO *o = out + static_cast<int64_t>(blockIdx.x) * hidden;
   const bool write_back = (d != nullptr) && (rows == nullptr);
+
+  if constexpr (PER_THREAD > 0) {
+    float val[PER_THREAD][VEC];
+    float ss = 0.0f;
+#pragma unroll
+    for (int it = 0; it < PER_THREAD; ++it) {
+      const int i = (it * blockDim.x + threadIdx.x) * VEC;
+      if (i < hidden) {
+        load_vec<float, VEC>(val[it], x + i);
+        if (d)
+          for (int p = 0; p < num_partials; ++p) {
+            float add[VEC];
+            load_vec<TD, VEC>(add, d + p * partial_stride + i);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) val[it][v] += add[v];
+          }
+        if (write_back) store_vec<float, VEC>(x + i, val[it]);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) ss += val[it][v] * val[it][v];
+      }
+    }
+    ss = le::block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / static_cast<float>(hidden) + eps);
+#pragma unroll
+    for (int it = 0; it < PER_THREAD; ++it) {
+      const int i = (it * blockDim.x + threadIdx.x) * VEC;
+      if (i < hidden) {
+        float w[VEC];
+        load_vec<float, VEC>(w, weight + i);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) w[v] = val[it][v] * inv * w[v];
+        store_vec<TO, VEC>(o + i, w);
+      }
+    }
+    return;
+  }
 
   float ss = 0.0f;
   for (int i = threadIdx.x * VEC; i < hidden; i += blockDim.x * VEC) {
@@ -60,11 +131,20 @@ int launch(void *out, float *resid, const void *delta, int num_partials, int64_t
            const int32_t *rows, float eps, int num_rows, int hidden, cudaStream_t stream) {
   int threads = 32;
   while (threads < 512 && threads * 8 < hidden) threads *= 2;
-  if (hidden % 4 == 0)
-    return le::launch_chained(rmsnorm_kernel<TO, TD, 4>, dim3(num_rows), dim3(threads), 0, stream, static_cast<TO *>(out), resid,
-                              static_cast<const TD *>(delta), num_partials, partial_stride, weight, rows, eps, hidden);
-  return le::launch_chained(rmsnorm_kernel<TO, TD, 1>, dim3(num_rows), dim3(threads), 0, stream, static_cast<TO *>(out), resid,
-                            static_cast<const TD *>(delta), num_partials, partial_stride, weight, rows, eps, hidden);
+#define LE_NORM(VEC, PER)                                                                                               \
+  return le::launch_chained(rmsnorm_kernel<TO, TD, VEC, PER>, dim3(num_rows), dim3(threads), 0, stream,                \
+                            static_cast<TO *>(out), resid, static_cast<const TD *>(delta), num_partials, partial_stride, \
+                            weight, rows, eps, hidden)
+  const bool aligned = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(resid) | reinterpret_cast<uintptr_t>(delta) |
+                         reinterpret_cast<uintptr_t>(weight)) & 15) == 0 && partial_stride % 4 == 0;
+  if (hidden % 4 == 0 && aligned) {
+    const int per_thread = (hidden / 4 + threads - 1) / threads;   // vectors of 4 a thread holds
+    if (per_thread <= 2) LE_NORM(4, 2);
+    if (per_thread <= 4) LE_NORM(4, 4);
+    LE_NORM(4, 0);
+  }
+  LE_NORM(1, 0);
+#undef LE_NORM
 }
 
 }  // namespace
