@@ -7,8 +7,8 @@
 // weight rows (so even a 2048-row matrix gives 128 blocks, each streaming long
 // contiguous rows) and its four warps split every k-tile between them; their
 // partial sums meet in shared memory at the end.  Weights and the matching
-// slice of x flow through a cp.async pipeline (eight stages for up to 16 rows,
-// four beyond) in swizzled shared
+// slice of x flow through a cp.async pipeline (eight stages for up to 16 rows
+// of the plain forms, else four) in swizzled shared
 // memory.  Three forms:
 //   * plain:   out (bfloat16 or float32) = x W^T;
 //   * split-K: the K range is cut into `splits` slices and slice s writes its
@@ -208,8 +208,9 @@ int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t
            int64_t split_stride, cudaStream_t stream) {
   constexpr int WSETS = GATED ? 2 : 1;
   constexpr int BK = 128;
-  // few rows leave shared memory for a deeper pipeline: more bytes in flight per block (measured 3 % on a decode step)
-  constexpr int STAGES = MT <= 2 ? 8 : 4;
+  // Few rows leave shared memory for a deeper pipeline: more bytes in flight per block (3 % of a decode step).
+  // Not for the gated form: with two weight tiles per stage its 512 blocks no longer fit the GPU all at once.
+  constexpr int STAGES = (MT <= 2 && !GATED) ? 8 : 4;
   size_t smem = static_cast<size_t>(STAGES) * (WSETS * BN * BK + MT * 8 * BK) * sizeof(bf16);
   const size_t reduce = static_cast<size_t>(WARPS) * WSETS * MT * 4 * 32 * sizeof(float);
   if (reduce > smem) smem = reduce;
