@@ -11,6 +11,8 @@ brings them back, and the scheduler finishes and frees.
 """
 from __future__ import annotations
 
+import contextlib
+
 import torch
 
 from .. import build, ops
@@ -102,6 +104,8 @@ class LLMEngine:
         self.config = config
         self.loaded = model
         self.runtime = model.runtime
+        dev = torch.device(self.runtime.device)
+        self._device_index = dev.index if dev.index is not None else (torch.cuda.current_device() if dev.type == "cuda" else 0)
         if config.dtype != self.runtime.dtype:
             raise ValueError(f"the model was loaded as {self.runtime.dtype}, the engine is configured as {config.dtype}")
         self.host = build.load_host()
@@ -191,7 +195,7 @@ class LLMEngine:
             outputs.append(self._output(seq))
         if not out.entries:
             return outputs
-        with torch.cuda.device(self.runtime.device):
+        with self._on_device():
             logits = self.runner.step(out.entries)
             sampled = out.sampled_seqs
             tokens: list[int] = []
@@ -203,7 +207,7 @@ class LLMEngine:
                 # two small transfers, one wait: the chosen ids and the kernels' status word
                 self._tokens_host[:n].copy_(ids, non_blocking=True)
                 self._tokens_host[n:n + 1].copy_(self.runtime.status[:1], non_blocking=True)
-                torch.cuda.current_stream().synchronize()
+                torch.cuda.current_stream(self._device_index).synchronize()
                 host = self._tokens_host[:n + 1].tolist()
                 tokens, status = host[:n], host[n]
                 self.d2h_bytes += 4 * (n + 1)
@@ -213,6 +217,13 @@ class LLMEngine:
         for seq in out.scheduled_seqs:
             outputs.append(self._output(seq))
         return outputs
+
+    def _on_device(self):
+        """The engine's device as the current one: nothing to do (and nothing
+        to pay, every step) when it already is."""
+        if torch.cuda.current_device() == self._device_index:
+            return contextlib.nullcontext()
+        return torch.cuda.device(self._device_index)
 
     def _output(self, seq) -> RequestOutput:
         seq_id = seq.get_seq_id()

@@ -43,6 +43,8 @@ class ModelRunner:
         self.use_cuda_graphs = use_cuda_graphs
         self.check_status = check_status
         self.tile_sizes = attention_kernels.tile_sizes()
+        dev = torch.device(runtime.device)
+        self._device_index = dev.index if dev.index is not None else torch.cuda.current_device()
         self.fixed_max_blocks = [(max_model_len + cache.block_size - 1) // cache.block_size for _ in model.groups]
         self._capacity = 0
         self._ring: list = []
@@ -73,19 +75,26 @@ class ModelRunner:
 
     def _pack(self, entries, pad_requests=0, fixed=False, all_wanted=False):
         fixed_blocks = self.fixed_max_blocks if fixed else []
-        layout = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks, 0, 0)
-        if layout.total > self._capacity:
-            self._reserve(int(layout.total * 1.5))
         pinned, event = self._ring[self._ring_pos]
         self._ring_pos = (self._ring_pos + 1) % len(self._ring)
         event.synchronize()
-        layout = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks,
-                                     pinned.data_ptr(), self._capacity)
+        try:
+            layout = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks,
+                                         pinned.data_ptr(), self._capacity)
+        except ValueError:
+            # more integers than the buffers hold (it does not happen within the limits given at construction):
+            # size them for this step and pack again
+            need = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks, 0, 0).total
+            self._reserve(int(need * 1.5))
+            pinned, event = self._ring[self._ring_pos]
+            self._ring_pos = (self._ring_pos + 1) % len(self._ring)
+            layout = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks,
+                                         pinned.data_ptr(), self._capacity)
         if all_wanted:
             n = layout.num_requests
             pinned.numpy()[layout.off_wanted_rows:layout.off_wanted_rows + n] = np.arange(n, dtype=np.int32)
         self._device_ints[:layout.total].copy_(pinned[:layout.total], non_blocking=True)
-        event.record()
+        event.record(torch.cuda.current_stream(self._device_index))
         return layout
 
     def _context(self, layout, workspace, num_wanted=None) -> StepContext:
