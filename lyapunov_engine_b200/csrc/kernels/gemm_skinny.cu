@@ -17,6 +17,13 @@
 //     does not depend on timing;
 //   * gated:   W holds gate rows then up rows ([2 I, K]); the block computes
 //     both for its columns and writes silu(gate) * up (bfloat16 [M, I]).
+//   * rotary: W is the fused query/key/value projection of an attention layer
+//     (plain form, bfloat16).  A block takes 8 columns of the low half of one
+//     head and the 8 columns of the high half that rotate with them, so the
+//     thread that holds a value also holds its partner: the epilogue rotates
+//     queries and keys by the tokens' positions (32-bit table), writes the
+//     queries to `out` and keys and values into the paged cache.  No kernel
+//     runs between the product and the attention.
 // The kernel may start before the kernel that produces x has finished: it
 // fetches its first weight tiles, then waits for x.
 //
@@ -49,12 +56,24 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
 }
 
 // MT: token tiles of 8 (M <= 8 MT).  GATED: gate and up rows, SiLU epilogue.
+// What the rotary form needs beyond the product's arguments (rope_kv.cu has the stand-alone kernel).
+struct RotaryArgs {
+  const float *cos_sin;            // [max_pos, head_dim]: cosines of the head_dim / 2 angles, then sines
+  const int32_t *positions;        // [M]
+  const int32_t *request_of_token; // [M]
+  const int32_t *block_table;      // [requests, max_blocks]
+  bf16 *k_cache, *v_cache;         // [pages, kv_heads, page, head_dim]
+  int *status;
+  int max_blocks, num_heads, num_kv_heads, head_dim, max_pos, page_size, num_pages, write_kv;
+};
+
 // BK: k per pipeline stage.
 // STAGES: depth of the cp.async pipeline.
-template <int MT, bool GATED, typename TO, int BK, int STAGES>
+// ROTARY: the fused qkv projection with rotation and cache write in the epilogue.
+template <int MT, bool GATED, typename TO, int BK, int STAGES, bool ROTARY>
 __global__ void __launch_bounds__(THREADS)
 gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 *__restrict__ w, int M, int N, int K,
-                   int64_t ldx, int64_t ldw, int64_t ldo, int k_per_split, int64_t split_stride) {
+                   int64_t ldx, int64_t ldw, int64_t ldo, int k_per_split, int64_t split_stride, RotaryArgs rotary) {
   constexpr int WSETS = GATED ? 2 : 1;
   constexpr int CPR = BK / 8;                      // 16-byte chunks per row of a tile
   constexpr int W_STAGE = WSETS * BN * BK;         // elements
@@ -73,6 +92,10 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
   const int k_end = min(K, k_begin + k_per_split);
   const int num_tiles = k_end > k_begin ? (k_end - k_begin + BK - 1) / BK : 0;
   const int n_out = GATED ? N / 2 : N;             // output columns
+  // rotary: the block's 16 weight rows are columns j0 .. j0 + 7 of a head's low half and of its high half
+  const int half = ROTARY ? rotary.head_dim / 2 : 0;
+  const int rot_head = ROTARY ? (blockIdx.x * 8) / half : 0;
+  const int rot_j0 = ROTARY ? (blockIdx.x * 8) % half : 0;
 
   auto load_w = [&](int stage, int kt) {
     const int k0 = k_begin + kt * BK;
@@ -85,7 +108,8 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
       const int n = n0 + row;
       const int k = k0 + chunk * 8;
       const bool valid = n < n_out && k < k_end;
-      const int64_t wrow = GATED ? (set == 0 ? n : n_out + n) : n;
+      int64_t wrow = GATED ? (set == 0 ? n : n_out + n) : n;
+      if constexpr (ROTARY) wrow = rot_head * rotary.head_dim + (row < 8 ? rot_j0 + row : half + rot_j0 + row - 8);
       cp16(dst + set * BN * BK + swz(row, chunk) * 8, w + (valid ? wrow * ldw + k : 0), valid);
     }
   };
@@ -107,6 +131,48 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
   for (int s = 0; s < STAGES - 1; ++s) {
     if (s < num_tiles) load_w(s, s);
     cp_commit();
+  }
+  // rotary: what the epilogue needs to know about this lane's tokens (rows 2t and 2t + 1 of every tile of 8) is
+  // asked for now, and is there long before the epilogue
+  float rot_cos[MT][2], rot_sin[MT][2];
+  int64_t rot_dst[MT][2];                          // where the pair goes: < 0: nowhere
+  if constexpr (ROTARY) {
+    if (warp == 0) {
+      const int g = lane >> 2, t = lane & 3;
+      const bool is_q = rot_head < rotary.num_heads;
+      const bool is_k = !is_q && rot_head < rotary.num_heads + rotary.num_kv_heads;
+#pragma unroll
+      for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const int row = m * 8 + 2 * t + q;
+          rot_dst[m][q] = -1;
+          rot_cos[m][q] = 1.0f, rot_sin[m][q] = 0.0f;
+          if (row >= M) continue;
+          const int pos = rotary.positions[row];
+          if (pos < 0 || pos >= rotary.max_pos) {
+            atomicOr(rotary.status, LE_STATUS_BAD_POSITION);
+            continue;
+          }
+          if (is_q || is_k) {
+            rot_cos[m][q] = rotary.cos_sin[static_cast<int64_t>(pos) * rotary.head_dim + rot_j0 + g];
+            rot_sin[m][q] = rotary.cos_sin[static_cast<int64_t>(pos) * rotary.head_dim + half + rot_j0 + g];
+          }
+          if (is_q) {
+            rot_dst[m][q] = static_cast<int64_t>(row) * ldo + rot_head * rotary.head_dim + rot_j0 + g;
+          } else if (rotary.write_kv) {
+            const int b = rotary.request_of_token[row];
+            const int page = rotary.block_table[static_cast<int64_t>(b) * rotary.max_blocks + pos / rotary.page_size];
+            if (page < 0 || page >= rotary.num_pages) {
+              atomicOr(rotary.status, LE_STATUS_BAD_PAGE);
+              continue;
+            }
+            const int kvh = is_k ? rot_head - rotary.num_heads : rot_head - rotary.num_heads - rotary.num_kv_heads;
+            rot_dst[m][q] = ((static_cast<int64_t>(page) * rotary.num_kv_heads + kvh) * rotary.page_size + pos % rotary.page_size) *
+                                rotary.head_dim + rot_j0 + g;
+          }
+        }
+    }
   }
   le::wait_for_predecessor();
 #pragma unroll
@@ -180,6 +246,30 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
   if (warp != 0) return;
   // fragment (n, m): c0, c1 at (n = g, m = 2t, 2t + 1); c2, c3 at (n = g + 8, same m)
   const int g = lane >> 2, t = lane & 3;
+  if constexpr (ROTARY) {
+    // c0 / c1 are the low-half values of tokens 2t / 2t + 1, c2 / c3 their partners in the high half
+    const bool is_q = rot_head < rotary.num_heads;
+    const bool is_k = !is_q && rot_head < rotary.num_heads + rotary.num_kv_heads;
+    bf16 *target = is_q ? reinterpret_cast<bf16 *>(out) : (is_k ? rotary.k_cache : rotary.v_cache);
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        float lo = 0.0f, hi = 0.0f;
+#pragma unroll
+        for (int wi = 0; wi < WARPS; ++wi) {
+          lo += red[(wi * VALUES + m * 4 + q) * 32 + lane];
+          hi += red[(wi * VALUES + m * 4 + 2 + q) * 32 + lane];
+        }
+        if (rot_dst[m][q] < 0) continue;
+        // the product's output is rounded to bfloat16 as the plain form rounds it, then rotated in 32 bits
+        const float x0 = __bfloat162float(__float2bfloat16_rn(lo)), x1 = __bfloat162float(__float2bfloat16_rn(hi));
+        const float c = rot_cos[m][q], sn = rot_sin[m][q];
+        target[rot_dst[m][q]] = __float2bfloat16_rn(x0 * c - x1 * sn);
+        target[rot_dst[m][q] + half] = __float2bfloat16_rn(x1 * c + x0 * sn);
+      }
+    return;
+  }
   TO *dst = out + static_cast<int64_t>(split) * split_stride;
 #pragma unroll
   for (int m = 0; m < MT; ++m) {
@@ -203,9 +293,9 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
   }
 }
 
-template <int MT, bool GATED, typename TO>
+template <int MT, bool GATED, typename TO, bool ROTARY = false>
 int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int splits,
-           int64_t split_stride, cudaStream_t stream) {
+           int64_t split_stride, cudaStream_t stream, const RotaryArgs &rotary = RotaryArgs{}) {
   constexpr int WSETS = GATED ? 2 : 1;
   constexpr int BK = 128;
   // Few rows leave shared memory for a deeper pipeline: more bytes in flight per block (3 % of a decode step).
@@ -214,7 +304,7 @@ int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t
   size_t smem = static_cast<size_t>(STAGES) * (WSETS * BN * BK + MT * 8 * BK) * sizeof(bf16);
   const size_t reduce = static_cast<size_t>(WARPS) * WSETS * MT * 4 * 32 * sizeof(float);
   if (reduce > smem) smem = reduce;
-  auto kernel = gemm_skinny_kernel<MT, GATED, TO, BK, STAGES>;
+  auto kernel = gemm_skinny_kernel<MT, GATED, TO, BK, STAGES, ROTARY>;
   if (smem >= 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return le::invalid("le_gemm_skinny: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -224,7 +314,7 @@ int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t
   k_per_split = (k_per_split + BK - 1) / BK * BK;
   dim3 grid((n_out + BN - 1) / BN, splits);
   return le::launch_chained(kernel, grid, dim3(THREADS), smem, stream, static_cast<TO *>(out), static_cast<const bf16 *>(x),
-                            static_cast<const bf16 *>(w), M, N, K, ldx, ldw, ldo, k_per_split, split_stride);
+                            static_cast<const bf16 *>(w), M, N, K, ldx, ldw, ldo, k_per_split, split_stride, rotary);
 }
 
 template <bool GATED, typename TO>
@@ -256,4 +346,34 @@ LE_API int le_gemm_skinny_bf16(void *out, int out_dtype, const void *x, const vo
   if (out_dtype == LE_F32) return dispatch_m<false, float>(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream);
   if (out_dtype == LE_BF16) return dispatch_m<false, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream);
   return le::invalid("le_gemm_skinny_bf16: unknown dtype code %d", out_dtype);
+}
+
+// The fused query/key/value projection of an attention layer with the rotary
+// position encoding and the cache write in its epilogue (at most 16 rows):
+//   qkv[t, head h] = rotate(x[t] W_h^T, positions[t]) for the query heads,
+//   keys (rotated) and values go to their place in the paged cache
+//   [pages, kv_heads, page, head_dim] through the block table (write_kv = 0:
+//   they are dropped, the layer reads another layer's cache).
+// W is [(heads + 2 kv_heads) head_dim, K]; the whole head rotates (the table
+// [max_pos, head_dim] holds head_dim / 2 cosines, then sines, per position);
+// head_dim is a multiple of 16.  Same arithmetic and roundings as the plain
+// product followed by le_rope_kv_write.
+LE_API int le_gemm_skinny_rotary_bf16(void *qkv, const void *x, const void *w, int M, int K, int64_t ldx, int64_t ldw, int64_t ldo,
+                                      void *k_cache, void *v_cache, const float *cos_sin, const int32_t *positions,
+                                      const int32_t *request_of_token, const int32_t *block_table, int max_blocks,
+                                      int num_heads, int num_kv_heads, int head_dim, int max_pos, int page_size, int num_pages,
+                                      int write_kv, int *status, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (M > 16) return le::invalid("le_gemm_skinny_rotary_bf16: at most 16 rows, got %d", M);
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) return le::invalid("le_gemm_skinny_rotary_bf16: K (%d) and the leading dimensions must be multiples of 8", K);
+  if (head_dim < 16 || head_dim % 16) return le::invalid("le_gemm_skinny_rotary_bf16: head size %d is no multiple of 16", head_dim);
+  if (num_heads < 1 || num_kv_heads < 0 || page_size < 1) return le::invalid("le_gemm_skinny_rotary_bf16: bad geometry");
+  RotaryArgs r{};
+  r.cos_sin = cos_sin, r.positions = positions, r.request_of_token = request_of_token, r.block_table = block_table;
+  r.k_cache = static_cast<bf16 *>(k_cache), r.v_cache = static_cast<bf16 *>(v_cache), r.status = status;
+  r.max_blocks = max_blocks, r.num_heads = num_heads, r.num_kv_heads = num_kv_heads, r.head_dim = head_dim;
+  r.max_pos = max_pos, r.page_size = page_size, r.num_pages = num_pages, r.write_kv = write_kv;
+  const int N = (num_heads + 2 * num_kv_heads) * head_dim;
+  if (M <= 8) return launch<1, false, bf16, true>(qkv, x, w, M, N, K, ldx, ldw, ldo, 1, 0, stream, r);
+  return launch<2, false, bf16, true>(qkv, x, w, M, N, K, ldx, ldw, ldo, 1, 0, stream, r);
 }

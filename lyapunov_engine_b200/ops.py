@@ -73,6 +73,9 @@ _CORE_SIGNATURES = {
                         c_void_p, c_void_p],
     "le_gemm_skinny_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
                             c_int64, c_int, c_void_p],
+    "le_gemm_skinny_rotary_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, c_void_p, c_void_p],
     "le_rope_kv_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "le_gemm_simt": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
@@ -278,6 +281,37 @@ def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, splits: int
     _check(core().le_gemm_skinny_bf16(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0),
                                       w.stride(0), ldo, splits, stride, 1 if gated else 0, _stream()),
            "le_gemm_skinny_bf16")
+
+
+FUSE_ROTARY = os.environ.get("LYAPUNOV_FUSE_ROTARY", "1") not in ("0", "")
+
+
+def rotary_product_applies(a: torch.Tensor, w: torch.Tensor, head_dim: int, rot: int) -> bool:
+    """Whether the qkv product, the rotation and the cache write can be one kernel."""
+    return skinny_applies(a, w) and rot == head_dim and head_dim % 16 == 0 and head_dim >= 16
+
+
+def gemm_skinny_rotary(qkv, a, w, k_cache, v_cache, cos_sin, positions, request_of_token, block_table, num_heads,
+                       num_kv_heads, head_dim, page_size, write_kv, status) -> None:
+    """The fused qkv projection of at most 16 rows with rotary encoding and
+    cache write in its epilogue: rotated queries into ``qkv`` (its key and
+    value columns are left alone), rotated keys and the values into the paged
+    cache.  Same arithmetic and roundings as linear() then rope_kv_write()."""
+    _need_cuda(qkv, a, w, k_cache, cos_sin, positions, block_table)
+    M, K = a.shape
+    assert rotary_product_applies(a, w, head_dim, cos_sin.shape[1]) and w.dtype == torch.bfloat16
+    assert w.shape == ((num_heads + 2 * num_kv_heads) * head_dim, K) and qkv.shape == (M, w.shape[0])
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+    assert block_table.dtype == torch.int32 and block_table.is_contiguous()
+    if write_kv:
+        assert k_cache.dtype == torch.bfloat16 and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert k_cache.shape[1:] == (num_kv_heads, page_size, head_dim)
+    num_pages = k_cache.shape[0] if k_cache is not None else 0
+    _check(core().le_gemm_skinny_rotary_bf16(_ptr(qkv), _ptr(a), _ptr(w), M, K, a.stride(0), w.stride(0), qkv.stride(0),
+                                             _ptr(k_cache), _ptr(v_cache), _ptr(cos_sin), _ptr(positions),
+                                             _ptr(request_of_token), _ptr(block_table), block_table.shape[1], num_heads,
+                                             num_kv_heads, head_dim, cos_sin.shape[0], page_size, num_pages,
+                                             1 if write_kv else 0, _ptr(status), _stream()), "le_gemm_skinny_rotary_bf16")
 
 
 _tc_status = {}

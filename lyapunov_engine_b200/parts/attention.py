@@ -62,8 +62,11 @@ class AttentionMixer(Mixer):
         T = x.shape[0]
         ws = ctx.workspace
         qkv = ws.get("qkv", (T, (nh + 2 * nkv) * hd), rt.dtype)
-        ops.linear(qkv, x, self.w_qkv, ctx.status)
-        self.position.encode_and_store(qkv, (nh, nkv, hd), ctx, cache.kv, cache.write)
+        # a position encoding may know how to run the product itself, with its own work in the epilogue
+        fused = getattr(self.position, "product_encode_store", None)
+        if fused is None or not fused(qkv, x, self.w_qkv, (nh, nkv, hd), ctx, cache.kv, cache.write):
+            ops.linear(qkv, x, self.w_qkv, ctx.status)
+            self.position.encode_and_store(qkv, (nh, nkv, hd), ctx, cache.kv, cache.write)
         attn = ws.get("attn", (T, nh * hd), rt.dtype)
         attention_kernels.run(attn, qkv, ctx, cache.kv, nh, nkv, hd, self.window, self.scale)
         return ops.linear_for_residual(attn, self.w_o, ws, "mixer_out", ctx.status)

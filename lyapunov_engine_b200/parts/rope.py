@@ -78,6 +78,19 @@ class RotaryEncoding(PositionEncoding):
             runtime.shared[key] = table
         self.table = table
 
+    def product_encode_store(self, qkv, x, w_qkv, geometry, ctx, kv, write: bool) -> bool:
+        """qkv = x @ w_qkv^T, rotated and stored, as one kernel where that exists
+        (few rows, bfloat16, the whole head rotates).  False: nothing was done,
+        the caller runs the product and encode_and_store."""
+        nh, nkv, hd = geometry
+        if not ops.FUSE_ROTARY or x.dtype != torch.bfloat16 or not ops.rotary_product_applies(x, w_qkv, hd, self.table.shape[1]):
+            return False
+        ops.gemm_skinny_rotary(qkv, x, w_qkv, kv.k if kv is not None else None, kv.v if kv is not None else None, self.table,
+                               ctx.positions, ctx.request_of_token,
+                               ctx.block_tables[kv.group] if kv is not None else ctx.block_tables[0], nh, nkv, hd,
+                               kv.page_size if kv is not None else 1, write and kv is not None, ctx.status)
+        return True
+
     def encode_and_store(self, qkv, geometry, ctx, kv, write: bool) -> None:
         nh, nkv, hd = geometry
         ops.rope_kv_write(qkv, kv.k if kv is not None else None, kv.v if kv is not None else None, self.table,

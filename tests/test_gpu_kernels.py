@@ -227,6 +227,51 @@ def test_sampling_frequencies_and_batch_independence():
         assert one.item() == out[i].item()
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("nh,nkv,hd,page,K", [(4, 2, 16, 4, 64), (3, 1, 32, 8, 96), (6, 3, 64, 16, 136), (32, 8, 64, 16, 2048)])
+@pytest.mark.parametrize("write", [True, False])
+def test_qkv_product_with_rotary_epilogue(M, nh, nkv, hd, page, K, write):
+    """The qkv product that rotates and writes the cache itself gives the bits
+    of the product followed by the rotary kernel, which has its own test
+    against the plain formulas."""
+    o = ops()
+    g = torch.Generator().manual_seed(M * hd + K)
+    N = (nh + 2 * nkv) * hd
+    x = (torch.randn(M, K, generator=g) * 0.5).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) * K ** -0.5).bfloat16().to(DEV)
+    # two requests at scattered positions, the second far into its pages
+    positions = torch.tensor([(3 * i) % 29 if i % 2 == 0 else 30 + i for i in range(M)], dtype=torch.int32)
+    request = torch.tensor([i % 2 for i in range(M)], dtype=torch.int32)
+    pages = 40
+    blocks = (64 + page - 1) // page
+    perm = torch.randperm(pages - 1, generator=g)[:2 * blocks].to(torch.int32)
+    table = perm.view(2, blocks).contiguous()
+    inv = plain_llama.plain_inv_freq(hd, 10000.0, None)
+    ang = torch.outer(torch.arange(64).float(), inv)
+    cos_sin = torch.cat([ang.cos(), ang.sin()], -1).contiguous().to(DEV)
+    status = o.new_status(DEV)
+    assert o.rotary_product_applies(x, w, hd, hd)
+    qkv1 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    k1 = torch.zeros(pages, nkv, page, hd, dtype=torch.bfloat16, device=DEV)
+    v1 = torch.zeros_like(k1)
+    o.gemm_skinny(qkv1, x, w)
+    o.rope_kv_write(qkv1, k1, v1, cos_sin, positions.to(DEV), request.to(DEV), table.to(DEV), nh, nkv, hd, page, write, status)
+    qkv2 = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    k2, v2 = torch.zeros_like(k1), torch.zeros_like(k1)
+    o.gemm_skinny_rotary(qkv2, x, w, k2, v2, cos_sin, positions.to(DEV), request.to(DEV), table.to(DEV), nh, nkv, hd, page, write, status)
+    o.check_status(status)
+    assert torch.equal(qkv2[:, :nh * hd], qkv1[:, :nh * hd])
+    assert torch.equal(k2, k1) and torch.equal(v2, v1)
+    assert (k1.abs().sum() > 0) == write
+    # a position outside the table is reported, and nothing of that token is written
+    bad = positions.clone()
+    bad[0] = 64
+    o.gemm_skinny_rotary(qkv2, x, w, k2, v2, cos_sin, bad.to(DEV), request.to(DEV), table.to(DEV), nh, nkv, hd, page, write, status)
+    with pytest.raises(o.KernelError):
+        o.check_status(status)
+    status.zero_()
+
+
 @pytest.mark.parametrize("M", [1, 8, 9, 16, 33, 64])
 @pytest.mark.parametrize("N,K", [(515, 96), (64, 2048), (1000, 136), (48, 328), (2048, 1024)])
 def test_skinny_product(M, N, K):
