@@ -349,7 +349,7 @@ LE_API int le_gemm_skinny_bf16(void *out, int out_dtype, const void *x, const vo
 }
 
 // The fused query/key/value projection of an attention layer with the rotary
-// position encoding and the cache write in its epilogue (at most 16 rows):
+// position encoding and the cache write in its epilogue (at most 64 rows):
 //   qkv[t, head h] = rotate(x[t] W_h^T, positions[t]) for the query heads,
 //   keys (rotated) and values go to their place in the paged cache
 //   [pages, kv_heads, page, head_dim] through the block table (write_kv = 0:
@@ -364,7 +364,7 @@ LE_API int le_gemm_skinny_rotary_bf16(void *qkv, const void *x, const void *w, i
                                       int num_heads, int num_kv_heads, int head_dim, int max_pos, int page_size, int num_pages,
                                       int write_kv, int *status, cudaStream_t stream) {
   if (M <= 0) return 0;
-  if (M > 16) return le::invalid("le_gemm_skinny_rotary_bf16: at most 16 rows, got %d", M);
+  if (M > 64) return le::invalid("le_gemm_skinny_rotary_bf16: at most 64 rows, got %d", M);
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) return le::invalid("le_gemm_skinny_rotary_bf16: K (%d) and the leading dimensions must be multiples of 8", K);
   if (head_dim < 16 || head_dim % 16) return le::invalid("le_gemm_skinny_rotary_bf16: head size %d is no multiple of 16", head_dim);
   if (num_heads < 1 || num_kv_heads < 0 || page_size < 1) return le::invalid("le_gemm_skinny_rotary_bf16: bad geometry");
@@ -375,5 +375,7 @@ LE_API int le_gemm_skinny_rotary_bf16(void *qkv, const void *x, const void *w, i
   r.max_pos = max_pos, r.page_size = page_size, r.num_pages = num_pages, r.write_kv = write_kv;
   const int N = (num_heads + 2 * num_kv_heads) * head_dim;
   if (M <= 8) return launch<1, false, bf16, true>(qkv, x, w, M, N, K, ldx, ldw, ldo, 1, 0, stream, r);
-  return launch<2, false, bf16, true>(qkv, x, w, M, N, K, ldx, ldw, ldo, 1, 0, stream, r);
+  if (M <= 16) return launch<2, false, bf16, true>(qkv, x, w, M, N, K, ldx, ldw, ldo, 1, 0, stream, r);
+  if (M <= 32) return launch<4, false, bf16, true>(qkv, x, w, M, N, K, ldx, ldw, ldo, 1, 0, stream, r);
+  return launch<8, false, bf16, true>(qkv, x, w, M, N, K, ldx, ldw, ldo, 1, 0, stream, r);
 }

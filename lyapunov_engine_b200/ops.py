@@ -256,7 +256,7 @@ def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
                                a.stride(0), w.stride(0), out.stride(0), _stream()), "le_gemm_simt")
 
 
-SKINNY_ROWS = 16          # up to this many rows a product streams weights through the package's own kernel
+SKINNY_ROWS = 32          # up to this many rows a product streams weights through the package's own kernel (64: slower than the library)
 SKINNY_BLOCKS = 2 * 148   # blocks worth having in flight on a B200
 
 
@@ -299,7 +299,8 @@ def gemm_skinny_rotary(qkv, a, w, k_cache, v_cache, cos_sin, positions, request_
     cache.  Same arithmetic and roundings as linear() then rope_kv_write()."""
     _need_cuda(qkv, a, w, k_cache, cos_sin, positions, block_table)
     M, K = a.shape
-    assert rotary_product_applies(a, w, head_dim, cos_sin.shape[1]) and w.dtype == torch.bfloat16
+    assert M <= 64 and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and cos_sin.shape[1] == head_dim and head_dim % 16 == 0
+    assert K % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
     assert w.shape == ((num_heads + 2 * num_kv_heads) * head_dim, K) and qkv.shape == (M, w.shape[0])
     assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
     assert block_table.dtype == torch.int32 and block_table.is_contiguous()

@@ -227,7 +227,7 @@ def test_sampling_frequencies_and_batch_independence():
         assert one.item() == out[i].item()
 
 
-@pytest.mark.parametrize("M", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16, 29, 64])
 @pytest.mark.parametrize("nh,nkv,hd,page,K", [(4, 2, 16, 4, 64), (3, 1, 32, 8, 96), (6, 3, 64, 16, 136), (32, 8, 64, 16, 2048)])
 @pytest.mark.parametrize("write", [True, False])
 def test_qkv_product_with_rotary_epilogue(M, nh, nkv, hd, page, K, write):
@@ -240,7 +240,7 @@ def test_qkv_product_with_rotary_epilogue(M, nh, nkv, hd, page, K, write):
     x = (torch.randn(M, K, generator=g) * 0.5).bfloat16().to(DEV)
     w = (torch.randn(N, K, generator=g) * K ** -0.5).bfloat16().to(DEV)
     # two requests at scattered positions, the second far into its pages
-    positions = torch.tensor([(3 * i) % 29 if i % 2 == 0 else 30 + i for i in range(M)], dtype=torch.int32)
+    positions = torch.tensor([(i // 2 * 7) % 32 if i % 2 == 0 else 32 + i // 2 for i in range(M)], dtype=torch.int32)   # no slot twice
     request = torch.tensor([i % 2 for i in range(M)], dtype=torch.int32)
     pages = 40
     blocks = (64 + page - 1) // page
@@ -250,7 +250,7 @@ def test_qkv_product_with_rotary_epilogue(M, nh, nkv, hd, page, K, write):
     ang = torch.outer(torch.arange(64).float(), inv)
     cos_sin = torch.cat([ang.cos(), ang.sin()], -1).contiguous().to(DEV)
     status = o.new_status(DEV)
-    assert o.rotary_product_applies(x, w, hd, hd)
+    assert o.rotary_product_applies(x, w, hd, hd) == (M <= o.SKINNY_ROWS)      # the engine's choice; the kernel takes 64 rows
     qkv1 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
     k1 = torch.zeros(pages, nkv, page, hd, dtype=torch.bfloat16, device=DEV)
     v1 = torch.zeros_like(k1)
