@@ -257,7 +257,7 @@ def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
 
 
 SKINNY_ROWS = 32          # up to this many rows a product streams weights through the package's own kernel (64: slower than the library)
-SKINNY_BLOCKS = 2 * 148   # blocks worth having in flight on a B200
+SKINNY_BLOCKS = 512       # blocks worth having in flight on a B200 (4 slices of K for 2048 columns: measured best of 1..8)
 
 
 def skinny_applies(a: torch.Tensor, w: torch.Tensor) -> bool:
