@@ -241,7 +241,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
   bf16 *v_tiles = k_tiles + PF_STAGES * BN * HD;
 
   // later tiles of a prompt see more keys and take longer: start them first
-  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  const int tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x;   // the tile is the slow index: the first wave holds the long blocks
   const int kvh = head / (num_heads / num_kv_heads);
   const int b = tile_request[tile];
   const int q0 = tile_q0[tile];
@@ -641,7 +641,8 @@ LE_API int le_attention_prefill_bf16(void *out, int64_t out_stride, const void *
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return le::invalid("le_attention_prefill_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   }
-  dim3 grid(num_tiles, num_heads);
+  if (num_tiles > 65535) return le::invalid("le_attention_prefill_bf16: %d tiles of queries are too many for one launch", num_tiles);
+  dim3 grid(num_heads, num_tiles);
   attention_prefill_kernel<<<grid, PF_THREADS, smem, stream>>>(
       static_cast<bf16 *>(out), out_stride, static_cast<const bf16 *>(q), q_stride, static_cast<const bf16 *>(k_cache),
       static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before, tile_request, tile_q0, num_heads,

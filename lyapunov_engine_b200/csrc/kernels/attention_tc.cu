@@ -103,10 +103,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // later tiles of a prompt see more keys and take longer: start them first
-  const int tile = gridDim.x - 1 - blockIdx.x;
+  // Later tiles of a prompt see more keys and take longer: they start first.  The tile is the slow index of
+  // the grid, so that the whole first wave of blocks holds the long ones, whatever the head.
+  const int tile = gridDim.y - 1 - blockIdx.y;
   const int group = num_heads / num_kv_heads, pairs = (group + 1) / 2;
-  const int kvh = blockIdx.y / pairs, pair = blockIdx.y % pairs;
+  const int kvh = blockIdx.x / pairs, pair = blockIdx.x % pairs;
   const int head0 = kvh * group + 2 * pair;
   const int heads_here = min(2, group - 2 * pair);
   const int b = tile_request[tile];
@@ -454,7 +455,8 @@ LE_API int le_attention_prefill_tc_bf16(void *out, int64_t out_stride, const voi
   cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return le::invalid("le_attention_prefill_tc_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   const int group = num_heads / num_kv_heads;
-  dim3 grid(num_tiles, num_kv_heads * ((group + 1) / 2));   // two heads of a group per block
+  if (num_tiles > 65535) return le::invalid("le_attention_prefill_tc_bf16: %d tiles of queries are too many for one launch", num_tiles);
+  dim3 grid(num_kv_heads * ((group + 1) / 2), num_tiles);   // two heads of a group per block
   attention_tc_kernel<<<grid, THREADS, smem, stream>>>(map_q, map_k, map_v, static_cast<bf16 *>(out), out_stride, block_table,
                                                        max_blocks, cu_q, ctx_before, tile_request, tile_q0, num_heads,
                                                        num_kv_heads, page_size, tc_page_shift_of(page_size), num_pages, window,
