@@ -106,14 +106,15 @@ PYBIND11_MODULE(_host, m) {
           [](SchedulerConfig &c, int32_t id) { c.eos_token_ids = id < 0 ? std::vector<int32_t>{} : std::vector<int32_t>{id}; });
 
   py::class_<StepEntry>(m, "StepEntry")
-      .def(py::init([](SequencePtr seq, int start, int count, std::vector<int32_t> want) {
-             return StepEntry{std::move(seq), start, count, std::move(want)};
+      .def(py::init([](SequencePtr seq, int start, int count, std::vector<int32_t> want, int ahead) {
+             return StepEntry{std::move(seq), start, count, std::move(want), ahead};
            }),
-           py::arg("seq"), py::arg("start"), py::arg("count"), py::arg("want") = std::vector<int32_t>{})
+           py::arg("seq"), py::arg("start"), py::arg("count"), py::arg("want") = std::vector<int32_t>{}, py::arg("ahead") = 0)
       .def_readwrite("seq", &StepEntry::seq)
       .def_readwrite("start", &StepEntry::start)
       .def_readwrite("count", &StepEntry::count)
-      .def_readwrite("want", &StepEntry::want);
+      .def_readwrite("want", &StepEntry::want)
+      .def_readwrite("ahead", &StepEntry::ahead);
 
   py::class_<SchedulerOutputs>(m, "SchedulerOutputs")
       .def_readonly("entries", &SchedulerOutputs::entries)
@@ -139,6 +140,7 @@ PYBIND11_MODULE(_host, m) {
       .def("get_num_waiting_sequences", &ContinuousScheduler::get_num_waiting_sequences)
       .def("get_num_running_sequences", &ContinuousScheduler::get_num_running_sequences)
       .def("schedule", &ContinuousScheduler::schedule)
+      .def("schedule_ahead", &ContinuousScheduler::schedule_ahead)
       .def("post_step", &ContinuousScheduler::post_step)
       .def("get_stats", &ContinuousScheduler::get_stats)
       .def("get_config", &ContinuousScheduler::get_config);

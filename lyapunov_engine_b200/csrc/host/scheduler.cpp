@@ -173,11 +173,45 @@ SchedulerOutputs ContinuousScheduler::schedule() {
   return out;
 }
 
+SchedulerOutputs ContinuousScheduler::schedule_ahead(const SchedulerOutputs &launched) {
+  SchedulerOutputs out;
+  if (launched.entries.empty() || launched.is_prefill || !launched.preempted_seqs.empty() || !waiting_.empty()) return out;
+  if (launched.entries.size() != running_.size() || launched.sampled_seqs.size() != launched.entries.size()) return out;
+  for (const auto &e : launched.entries) {
+    const SequencePtr &seq = e.seq;
+    if (e.count != 1 || e.want.size() != 1 || seq->get_status() != SequenceStatus::RUNNING) return out;
+    // with the token that is still to come: the lengths the finish rules of post_step will see
+    const size_t total_then = static_cast<size_t>(e.start) + 2;          // tokens of the request after `launched`
+    const size_t output_then = total_then - seq->get_prompt_len();
+    if (static_cast<int>(output_then) >= seq->get_sampling_params().max_tokens) return out;
+    if (total_then >= static_cast<size_t>(config_.max_model_len)) return out;
+  }
+  // every request needs room for one more token than `launched` gave it
+  for (const auto &e : launched.entries)
+    if (block_manager_->max_growth(e.seq, static_cast<size_t>(e.start) + 2) < static_cast<size_t>(e.start) + 2) return out;
+  for (const auto &e : launched.entries) {
+    if (!block_manager_->grow(e.seq, static_cast<size_t>(e.start) + 2)) throw std::logic_error("schedule_ahead: grow failed after max_growth");
+    StepEntry next;
+    next.seq = e.seq;
+    next.start = e.start + 1;
+    next.count = 1;
+    next.want.push_back(0);
+    next.ahead = 1;
+    out.entries.push_back(std::move(next));
+    out.scheduled_seqs.push_back(e.seq);
+    out.sampled_seqs.push_back(e.seq);
+    out.num_batched_tokens += 1;
+  }
+  ++stats_.steps;
+  return out;
+}
+
 void ContinuousScheduler::post_step(const SchedulerOutputs &outputs, const std::vector<int32_t> &next_tokens) {
   if (outputs.sampled_seqs.size() != next_tokens.size())
     throw std::runtime_error("post_step: " + std::to_string(outputs.sampled_seqs.size()) + " requests were sampled but " +
                              std::to_string(next_tokens.size()) + " tokens were given");
   for (const auto &e : outputs.entries) {
+    if (e.seq->is_finished()) continue;  // it ended with the step before, while this one was already running
     e.seq->set_num_computed_tokens(static_cast<size_t>(e.start + e.count));
     if (e.count > 1 || e.want.empty()) stats_.prefill_tokens += static_cast<uint64_t>(e.count);
     else stats_.decode_tokens += 1;

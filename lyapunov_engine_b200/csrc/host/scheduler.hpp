@@ -45,11 +45,16 @@ struct SchedulerConfig {
 
 // Tokens [start, start + count) of one request in one step.  `want` lists the
 // places among them (0 .. count-1) whose logits the step returns.
+// `ahead` = 1: the entry belongs to a step that is launched before the result of
+// the step before it has been read (schedule_ahead): the request's recorded
+// state lags one token behind, and the entry's token is not known on the host
+// yet (the device passes it on).
 struct StepEntry {
   SequencePtr seq;
   int start{0};
   int count{0};
   std::vector<int32_t> want;
+  int ahead{0};
 };
 
 struct SchedulerOutputs {
@@ -81,7 +86,17 @@ public:
   int get_num_running_sequences() const { return static_cast<int>(running_.size()); }
 
   SchedulerOutputs schedule();
-  // `next_tokens[i]` is the token sampled for outputs.sampled_seqs[i].
+  // The step after `launched` (a step of single decoded tokens whose result has
+  // not been read yet), built without that result: every request goes on by one
+  // more token.  Empty (no entries) when that cannot be known to be the next
+  // step: a request waits for admission, `launched` held a prompt portion or
+  // pre-empted, a request reaches max_tokens or max_model_len with the token
+  // still to come, or a page is missing.  A request that ends for another
+  // reason (an end-of-sequence token) has one token too many computed, which
+  // post_step ignores.
+  SchedulerOutputs schedule_ahead(const SchedulerOutputs &launched);
+  // `next_tokens[i]` is the token sampled for outputs.sampled_seqs[i].  Steps
+  // are given back in the order in which they were scheduled.
   void post_step(const SchedulerOutputs &outputs, const std::vector<int32_t> &next_tokens);
 
   const SchedulerStats &get_stats() const { return stats_; }

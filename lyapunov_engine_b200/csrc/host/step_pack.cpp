@@ -20,11 +20,12 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
   int T = 0;
   for (const auto &e : entries) {
     if (e.count < 1) throw std::invalid_argument("pack_step: an entry brings no token");
-    if (e.start != static_cast<int>(e.seq->get_num_computed_tokens()))
+    if (e.ahead < 0 || e.ahead > 1) throw std::invalid_argument("pack_step: an entry is at most one step ahead");
+    if (e.start != static_cast<int>(e.seq->get_num_computed_tokens()) + e.ahead)
       throw std::invalid_argument("pack_step: request " + std::to_string(e.seq->get_seq_id()) + " has " +
                                   std::to_string(e.seq->get_num_computed_tokens()) +
                                   " tokens in the cache but its entry starts at " + std::to_string(e.start));
-    if (static_cast<size_t>(e.start + e.count) > e.seq->get_total_len())
+    if (static_cast<size_t>(e.start + e.count) > e.seq->get_total_len() + static_cast<size_t>(e.ahead))
       throw std::invalid_argument("pack_step: an entry runs past the request's tokens");
     for (int32_t w : e.want)
       if (w < 0 || w >= e.count) throw std::invalid_argument("pack_step: a wanted place lies outside the entry's tokens");
@@ -90,7 +91,9 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
     if (b < real) {
       const auto &e = entries[b];
       for (int j = 0; j < e.count; ++j) {
-        tok[t + j] = e.seq->token_at(static_cast<size_t>(e.start + j));
+        // (a token the host does not know yet is written by the device before the step runs)
+        const size_t at = static_cast<size_t>(e.start + j);
+        tok[t + j] = at < e.seq->get_total_len() ? e.seq->token_at(at) : 0;
         pos[t + j] = e.start + j;
         req[t + j] = b;
       }

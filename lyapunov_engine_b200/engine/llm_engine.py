@@ -11,7 +11,9 @@ brings them back, and the scheduler finishes and frees.
 """
 from __future__ import annotations
 
+import collections
 import contextlib
+import os
 
 import torch
 
@@ -35,7 +37,7 @@ class EngineConfig:
     def __init__(self, model_config=None, num_blocks: int = 1024, num_gpu_blocks: int | None = None,
                  block_size: int = 16, max_num_seqs: int = 64, max_num_batched_tokens: int = 2048,
                  dtype=torch.bfloat16, device: str = "cuda:0", max_model_len: int | None = None,
-                 max_prefill_chunk: int = 0, use_cuda_graphs: bool = True, seed: int = 0):
+                 max_prefill_chunk: int = 0, use_cuda_graphs: bool = True, seed: int = 0, lookahead: bool | None = None):
         self.model_config = model_config
         self.num_blocks = num_gpu_blocks if num_gpu_blocks is not None else num_blocks
         self.block_size = block_size
@@ -47,6 +49,17 @@ class EngineConfig:
         self.max_prefill_chunk = max_prefill_chunk
         self.use_cuda_graphs = use_cuda_graphs
         self.seed = seed
+        # launch the next decode step before the result of the one before has been read (see LLMEngine.step)
+        self.lookahead = (os.environ.get("LYAPUNOV_LOOKAHEAD", "1") not in ("0", "")) if lookahead is None else bool(lookahead)
+
+
+class _LaunchedStep:
+    """A step that runs on the device: what was scheduled, and where its tokens arrive."""
+    __slots__ = ("out", "num_sampled", "host", "event", "ids")
+
+    def __init__(self, out, num_sampled):
+        self.out, self.num_sampled = out, num_sampled
+        self.host = self.event = self.ids = None
 
 
 class RequestOutput:
@@ -133,7 +146,12 @@ class LLMEngine:
         self.req_counter = 0
         self.active_sequences: dict[int, tuple] = {}
         self._prompts: dict[int, list] = {}
-        self._tokens_host = torch.empty(config.max_num_seqs + 1, dtype=torch.int32, pin_memory=True)
+        # steps that run on the device and whose tokens have not been read: at most two
+        self._launched: collections.deque = collections.deque()
+        self._token_slots = [(torch.empty(config.max_num_seqs + 1, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+                             for _ in range(4)]
+        self._token_slot = 0
+        self.num_steps_ahead = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -186,37 +204,77 @@ class LLMEngine:
 
     def step(self) -> list[RequestOutput]:
         """One scheduler step: returns an output for every request that was in
-        the step (and for those that failed or were finished by it)."""
-        if not self.has_unfinished_requests():
+        the step (and for those that failed or were finished by it).
+
+        The device runs one step ahead of what this returns: while the tokens
+        of a decode step are on their way to the host, the step after it is
+        already launched (its input tokens pass from the sampler to the
+        embedding on the device), so the host's work between two steps does
+        not leave the device idle.  A request that ends with an
+        end-of-sequence token has then had one token too many computed, which
+        is dropped."""
+        while self._launched and all(s.is_finished() for s in self._launched[0].out.scheduled_seqs):
+            self._launched.popleft()           # a step launched ahead for requests that all ended before it
+        if not self._launched and not self.has_unfinished_requests():
             return []
-        out = self.scheduler.schedule()
         outputs: list[RequestOutput] = []
-        for seq in out.finished_seqs:
-            outputs.append(self._output(seq))
-        if not out.entries:
-            return outputs
         with self._on_device():
-            logits = self.runner.step(out.entries)
-            sampled = out.sampled_seqs
-            tokens: list[int] = []
-            n = len(sampled)
-            if n:
-                params = [self.active_sequences[s.get_seq_id()][1] for s in sampled]
-                indices = [s.get_total_len() for s in sampled]
-                ids = self.sampler.sample(logits, params, indices)
-                # two small transfers, one wait: the chosen ids and the kernels' status word
-                self._tokens_host[:n].copy_(ids, non_blocking=True)
-                self._tokens_host[n:n + 1].copy_(self.runtime.status[:1], non_blocking=True)
-                torch.cuda.current_stream(self._device_index).synchronize()
-                host = self._tokens_host[:n + 1].tolist()
-                tokens, status = host[:n], host[n]
-                self.d2h_bytes += 4 * (n + 1)
-                if status:
-                    ops.check_status(self.runtime.status)
-        self.scheduler.post_step(out, tokens)
-        for seq in out.scheduled_seqs:
-            outputs.append(self._output(seq))
+            if not self._launched:
+                out = self.scheduler.schedule()
+                for seq in out.finished_seqs:
+                    outputs.append(self._output(seq))
+                if not out.entries:
+                    return outputs
+                self._launch(out, None)
+            newest = self._launched[-1]
+            if self.config.lookahead and len(self._launched) < 2 and newest.ids is not None:
+                ahead = self.scheduler.schedule_ahead(newest.out)
+                if ahead.entries:
+                    self._launch(ahead, newest.ids)
+                    self.num_steps_ahead += 1
+            step = self._launched.popleft()
+            tokens = self._read(step)
+        ended_before = [s.is_finished() for s in step.out.scheduled_seqs]
+        self.scheduler.post_step(step.out, tokens)
+        for seq, ended in zip(step.out.scheduled_seqs, ended_before):
+            if not ended:
+                outputs.append(self._output(seq))
         return outputs
+
+    def _launch(self, out, device_tokens) -> None:
+        """Puts a scheduled step on the device: the model, the sampler and the
+        transfer of the chosen tokens (and the kernels' status word) to the host."""
+        logits = self.runner.step(out.entries, device_tokens)
+        sampled = out.sampled_seqs
+        n = len(sampled)
+        step = _LaunchedStep(out, n)
+        if n:
+            ahead = out.entries[0].ahead if device_tokens is not None else 0
+            params = [self.active_sequences[s.get_seq_id()][1] for s in sampled]
+            indices = [s.get_total_len() + ahead for s in sampled]
+            ids = self.sampler.sample(logits, params, indices)
+            host, event = self._token_slots[self._token_slot]
+            self._token_slot = (self._token_slot + 1) % len(self._token_slots)
+            event.synchronize()                # (the slot's transfer of four steps ago)
+            host[:n].copy_(ids, non_blocking=True)
+            host[n:n + 1].copy_(self.runtime.status[:1], non_blocking=True)
+            event.record(torch.cuda.current_stream(self._device_index))
+            step.host, step.event = host, event
+            # the next step may take its tokens from here if every entry is a single decoded token
+            if n == len(out.entries) and all(e.count == 1 for e in out.entries):
+                step.ids = ids
+            self.d2h_bytes += 4 * (n + 1)
+        self._launched.append(step)
+
+    def _read(self, step) -> list[int]:
+        """Waits for a launched step's tokens."""
+        if step.num_sampled == 0:
+            return []
+        step.event.synchronize()
+        host = step.host[:step.num_sampled + 1].tolist()
+        if host[-1]:
+            ops.check_status(self.runtime.status)
+        return host[:-1]
 
     def _on_device(self):
         """The engine's device as the current one: nothing to do (and nothing
@@ -262,5 +320,6 @@ class LLMEngine:
         s = self.scheduler.get_stats()
         return {"steps": s.steps, "prefill_tokens": s.prefill_tokens, "decode_tokens": s.decode_tokens,
                 "preemptions": s.preemptions, "failed": s.failed, "graph_steps": self.runner.num_graph_steps,
+                "steps_ahead": self.num_steps_ahead,
                 "free_blocks": self.block_manager.get_num_free_blocks() if self.loaded.model.groups else 0,
                 "cache_bytes": self.cache.bytes()}

@@ -73,7 +73,7 @@ class ModelRunner:
         self._device_ints = torch.empty(n, dtype=torch.int32, device=self.runtime.device)
         self._graphs.clear()  # they point into the old buffer
 
-    def _pack(self, entries, pad_requests=0, fixed=False, all_wanted=False):
+    def _pack(self, entries, pad_requests=0, fixed=False, all_wanted=False, device_tokens=None):
         fixed_blocks = self.fixed_max_blocks if fixed else []
         pinned, event = self._ring[self._ring_pos]
         self._ring_pos = (self._ring_pos + 1) % len(self._ring)
@@ -95,6 +95,10 @@ class ModelRunner:
             pinned.numpy()[layout.off_wanted_rows:layout.off_wanted_rows + n] = np.arange(n, dtype=np.int32)
         self._device_ints[:layout.total].copy_(pinned[:layout.total], non_blocking=True)
         event.record(torch.cuda.current_stream(self._device_index))
+        if device_tokens is not None:
+            # the entries' tokens were sampled by the step before and have not left the device
+            n = len(entries)
+            self._device_ints[layout.off_token_ids:layout.off_token_ids + n].copy_(device_tokens[:n], non_blocking=True)
         return layout
 
     def _context(self, layout, workspace, num_wanted=None) -> StepContext:
@@ -125,11 +129,13 @@ class ModelRunner:
         return c
 
     # ---- the step
-    def step(self, entries):
+    def step(self, entries, device_tokens=None):
         """Runs the entries as one batch.  Returns float32 logits [wanted, vocab]
         in the order of the entries and of their ``want`` lists, or None when
         nothing is wanted.  The tensor is scratch: it is overwritten by the
-        next step."""
+        next step.  ``device_tokens`` (int32 on the device, one per entry): the
+        entries bring one token each that the host does not know yet (entries
+        with ``ahead`` = 1); they are taken from there."""
         if not entries:
             return None
         self.num_steps += 1
@@ -140,9 +146,9 @@ class ModelRunner:
             raise ValueError(f"the step brings {len(entries)} requests, max_num_seqs is {self.max_num_seqs}")
         decode_only = all(e.count == 1 for e in entries)
         if self.use_cuda_graphs and decode_only:
-            logits = self._graph_step(entries)
+            logits = self._graph_step(entries, device_tokens)
         else:
-            layout = self._pack(entries)
+            layout = self._pack(entries, device_tokens=device_tokens)
             ctx = self._context(layout, self.runtime.workspace)
             logits = self.model.forward(ctx, self.cache)
         if self.check_status:
@@ -156,14 +162,14 @@ class ModelRunner:
             b *= 2
         return min(b, max(self.max_num_seqs, n))
 
-    def _graph_step(self, entries):
+    def _graph_step(self, entries, device_tokens=None):
         bucket = self._bucket(len(entries))
         graph = self._graphs.get(bucket)
         if graph is None:
             graph = _DecodeGraph(self, bucket, entries)
             self._graphs[bucket] = graph
         self.num_graph_steps += 1
-        logits = graph.run(entries)
+        logits = graph.run(entries, device_tokens)
         rows = [i for i, e in enumerate(entries) if len(e.want)]
         if not rows:
             return None
@@ -187,9 +193,9 @@ class _DecodeGraph:
         self.graph = None
         self.logits = None
 
-    def run(self, entries):
+    def run(self, entries, device_tokens=None):
         r = self.runner
-        layout = r._pack(entries, pad_requests=self.bucket, fixed=True, all_wanted=True)
+        layout = r._pack(entries, pad_requests=self.bucket, fixed=True, all_wanted=True, device_tokens=device_tokens)
         if r._capacity != self.capacity_at_capture:
             raise RuntimeError("the integer buffer moved after a decode graph was captured")
         if self.graph is None:

@@ -19,7 +19,10 @@ class Sampler:
     def __init__(self, device, max_rows: int):
         self.device = device
         self.max_rows = max_rows
-        self._host = torch.empty((max_rows, 6), dtype=torch.int32, pin_memory=True)
+        # A ring of pinned buffers: the copy to the device runs when the device gets to it, which may be after
+        # the next call has been made (the engine launches steps ahead of reading their results).
+        self._hosts = [(torch.empty((max_rows, 6), dtype=torch.int32, pin_memory=True), torch.cuda.Event()) for _ in range(4)]
+        self._host_at = 0
         self._dev = torch.empty((max_rows, 6), dtype=torch.int32, device=device)
         self._out = torch.empty(max_rows, dtype=torch.int32, device=device)
         self._scratch = None
@@ -36,7 +39,10 @@ class Sampler:
                 self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
             ops.argmax(out, logits, self._scratch)
             return out
-        host = self._host.numpy()
+        pinned, event = self._hosts[self._host_at]
+        self._host_at = (self._host_at + 1) % len(self._hosts)
+        event.synchronize()
+        host = pinned.numpy()
         f = host.view(np.float32)
         for i, p in enumerate(params):
             f[i, 0] = p.temperature
@@ -45,7 +51,8 @@ class Sampler:
             seed = int(p.seed) & 0xFFFFFFFFFFFFFFFF
             host[i, 3:5] = np.array([seed & 0xFFFFFFFF, seed >> 32], dtype=np.uint32).view(np.int32)
             host[i, 5] = token_indices[i]
-        self._dev[:n].copy_(self._host[:n], non_blocking=True)
+        self._dev[:n].copy_(pinned[:n], non_blocking=True)
+        event.record()
         d = self._dev[:n]
         cols = d.t().contiguous()  # [6, n]: each option contiguous
         temperature = cols[0].view(torch.float32)

@@ -96,6 +96,52 @@ def test_temperature_sampling_is_seeded_and_batch_independent(folders):
     assert other[0].output_tokens != together[0] and all(0 <= t < cfg["vocab_size"] for t in other[0].output_tokens)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_give_the_same_tokens(folders, dtype):
+    """The engine launches a decode step before it has read the tokens of the
+    step before (they pass on the device).  Same tokens, finish reasons and
+    number of step() calls as without; a request that stops at an
+    end-of-sequence token, one that arrives while others decode, one that is
+    aborted, greedy and seeded sampling."""
+    cfg, w, d32, d16 = folders["b"]
+    folder = d32 if dtype == "float32" else d16
+    prompts = [fixtures.random_ids(cfg, n, 300 + n) for n in (9, 17, 5, 12)]
+    free_run = plain_llama.plain_greedy_generate(cfg, w, prompts[0], 14)
+    raw = dict(cfg, eos_token_id=[free_run[6]])
+    import json
+    import shutil
+    import tempfile
+    runs = []
+    with tempfile.TemporaryDirectory() as d:
+        shutil.copy(os.path.join(folder, "model.safetensors"), d)
+        json.dump(raw, open(os.path.join(d, "config.json"), "w"))
+        for ahead in (False, True):
+            engine = LLMEngine.from_pretrained(d, dtype=dtype, num_blocks=64, block_size=8, max_num_seqs=4,
+                                               max_num_batched_tokens=32, lookahead=ahead)
+            engine.add_request("stops", prompts[0], SamplingParams(temperature=0.0, max_tokens=14))
+            engine.add_request("sampled", prompts[1], SamplingParams(temperature=0.8, top_p=0.9, max_tokens=20, ignore_eos=True, seed=5))
+            engine.add_request("aborted", prompts[2], SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True))
+            done, calls = {}, 0
+            while engine.has_unfinished_requests():
+                calls += 1
+                if calls == 6:
+                    engine.add_request("late", prompts[3], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+                if calls == 9:
+                    engine.abort_request("aborted")
+                for o in engine.step():
+                    if o.finished:
+                        done[o.request_id] = (o.output_tokens, o.finish_reason)
+                assert calls < 200
+            assert engine.block_manager.audit() == "" and engine.block_manager.get_num_free_blocks() == 64
+            runs.append((done, calls, engine.stats()["steps_ahead"]))
+    assert runs[0][0] == runs[1][0] and runs[0][1] == runs[1][1]
+    assert runs[0][2] == 0 and runs[1][2] >= 10
+    done = runs[1][0]
+    if dtype == "float32":
+        assert done["stops"] == (free_run[:free_run.index(free_run[6]) + 1], "stop")
+    assert len(done["sampled"][0]) == 20 and len(done["late"][0]) == 8 and done["late"][1] == "length"
+
+
 def test_command_line(folders):
     cfg, w, d32, _ = folders["a"]
     prompt = fixtures.random_ids(cfg, 9, 3)

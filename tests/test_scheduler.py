@@ -217,3 +217,59 @@ def test_random_load_with_few_pages_gives_the_same_tokens_as_no_pressure(seed):
         assert s.is_finished() and s.finish_reason() in ("stop", "length"), (s.get_seq_id(), s.finish_reason(), s.get_error())
         assert s.get_output_tokens() == expected[s.get_seq_id()]
     assert bm.get_num_free_blocks() == bm.get_num_blocks() and bm.get_num_free_state_slots() == bm.get_num_state_slots()
+
+
+def test_a_decode_step_is_scheduled_ahead_of_the_result_before_it():
+    """schedule_ahead builds the step after a launched decode step without its
+    tokens: one more token each, one step ahead; the results come back in order."""
+    sched, bm = make(block_size=4, eos=(99,))
+    a, b = seq(0, [1, 2, 3], max_tokens=6), seq(1, [4, 5, 6, 7, 8], max_tokens=6)
+    sched.add_sequence(a); sched.add_sequence(b)
+    first = sched.schedule()
+    assert first.is_prefill and not sched.schedule_ahead(first).entries          # prompts: nothing is known ahead
+    sched.post_step(first, [10, 20])
+    step1 = sched.schedule()
+    assert shape(step1) == [(0, 3, 1, [0]), (1, 5, 1, [0])]
+    ahead = sched.schedule_ahead(step1)                                          # before step1's tokens are known
+    assert [(e.seq.get_seq_id(), e.start, e.count, list(e.want), e.ahead) for e in ahead.entries] == \
+        [(0, 4, 1, [0], 1), (1, 6, 1, [0], 1)]
+    assert [s.get_seq_id() for s in ahead.sampled_seqs] == [0, 1] and not ahead.is_prefill
+    # the step packs although the host does not know its tokens: they come from the device
+    packed = host.pack_step(list(ahead.entries), bm, [16], 0, [], 0, 0)
+    assert packed.num_tokens == 2 and packed.max_context == 7
+    # pages for the token after next are there
+    assert len(a.get_block_table()) * 4 >= 5 and bm.audit() == ""
+    sched.post_step(step1, [11, 21])
+    again = sched.schedule_ahead(ahead)
+    assert [(e.start, e.ahead) for e in again.entries] == [(5, 1), (7, 1)]
+    sched.post_step(ahead, [12, 99])                                             # b ends with an end-of-sequence token
+    assert b.is_finished() and b.finish_reason() == "stop" and b.get_output_tokens() == [20, 21, 99]
+    sched.post_step(again, [13, 55])                                             # its token of the step ahead is dropped
+    assert b.get_output_tokens() == [20, 21, 99] and a.get_output_tokens() == [10, 11, 12, 13]
+    assert a.get_num_computed_tokens() == 6 and not a.is_finished()
+    sched.post_step(sched.schedule(), [14])
+    # a reaches max_tokens with the token that is still to come: that cannot be scheduled ahead
+    last = sched.schedule()
+    assert shape(last) == [(0, 7, 1, [0])] and not sched.schedule_ahead(last).entries
+    sched.post_step(last, [15])
+    assert a.is_finished() and a.finish_reason() == "length" and bm.get_num_free_blocks() == 100 and bm.audit() == ""
+
+
+def test_nothing_is_scheduled_ahead_of_an_admission_or_without_pages():
+    sched, bm = make(num_blocks=3, block_size=4, max_num_seqs=2)
+    a = seq(0, [1, 2, 3], max_tokens=50)
+    sched.add_sequence(a)
+    sched.post_step(sched.schedule(), [9])
+    sched.post_step(sched.schedule(), [9])
+    step = sched.schedule()
+    waiting = seq(1, [5, 6], max_tokens=2)
+    sched.add_sequence(waiting)
+    assert not sched.schedule_ahead(step).entries                                # a request waits to be admitted
+    sched.abort_sequence(1)
+    assert sched.schedule_ahead(step).entries
+    sched.post_step(step, [9])
+    # run a up to the end of its third and last page: the step after needs a fourth
+    while a.get_total_len() < 12:
+        sched.post_step(sched.schedule(), [9])
+    step = sched.schedule()
+    assert shape(step) == [(0, 11, 1, [0])] and not sched.schedule_ahead(step).entries and bm.audit() == ""
