@@ -222,9 +222,10 @@ def run_ours(args):
             print(json.dumps({"only": "decode", "batch": args.batch, "context": args.context or CONTEXT, "ms_per_step": round(ms, 4),
                               "layers": cfg["num_hidden_layers"], "cuda_graph": runner.use_cuda_graphs}))
         else:
-            ms = timed_prefill(PREFILL_TOKENS, args.steps, args.warmup)
-            print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(ms, 4),
-                              "layers": cfg["num_hidden_layers"]}))
+            tokens = args.tokens or PREFILL_TOKENS
+            ms = timed_prefill(tokens, args.steps, args.warmup)
+            print(json.dumps({"only": "prefill", "tokens": tokens, "ms": round(ms, 4), "layers": cfg["num_hidden_layers"],
+                              "tflops": round(prefill_flops(cfg, tokens) / (ms * 1e-3) / 1e12, 1)}))
         return 0
 
     clocks = ClockSampler()
@@ -435,6 +436,7 @@ def main():
     p.add_argument("--only", choices=["decode", "prefill"], default=None, help="run one kind of step and exit (for profilers)")
     p.add_argument("--batch", type=int, default=8, help="batch of --only decode")
     p.add_argument("--page", type=int, default=BLOCK_SIZE, help="tokens per page of the cache")
+    p.add_argument("--tokens", type=int, default=0, help="with --only prefill: tokens of the prompt (at most 4096)")
     p.add_argument("--context", type=int, default=0, help="with --only decode: the context the last step ends at")
     p.add_argument("--no-cuda-graphs", action="store_true", help="with --only decode: launch every kernel by itself")
     args = p.parse_args()

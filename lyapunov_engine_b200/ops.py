@@ -143,8 +143,8 @@ _EXTRA_ATTENTION_SIGNATURES: dict[str, list] = {
 counters = {"own_kernels": 0, "library_products": 0}
 
 
-def _check(code: int, name: str, lib=None):
-    counters["own_kernels"] += 1
+def _check(code: int, name: str, lib=None, launches: int = 1):
+    counters["own_kernels"] += launches
     if code != 0:
         lib = lib or core()
         detail = ""
@@ -520,7 +520,8 @@ def attention_decode_bf16(out, scratch, q, q_stride, k_cache, v_cache, block_tab
                                         _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
                                         _ptr(ctx_before), _ptr(requests), num_requests, num_heads, num_kv_heads,
                                         page_size, k_cache.shape[0], int(window or 0), float(scale), num_splits,
-                                        _ptr(status), _stream()), "le_attention_decode_bf16", lib)
+                                        _ptr(status), _stream()), "le_attention_decode_bf16", lib,
+           launches=2 if num_splits > 1 else 1)       # the attention kernel and the merge
 
 
 def argmax_scratch_floats(num_rows: int, vocab: int) -> int:
@@ -535,7 +536,9 @@ def argmax(out: torch.Tensor, logits: torch.Tensor, scratch=None) -> None:
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and logits.stride(1) == 1
     if scratch is not None:
         assert scratch.dtype == torch.float32 and scratch.numel() >= argmax_scratch_floats(n, V)
-    _check(core().le_argmax(_ptr(out), _ptr(logits), n, V, logits.stride(0), _ptr(scratch), _stream()), "le_argmax")
+    two_stages = scratch is not None and (V + 4095) // 4096 >= 4
+    _check(core().le_argmax(_ptr(out), _ptr(logits), n, V, logits.stride(0), _ptr(scratch), _stream()), "le_argmax",
+           launches=2 if two_stages else 1)
 
 
 def sample(out, logits, temperature, top_p, top_k, seeds, uniforms=None, probs_out=None) -> None:
