@@ -17,9 +17,14 @@ class Workspace:
         self.device = device
         self.pin_old = pin_old
         self._buffers: dict[tuple, torch.Tensor] = {}
+        self._views: dict[tuple, torch.Tensor] = {}
         self._old: list[torch.Tensor] = []
 
     def get(self, name: str, shape, dtype) -> torch.Tensor:
+        # the same name, shape and type as before (every layer of a step, every step of a decode): the same view
+        view = self._views.get((name, shape, dtype)) if type(shape) is tuple else None
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= int(s)
@@ -30,7 +35,11 @@ class Workspace:
                 self._old.append(buf)
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._buffers[key] = buf
-        return buf[:n].view(*shape)
+            self._views = {k: v for k, v in self._views.items() if (k[0], k[2]) != key}   # they point into the old storage
+        view = buf[:n].view(*shape)
+        if type(shape) is tuple and len(self._views) < 4096:
+            self._views[(name, shape, dtype)] = view
+        return view
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
