@@ -342,7 +342,7 @@ def run_reference(args):
 def reference_unavailable() -> str:
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "lyapunov_engine")):
-        return "IanConery/lyapunov-engine is not installed under baseline/_ref (see DESIGN.md, reference arm)"
+        return "IanConery/lyapunov-engine is not installed under baseline/_ref (pip install --no-index --target baseline/_ref of the reference)"
     if not any(f.startswith("_C") and f.endswith(".so") for f in os.listdir(os.path.join(ref, "lyapunov_engine"))):
         return "the reference was installed without its CUDA extension; its engine then returns nothing from step()"
     return ""
