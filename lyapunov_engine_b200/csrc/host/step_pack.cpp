@@ -143,6 +143,17 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
         if ((pass == 0) != (count > 1)) continue;
         for (int q0 = 0; q0 < count; q0 += tile_sizes[k]) { tr[n] = b; tq[n] = q0; ++n; }
       }
+      if (pass == 0 && n > 1) {
+        // Tiles of several tokens in the order of the keys they see, fewest first: the attention kernels walk
+        // the list from its end, so that the longest tiles of a step start first whatever request they are of.
+        std::vector<int> order(static_cast<size_t>(n));
+        for (int i = 0; i < n; ++i) order[static_cast<size_t>(i)] = i;
+        auto keys_seen = [&](int i) { return entries[static_cast<size_t>(tr[i])].start + tq[i] + tile_sizes[k]; };
+        std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return keys_seen(x) < keys_seen(y); });
+        std::vector<int32_t> r2(static_cast<size_t>(n)), q2(static_cast<size_t>(n));
+        for (int i = 0; i < n; ++i) { r2[static_cast<size_t>(i)] = tr[order[static_cast<size_t>(i)]]; q2[static_cast<size_t>(i)] = tq[order[static_cast<size_t>(i)]]; }
+        for (int i = 0; i < n; ++i) { tr[i] = r2[static_cast<size_t>(i)]; tq[i] = q2[static_cast<size_t>(i)]; }
+      }
     }
   }
   return p;

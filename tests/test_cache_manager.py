@@ -191,8 +191,10 @@ def test_pack_step_layout():
     assert table[0].tolist() == a.get_block_table() + [20] * 4 and table[1].tolist() == b.get_block_table() + [20] * 5
     assert table[2].tolist() == [20] * 6                       # padding writes to the page nobody owns
     assert p.num_tiles == [5, 4] and p.num_tiles_multi == [3, 2] and p.num_decode == 2
-    assert buf[p.off_tile_request[0]:p.off_tile_request[0] + 5].tolist() == [0, 1, 1, 2, 3]
-    assert buf[p.off_tile_q0[0]:p.off_tile_q0[0] + 5].tolist() == [0, 0, 2, 0, 0]
+    # tiles of several tokens by the keys they see, fewest first (the kernels start from the end); then single tokens
+    assert buf[p.off_tile_request[0]:p.off_tile_request[0] + 5].tolist() == [1, 1, 0, 2, 3]
+    assert buf[p.off_tile_q0[0]:p.off_tile_q0[0] + 5].tolist() == [0, 2, 0, 0, 0]
+    assert buf[p.off_tile_request[1]:p.off_tile_request[1] + 4].tolist() == [1, 0, 2, 3]
     assert buf[p.off_decode_requests:p.off_decode_requests + 2].tolist() == [2, 3]
     # single-token requests come after the others in the tile lists
     c = host.Sequence(2, [1, 2, 3], host.SamplingParams())
