@@ -142,6 +142,47 @@ def test_steps_launched_ahead_give_the_same_tokens(folders, dtype):
     assert len(done["sampled"][0]) == 20 and len(done["late"][0]) == 8 and done["late"][1] == "length"
 
 
+@pytest.mark.parametrize("seed", [0, 2, 3, 8])
+def test_random_traffic_with_and_without_steps_ahead(folders, seed):
+    """Random arrivals, lengths, sampling options, end-of-sequence tokens,
+    aborts and page pools small enough to pre-empt: the same tokens and finish
+    reasons whether or not steps are launched ahead.  float32, whose logits do
+    not depend on what else is in a batch, so every token must agree."""
+    import json
+    import random
+    import shutil
+    import tempfile
+    cfg, w, d32, _ = folders["b"]
+    results = []
+    with tempfile.TemporaryDirectory() as d:
+        shutil.copy(os.path.join(d32, "model.safetensors"), d)
+        json.dump(dict(cfg, eos_token_id=[3, 4, 77, 120, 301]), open(os.path.join(d, "config.json"), "w"))
+        for ahead in (False, True):
+            rng = random.Random(seed)
+            engine = LLMEngine.from_pretrained(d, dtype="float32", num_blocks=rng.choice([12, 20, 48]), block_size=8, max_num_seqs=4,
+                                               max_num_batched_tokens=rng.choice([16, 48]), lookahead=ahead, max_model_len=160)
+            plan = [(rng.randint(0, 60), f"r{i}", fixtures.random_ids(cfg, rng.randint(1, 40), seed * 100 + i),
+                     SamplingParams(temperature=rng.choice([0.0, 0.0, 0.7]), top_p=rng.choice([1.0, 0.9]), top_k=rng.choice([-1, 20]),
+                                    max_tokens=rng.randint(1, 30), ignore_eos=rng.random() < 0.3, seed=i)) for i in range(14)]
+            aborts = {rng.randint(5, 70): f"r{rng.randint(0, 13)}" for _ in range(3)}
+            done, call = {}, 0
+            while call < 2000 and (call <= 70 or engine.has_unfinished_requests()):
+                call += 1
+                for when, rid, prompt, sp in plan:
+                    if when == call:
+                        engine.add_request(rid, prompt, sp)
+                if call in aborts:
+                    engine.abort_request(aborts[call])
+                for o in engine.step():
+                    if o.finished:
+                        done[o.request_id] = (tuple(o.output_tokens), o.finish_reason)
+            assert engine.block_manager.audit() == "" and not engine.has_unfinished_requests()
+            results.append((done, engine.stats()))
+    assert results[0][0] == results[1][0] and len(results[0][0]) >= 11
+    assert results[0][1]["steps_ahead"] == 0 and results[1][1]["steps_ahead"] > 0
+    assert results[0][1]["preemptions"] == results[1][1]["preemptions"]
+
+
 def test_command_line(folders):
     cfg, w, d32, _ = folders["a"]
     prompt = fixtures.random_ids(cfg, 9, 3)
