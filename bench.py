@@ -34,6 +34,12 @@ LLAMA_1B = {
     "tie_word_embeddings": True, "hidden_act": "silu", "attention_bias": False, "mlp_bias": False,
     "bos_token_id": 128000, "eos_token_id": 128001, "torch_dtype": "bfloat16",
 }
+# The same architecture at the sizes of Llama-3.2-3B and Llama-3.1-8B, for --only runs at further sizes.
+LLAMA_3B = dict(LLAMA_1B, hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, head_dim=128)
+LLAMA_8B = dict(LLAMA_1B, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, head_dim=128,
+                tie_word_embeddings=False,
+                rope_scaling=dict(LLAMA_1B["rope_scaling"], factor=8.0))
+SHAPES = {"1b": LLAMA_1B, "3b": LLAMA_3B, "8b": LLAMA_8B}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 BLOCK_SIZE = 16
@@ -107,7 +113,7 @@ def decode_bytes(cfg, batch, context):
     H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
     nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     per_layer = (nh + 2 * nkv) * hd * H + H * nh * hd + 2 * I * H + H * I
-    weights = 2 * (L * per_layer + V * H) + 4 * (2 * L + 1) * H
+    weights = 2 * (L * per_layer + V * H) + 4 * (2 * L + 1) * H   # the head's table; the embedding reads `batch` rows
     kv = 2 * batch * context * 2 * nkv * hd * L
     return weights + kv
 
@@ -122,21 +128,23 @@ def prefill_flops(cfg, tokens):
 
 
 def run_ours(args):
-    global BLOCK_SIZE
+    global BLOCK_SIZE, CONTEXT
     import torch
     BLOCK_SIZE = args.page
+    if args.only and args.context:
+        CONTEXT = args.context
 
     from lyapunov_engine_b200 import EngineConfig, LLMEngine, SamplingParams, build, load_model, ops
 
-    cfg = dict(LLAMA_1B)
+    cfg = dict(SHAPES[args.shapes if args.only else "1b"])
     layers_full = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     pk = peaks()
     torch.cuda.set_device(0)
     host = build.load_host()
-    max_batch = 64
-    num_blocks = (max_batch * (CONTEXT + 64) + 2 * PREFILL_TOKENS) // BLOCK_SIZE
+    max_batch = 64 + (args.only == "mixed")   # the prompt beside 64 decoding requests holds a state slot too
+    num_blocks = (max_batch * (CONTEXT + 64) + 2 * PREFILL_TOKENS + CONTEXT) // BLOCK_SIZE
     loaded = load_model(config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", max_model_len=CONTEXT + 64)
     engine = LLMEngine(loaded, EngineConfig(num_blocks=num_blocks, block_size=BLOCK_SIZE, max_num_seqs=max_batch,
                                             max_num_batched_tokens=8192, dtype="bfloat16", device="cuda:0",
@@ -213,19 +221,93 @@ def run_ours(args):
         best.sort()
         return best[len(best) // 2]
 
+    def timed_mixed(batch, steps, warmup, context_end, chunk):
+        """K steps of `batch` decoding requests beside one `chunk`-token
+        portion of a prompt (a new prompt starts when one is through)."""
+        start_len = context_end - (steps + warmup)
+        seqs = []
+        for i in range(batch):
+            ids = torch.randint(0, vocab, (start_len + 1,), generator=gen).tolist()
+            s = host.Sequence(30_000 + i, ids, host.SamplingParams())
+            assert manager.grow(s, start_len)
+            s.set_num_computed_tokens(start_len)
+            seqs.append(s)
+        prompt_len = context_end // chunk * chunk
+        state = {"prompt": None, "made": 0, "keys": 0}
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+        def one_step(count):
+            if state["prompt"] is None:
+                ids = torch.randint(0, vocab, (prompt_len,), generator=gen).tolist()
+                state["prompt"] = host.Sequence(40_000 + state["made"], ids, host.SamplingParams())
+                state["made"] += 1
+            pr = state["prompt"]
+            done = pr.get_num_computed_tokens()
+            assert manager.grow(pr, done + chunk)
+            entries = [host.StepEntry(pr, done, chunk, [chunk - 1])]
+            for s in seqs:
+                n = s.get_num_computed_tokens()
+                assert manager.grow(s, n + 1)
+                entries.append(host.StepEntry(s, n, 1, [0]))
+            logits = runner.step(entries)
+            sampler.sample(logits, [greedy] * (batch + 1), [0] * (batch + 1))
+            if count:   # keys that the step's queries read: the portion's causal triangle and every decode context
+                state["keys"] += chunk * done + chunk * (chunk + 1) // 2 + sum(s.get_num_computed_tokens() + 1 for s in seqs)
+            for s in seqs:
+                s.set_num_computed_tokens(s.get_num_computed_tokens() + 1)
+                s.extend_prompt([1])
+            pr.set_num_computed_tokens(done + chunk)
+            if done + chunk >= prompt_len:
+                manager.free(pr)
+                state["prompt"] = None
+
+        for _ in range(warmup):
+            one_step(False)
+        torch.cuda.synchronize()
+        begin.record()
+        for _ in range(steps):
+            one_step(True)
+        end.record()
+        torch.cuda.synchronize()
+        ms = begin.elapsed_time(end) / steps
+        for s in seqs:
+            manager.free(s)
+        if state["prompt"] is not None:
+            manager.free(state["prompt"])
+        return ms, state["keys"] / steps
+
     if args.only:
         # A short run of one kind of step, for profilers: no CUDA graph, so
         # that every kernel shows as its own launch.
         runner.use_cuda_graphs = not args.no_cuda_graphs
         if args.only == "decode":
             ms, _, _ = timed_decode(args.batch, args.steps, args.warmup, args.context or CONTEXT)
-            print(json.dumps({"only": "decode", "batch": args.batch, "context": args.context or CONTEXT, "ms_per_step": round(ms, 4),
+            nbytes = decode_bytes(cfg, args.batch, (args.context or CONTEXT) - (args.steps - 1) // 2)
+            print(json.dumps({"only": "decode", "shapes": args.shapes, "batch": args.batch, "context": args.context or CONTEXT,
+                              "ms_per_step": round(ms, 4), "tokens_per_s": round(args.batch * 1000.0 / ms, 1),
+                              "hbm_frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
                               "layers": cfg["num_hidden_layers"], "cuda_graph": runner.use_cuda_graphs}))
+        elif args.only == "mixed":
+            chunk = args.tokens or PREFILL_TOKENS
+            ms, keys = timed_mixed(args.batch, args.steps, args.warmup, CONTEXT, chunk)
+            H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+            nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+            per_layer = (nh + 2 * nkv) * hd * H + H * nh * hd + 3 * I * H
+            flops = 2 * (chunk + args.batch) * L * per_layer + 2 * (args.batch + 1) * cfg["vocab_size"] * H + 4 * nh * hd * keys * L
+            nbytes = decode_bytes(cfg, args.batch, CONTEXT - (args.steps - 1) // 2)
+            print(json.dumps({"only": "mixed", "shapes": args.shapes, "decoding": args.batch, "portion": chunk, "context": CONTEXT,
+                              "ms_per_step": round(ms, 4), "tokens_per_s": round((args.batch + chunk) * 1000.0 / ms, 1),
+                              "layers": cfg["num_hidden_layers"],
+                              "tflops": round(flops / (ms * 1e-3) / 1e12, 1),
+                              "flops_frac": round(flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], 4),
+                              "hbm_frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}))
         else:
             tokens = args.tokens or PREFILL_TOKENS
             ms = timed_prefill(tokens, args.steps, args.warmup)
-            print(json.dumps({"only": "prefill", "tokens": tokens, "ms": round(ms, 4), "layers": cfg["num_hidden_layers"],
-                              "tflops": round(prefill_flops(cfg, tokens) / (ms * 1e-3) / 1e12, 1)}))
+            print(json.dumps({"only": "prefill", "shapes": args.shapes, "tokens": tokens, "ms": round(ms, 4),
+                              "layers": cfg["num_hidden_layers"],
+                              "tflops": round(prefill_flops(cfg, tokens) / (ms * 1e-3) / 1e12, 1),
+                              "flops_frac": round(prefill_flops(cfg, tokens) / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)}))
         return 0
 
     clocks = ClockSampler()
@@ -433,10 +515,13 @@ def main():
     p.add_argument("--warmup", type=int, default=16)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    p.add_argument("--only", choices=["decode", "prefill"], default=None, help="run one kind of step and exit (for profilers)")
+    p.add_argument("--only", choices=["decode", "prefill", "mixed"], default=None,
+                   help="run one kind of step and exit (for profilers and for further sizes); mixed = --batch decoding "
+                        "requests beside one --tokens portion of a prompt in every step")
+    p.add_argument("--shapes", choices=sorted(SHAPES), default="1b", help="with --only: layer sizes of Llama-3.2-1B, 3.2-3B or 3.1-8B")
     p.add_argument("--batch", type=int, default=8, help="batch of --only decode")
     p.add_argument("--page", type=int, default=BLOCK_SIZE, help="tokens per page of the cache")
-    p.add_argument("--tokens", type=int, default=0, help="with --only prefill: tokens of the prompt (at most 4096)")
+    p.add_argument("--tokens", type=int, default=0, help="with --only prefill or mixed: tokens of the prompt or of its portion (at most the context and 8192)")
     p.add_argument("--context", type=int, default=0, help="with --only decode: the context the last step ends at")
     p.add_argument("--no-cuda-graphs", action="store_true", help="with --only decode: launch every kernel by itself")
     args = p.parse_args()

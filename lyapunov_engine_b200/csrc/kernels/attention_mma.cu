@@ -594,27 +594,59 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
 }
 
 // out[request, head] = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s
+// The first warp turns the splits' (m_s, l_s) into weights, lanes side by side; then every thread adds its
+// column of the partial outputs with loads that do not wait for one another.
+constexpr int MERGE_MAX_SPLITS = 1024;
 __global__ void attention_merge_kernel(bf16 *__restrict__ out, int64_t out_stride, const float *__restrict__ part_o,
                                        const float *__restrict__ part_ml, const int32_t *__restrict__ cu_q,
                                        const int32_t *__restrict__ requests, int num_heads, int num_splits) {
+  extern __shared__ float merge_weight[];          // [num_splits], then the reciprocal of the sum
   le::let_successor_start();
   le::wait_for_predecessor();
   const int head = blockIdx.x, z = blockIdx.y;
   const int b = requests ? requests[z] : z;
   const int tok = cu_q[b];
   const int64_t base = (static_cast<int64_t>(z) * num_heads + head) * num_splits;
-  float m = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-    float acc = 0.0f, l = 0.0f;
-    for (int s = 0; s < num_splits; ++s) {
-      const float ms = part_ml[(base + s) * 2];
-      if (ms == -INFINITY) continue;
-      const float f = le::fast_exp2(ms - m);
-      acc += f * part_o[(base + s) * HD + d];
-      l += f * part_ml[(base + s) * 2 + 1];
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    const float2 *ml = reinterpret_cast<const float2 *>(part_ml) + base;
+    float m = -INFINITY;
+    for (int s = lane; s < num_splits; s += 32) m = fmaxf(m, ml[s].x);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float l = 0.0f;
+    for (int s = lane; s < num_splits; s += 32) {
+      const float2 v = ml[s];
+      const float f = v.x == -INFINITY ? 0.0f : le::fast_exp2(v.x - m);
+      merge_weight[s] = f;
+      l += f * v.y;
     }
-    out[tok * out_stride + head * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) merge_weight[num_splits] = l > 0.0f ? 1.0f / l : 0.0f;
+  }
+  __syncthreads();
+  const float inv_l = merge_weight[num_splits];
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    const float *col = part_o + base * HD + d;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    int s = 0;
+    for (; s + 4 <= num_splits; s += 4) {
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = col[static_cast<int64_t>(s + u) * HD];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float f = merge_weight[s + u];
+        acc[u] += f != 0.0f ? f * v[u] : 0.0f;     // a split without keys left its row unwritten
+      }
+    }
+    for (; s < num_splits; ++s) {
+      const float f = merge_weight[s];
+      const float v = col[static_cast<int64_t>(s) * HD];
+      acc[0] += f != 0.0f ? f * v : 0.0f;
+    }
+    out[tok * out_stride + head * HD + d] = __float2bfloat16_rn(((acc[0] + acc[1]) + (acc[2] + acc[3])) * inv_l);
   }
 }
 
@@ -665,8 +697,9 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
                                     int window, float scale, int num_splits, int *status, cudaStream_t stream) {
   if (num_requests <= 0) return 0;
   if (num_kv_heads <= 0 || num_heads % num_kv_heads) return le::invalid("le_attention_decode_bf16: %d heads do not divide into %d groups", num_heads, num_kv_heads);
-  if (num_splits < 1 || num_splits > 65535) return le::invalid("le_attention_decode_bf16: %d splits", num_splits);
+  if (num_splits < 1 || num_splits > MERGE_MAX_SPLITS) return le::invalid("le_attention_decode_bf16: %d splits (1..%d)", num_splits, MERGE_MAX_SPLITS);
   if (num_splits > 1 && scratch == nullptr) return le::invalid("le_attention_decode_bf16: splitting the keys needs scratch memory");
+  if (reinterpret_cast<uintptr_t>(scratch) % 8) return le::invalid("le_attention_decode_bf16: the scratch memory must start on an 8-byte boundary");
   const int group = num_heads / num_kv_heads;
   const int row_tiles = (group + 15) / 16;
   if (num_kv_heads * row_tiles > 65535 || num_requests > 65535) return le::invalid("le_attention_decode_bf16: the batch is too large for one launch");
@@ -686,7 +719,8 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
                               num_kv_heads, page_size, page_shift_of(page_size), num_pages, window, scale, num_splits, status);
   if (rc != 0 || num_splits == 1) return rc;
   dim3 mgrid(num_heads, num_requests);
-  return le::launch_chained(attention_merge_kernel, mgrid, dim3(HD < 32 ? 32 : (HD > 128 ? 128 : HD)), 0, stream,
+  return le::launch_chained(attention_merge_kernel, mgrid, dim3(HD < 32 ? 32 : (HD > 128 ? 128 : HD)),
+                            (static_cast<size_t>(num_splits) + 1) * sizeof(float), stream,
                             static_cast<bf16 *>(out), out_stride, static_cast<const float *>(part_o),
                             static_cast<const float *>(part_ml), cu_q, requests, num_heads, num_splits);
 }
