@@ -4,7 +4,6 @@ sizes in steps of 16, and inputs made so that one far key decides the result."""
 import pytest
 import torch
 
-import plain_llama
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -52,7 +51,6 @@ def build_case(dtype, nh, nkv, hd, page, q_lens, ctx_before, seed, window=None, 
             p = ctx_before[b] + j
             lo = max(0, p - window + 1) if window else 0
             qq = q[t0 + j].float().view(nh, 1, hd)
-            o = plain_llama.plain_attention(qq, ks[b][:, lo:p + 1], vs[b][:, lo:p + 1]) if False else None
             # plain attention of one query over its visible keys (no mask needed)
             kk = ks[b][:, lo:p + 1].repeat_interleave(nh // nkv, 0)
             vv = vs[b][:, lo:p + 1].repeat_interleave(nh // nkv, 0)
