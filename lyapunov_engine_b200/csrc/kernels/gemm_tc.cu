@@ -21,6 +21,19 @@
 // two accumulators in tensor memory, so the epilogue of a tile overlaps the
 // products of the next.
 //
+// PAIR form: two blocks on neighbouring SMs (a cluster of two) compute one
+// 256 x 256 tile with tcgen05.mma.cta_group::2.  Each block loads its own 128
+// rows of x and half of the tile's 256 rows of W (in the gated form the first
+// block the gate rows, the second the up rows), so a stage is 32 KB a block
+// instead of 48 and six stages fit where four did; the first block's thread
+// issues every MMA, which reads W from both blocks' shared memory and writes
+// each block's 128 rows of the accumulator into that block's tensor memory.
+// Barriers: a stage's "full" barrier lives in the first block and counts both
+// blocks' copies; "empty" and "accumulator full" are signalled in both blocks
+// by one multicast commit; the epilogue warps of both blocks arrive on the
+// first block's "accumulator empty".  The blocks meet at a cluster barrier
+// before anything remote is touched and before either leaves.
+//
 // Every wait on an mbarrier is bounded: when a limit runs out the block sets
 // the status word (LE_STATUS_WAIT_TIMEOUT), stops issuing work, lets what is in
 // flight land (again bounded), frees its tensor memory and returns.
@@ -38,17 +51,72 @@ constexpr int BK = 64;                 // 128 bytes of bfloat16: one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;           // producer warp, MMA warp, four epilogue warps
 
+// ---- a pair of blocks on one tile
+// Shared-memory addresses of a block in a cluster carry the block's rank; with this bit cleared an address names
+// the same offset in the pair's first block.
+constexpr uint32_t FIRST_OF_PAIR = 0xFEFFFFFFu;
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Every thread of both blocks arrives by itself (the roles leave their loops at different times, so warps
+// are not converged here).
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_first(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(smem_u32(bar) & FIRST_OF_PAIR), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_first(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & FIRST_OF_PAIR) : "memory");
+}
+// A tile into this block's shared memory; the bytes count on the first block's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(void *smem, const CUtensorMap *map, uint64_t *bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar) & FIRST_OF_PAIR), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives, when the MMAs issued so far are done, on the barrier at this offset in both blocks of the pair.
+__device__ __forceinline__ void tc_commit_pair(uint64_t *bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(both) : "memory");
+}
+
+// Tiles in the order the blocks take them: bands of eight tiles of rows, and within a band down the rows first.
+// What runs at one time then covers about as many tiles of W as of x (it reads the fewest distinct bytes),
+// however many rows x has.
+constexpr int BAND = 8;
+__device__ __forceinline__ void tile_position(int tile, int tiles_m, int tiles_n, int &m_idx, int &n_idx) {
+  const int band_tiles = BAND * tiles_n;
+  const int band = tile / band_tiles, within = tile - band * band_tiles;
+  const int first_m = band * BAND;
+  const int rows = min(BAND, tiles_m - first_m);
+  m_idx = first_m + within % rows;
+  n_idx = within / rows;
+}
+
 // BN: output columns of the MMA.  GATED: the BN-row operand is BN/2 gate rows
 // and their BN/2 up rows; a tile then has BN/2 output columns.  STAGES:
 // shared-memory stages.  The kernel is persistent: block b takes tiles b,
 // b + gridDim.x, ...; two accumulators in tensor memory alternate, so the
 // epilogue of one tile runs while the tensor core works on the next.
-template <int BN, bool GATED, typename TO, int STAGES>
+template <int BN, bool GATED, typename TO, int STAGES, bool PAIR>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO *__restrict__ out,
                int M, int N, int K, int64_t ldo, int up_row_offset, int tiles_m, int tiles_n, int *__restrict__ status) {
-  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  static_assert(!PAIR || BN == 256, "a pair of blocks computes 256 x 256 tiles");
+  constexpr int B_ROWS = PAIR ? BN / 2 : BN;         // rows of W in this block's stage
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = B_ROWS * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int N_TILE = GATED ? BN / 2 : BN;        // output columns per tile
+  constexpr int TILE_ROWS = PAIR ? 2 * BM : BM;      // output rows per tile
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
@@ -61,19 +129,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_k_tiles = (K + BK - 1) / BK;
   const int num_tiles = tiles_m * tiles_n;
+  const int rank = PAIR ? static_cast<int>(cluster_rank()) : 0;           // which block of the pair
+  const int first_tile = PAIR ? blockIdx.x >> 1 : blockIdx.x;
+  const int tile_step = PAIR ? gridDim.x >> 1 : gridDim.x;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(acc_full + a, 1); mbar_init(acc_empty + a, 4); }
+    // pair: both blocks' producers arrive on the first block's "full"; both blocks' epilogue warps on its "accumulator empty"
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, PAIR ? 2 : 1); mbar_init(empty + s, 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(acc_full + a, 1); mbar_init(acc_empty + a, PAIR ? 8 : 4); }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync();      // the other block's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -81,13 +159,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---- producer: one thread keeps the ring of stages full across all of this block's tiles
     if (lane == 0) {
       int issued = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !*failed; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * N_TILE;
+      for (int tile = first_tile; tile < num_tiles && !*failed; tile += tile_step) {
+        int m_idx, n_idx;
+        tile_position(tile, tiles_m, tiles_n, m_idx, n_idx);
+        const int m0 = m_idx * TILE_ROWS + rank * BM, n0 = n_idx * N_TILE;
         for (int kt = 0; kt < num_k_tiles; ++kt, ++issued) {
           const int s = issued % STAGES;
           const uint32_t phase = (issued / STAGES) & 1;
           if (*failed || !mbar_wait(empty + s, phase ^ 1, failed)) { *failed = 1; break; }
           unsigned char *a_dst = smem + s * STAGE_BYTES, *b_dst = a_dst + A_BYTES;
+          if constexpr (PAIR) {
+            // this block's rows of x and its half of the tile's rows of W; the bytes count in the first block
+            mbar_expect_tx_first(full + s, STAGE_BYTES);
+            tma_load_2d_pair(a_dst, &map_a, full + s, kt * BK, m0);
+            const int w_row = GATED ? (rank == 0 ? n0 : up_row_offset + n0) : n0 + rank * B_ROWS;
+            tma_load_2d_pair(b_dst, &map_b, full + s, kt * BK, w_row);
+            continue;
+          }
           mbar_expect_tx(full + s, STAGE_BYTES);
           tma_load_2d(a_dst, &map_a, full + s, kt * BK, m0);
           if (GATED) {
@@ -99,21 +187,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
       if (*failed) {
-        // let the copies already issued land before the block goes away
+        // let the copies already issued land before the block goes away (the second block of a pair cannot see
+        // the barrier they count on; it has waited out its own time limit by now, far longer than a copy takes)
         atomicOr(status, LE_STATUS_WAIT_TIMEOUT);
         volatile int never = 0;
-        for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(full + i % STAGES, (i / STAGES) & 1, &never);
+        if (rank == 0)
+          for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(full + i % STAGES, (i / STAGES) & 1, &never);
       }
     }
   } else if (warp == 1) {
     // ---- tensor-core issue
-    if (lane == 0) {
-      // instruction descriptor: F32 accumulate, BF16 x BF16, both K-major, N >> 3, M >> 4
+    if (lane == 0 && rank == 0) {
+      // instruction descriptor: F32 accumulate, BF16 x BF16, both K-major, N >> 3, M >> 4 (the pair's 256 rows)
       constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                                 (static_cast<uint32_t>(BM >> 4) << 24);
+                                 (static_cast<uint32_t>(TILE_ROWS >> 4) << 24);
       int consumed = 0, local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local) {
         const int acc = local & 1;
         // the epilogue must have drained this accumulator (two tiles ago)
         if (*failed || !mbar_wait(acc_empty + acc, ((local >> 1) & 1) ^ 1, failed)) { ok = false; break; }
@@ -128,11 +218,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t da = smem_desc(a_addr + k * UMMA_K * 2), db = smem_desc(b_addr + k * UMMA_K * 2);
-            tc_mma(tmem_acc, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+            if constexpr (PAIR) tc_mma_pair(tmem_acc, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+            else tc_mma(tmem_acc, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
           }
-          tc_commit(empty + s);          // arrives when the MMAs above have read the stage
+          // arrives when the MMAs above have read the stage (pair: in both blocks)
+          if constexpr (PAIR) tc_commit_pair(empty + s);
+          else tc_commit(empty + s);
         }
-        if (ok) tc_commit(acc_full + acc);   // arrives when this tile's accumulator is complete
+        if (ok) {                        // arrives when this tile's accumulator is complete
+          if constexpr (PAIR) tc_commit_pair(acc_full + acc);
+          else tc_commit(acc_full + acc);
+        }
       }
       if (!ok) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
     }
@@ -140,8 +236,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---- epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. + 31, i.e. those rows of the tile
     const int quarter = warp & 3;
     int local = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * N_TILE;
+    for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++local) {
+      int m_idx, n_idx;
+      tile_position(tile, tiles_m, tiles_n, m_idx, n_idx);
+      const int m0 = m_idx * TILE_ROWS + rank * BM, n0 = n_idx * N_TILE;
       const int acc = local & 1;
       const int row = m0 + quarter * 32 + lane;
       bool ok = mbar_wait(acc_full + acc, (local >> 1) & 1, failed);
@@ -191,48 +289,92 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // this warp has read its part of the accumulator: hand it back to the tensor core
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty + acc);
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_first(acc_empty + acc);
+        else mbar_arrive(acc_empty + acc);
+      }
     }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync();      // neither block leaves, or frees tensor memory, while the other may still use it
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
   }
 }
 
-template <int BN, bool GATED, typename TO>
+int sm_count() {
+  static int cached = 0;
+  if (cached == 0) {
+    int dev = 0, count = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && count > 0) cached = count;
+    else cached = 148;
+  }
+  return cached;
+}
+
+// LYAPUNOV_TC_PAIR=0 keeps every product on single SMs.
+bool pairs_enabled() {
+  static const bool on = [] {
+    const char *env = getenv("LYAPUNOV_TC_PAIR");
+    return env == nullptr || env[0] != '0';
+  }();
+  return on;
+}
+
+template <int BN, bool GATED, typename TO, bool PAIR = false>
 int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int *status,
            cudaStream_t stream) {
-  constexpr int STAGES = BN == 256 ? 4 : 6;   // 192 KB either way: one persistent block per SM
-  constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
+  // 192 KB of stages either way: one persistent block per SM
+  constexpr int STAGES = PAIR ? 6 : (BN == 256 ? 4 : 6);
+  constexpr int W_ROWS = PAIR ? BN / 2 : BN;             // rows of W per block and stage
+  constexpr int STAGE_BYTES = (BM + W_ROWS) * BK * 2;
+  constexpr int TILE_ROWS = PAIR ? 2 * BM : BM;
   const size_t smem = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024 + 256;
   CUtensorMap map_a, map_b;
   int rc = tensor_map(&map_a, x, M, K, ldx, BM);
   if (rc != 0) return rc;
-  rc = tensor_map(&map_b, w, N, K, ldw, GATED ? BN / 2 : BN);
+  rc = tensor_map(&map_b, w, N, K, ldw, (GATED || PAIR) ? BN / 2 : BN);
   if (rc != 0) return rc;
-  auto kernel = gemm_tc_kernel<BN, GATED, TO, STAGES>;
+  auto kernel = gemm_tc_kernel<BN, GATED, TO, STAGES, PAIR>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return le::invalid("le_gemm_tc_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   const int n_out = GATED ? N / 2 : N;
   const int n_tile = GATED ? BN / 2 : BN;
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (n_out + n_tile - 1) / n_tile;
-  int sms = 148;
-  {
-    static int cached = 0;
-    if (cached == 0) {
-      int dev = 0, count = 0;
-      if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && count > 0) cached = count;
-      else cached = 148;
-    }
-    sms = cached;
-  }
+  const int tiles_m = (M + TILE_ROWS - 1) / TILE_ROWS, tiles_n = (n_out + n_tile - 1) / n_tile;
   const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
-  const int blocks = static_cast<int>(tiles < sms ? tiles : sms);
-  kernel<<<blocks, THREADS, smem, stream>>>(map_a, map_b, static_cast<TO *>(out), M, N, K, ldo, GATED ? N / 2 : 0, tiles_m,
-                                             tiles_n, status);
+  const int sms = sm_count();
+  cudaLaunchConfig_t config = {};
+  config.blockDim = dim3(THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if constexpr (PAIR) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    // as many pairs as the GPU holds at once (fewer than SMs / 2 where a pair does not fit into what is left of a GPC)
+    static int resident_pairs = 0;
+    if (resident_pairs == 0) {
+      config.gridDim = dim3(sms / 2 * 2);
+      int clusters = 0;
+      e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &config);
+      resident_pairs = (e == cudaSuccess && clusters > 0) ? clusters : sms / 2;
+      (void)cudaGetLastError();
+    }
+    const int pairs = static_cast<int>(tiles < resident_pairs ? tiles : resident_pairs);
+    config.gridDim = dim3(2 * pairs);
+  } else {
+    config.gridDim = dim3(static_cast<int>(tiles < sms ? tiles : sms));
+  }
+  e = cudaLaunchKernelEx(&config, kernel, map_a, map_b, static_cast<TO *>(out), M, N, K, ldo, GATED ? N / 2 : 0, tiles_m, tiles_n,
+                         status);
+  if (e != cudaSuccess) return le::invalid("le_gemm_tc_bf16: launch failed: %s", cudaGetErrorString(e));
   return le::launched();
 }
 
@@ -247,8 +389,12 @@ LE_API int le_gemm_tc_bf16(void *out, int out_dtype, const void *x, const void *
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) return le::invalid("le_gemm_tc_bf16: K (%d) and the leading dimensions must be multiples of 8", K);
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return le::invalid("le_gemm_tc_bf16: x and W must be 16-byte aligned");
+  // pairs of SMs on 256 x 256 tiles where those give at least half of the pairs a tile
+  const int64_t pair_tiles = static_cast<int64_t>((M + 2 * BM - 1) / (2 * BM)) * (((gated ? N / 2 : N) + (gated ? 127 : 255)) / (gated ? 128 : 256));
+  const bool pair = pairs_enabled() && pair_tiles >= 37;
   if (gated) {
     if (out_dtype != LE_BF16 || N % 2) return le::invalid("le_gemm_tc_bf16: the gated form has bfloat16 output and an even N");
+    if (pair) return launch<256, true, bf16, true>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);
     // a tile's 256 rows of W are 128 gate and 128 up rows; narrower tiles only where the wide ones would leave
     // more than half of the SMs without one (few rows of x: the product is bound by fetching W)
     const int64_t gated_tiles = static_cast<int64_t>((M + BM - 1) / BM) * ((N / 2 + 127) / 128);
@@ -260,6 +406,8 @@ LE_API int le_gemm_tc_bf16(void *out, int out_dtype, const void *x, const void *
   // of the SMs without a tile
   const int64_t tiles_m = (M + BM - 1) / BM;
   const bool wide = tiles_m * ((N + 255) / 256) >= 74;
+  if (pair && out_dtype == LE_BF16) return launch<256, false, bf16, true>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);
+  if (pair && out_dtype == LE_F32) return launch<256, false, float, true>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);
   if (out_dtype == LE_BF16)
     return wide ? launch<256, false, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream)
                 : launch<128, false, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);
