@@ -169,6 +169,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       fence_async_proxy();
     }
     __syncwarp();
+    // Launched as a dependent of the kernel before it (which wrote the queries and this step's keys and values):
+    // up to here the block overlapped that kernel's end; nothing of its output is read before this line, and
+    // every other role works on what this warp's copies bring.
+    le::wait_for_predecessor();
     // The first copies need nothing but the barriers: they start before tensor memory is set up and the block
     // meets, so the scores of tile 0 can follow the block's start closely.
     if (lane == 0) {
@@ -457,11 +461,9 @@ LE_API int le_attention_prefill_tc_bf16(void *out, int64_t out_stride, const voi
   const int group = num_heads / num_kv_heads;
   if (num_tiles > 65535) return le::invalid("le_attention_prefill_tc_bf16: %d tiles of queries are too many for one launch", num_tiles);
   dim3 grid(num_kv_heads * ((group + 1) / 2), num_tiles);   // two heads of a group per block
-  attention_tc_kernel<<<grid, THREADS, smem, stream>>>(map_q, map_k, map_v, static_cast<bf16 *>(out), out_stride, block_table,
-                                                       max_blocks, cu_q, ctx_before, tile_request, tile_q0, num_heads,
-                                                       num_kv_heads, page_size, tc_page_shift_of(page_size), num_pages, window,
-                                                       scale, status);
-  return le::launched();
+  return le::launch_chained(attention_tc_kernel, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, static_cast<bf16 *>(out),
+                            out_stride, block_table, max_blocks, cu_q, ctx_before, tile_request, tile_q0, num_heads,
+                            num_kv_heads, page_size, tc_page_shift_of(page_size), num_pages, window, scale, status);
 }
 
 #else
