@@ -89,7 +89,6 @@ rope_kv_vec_kernel(T *__restrict__ qkv, T *__restrict__ k_cache, T *__restrict__
     if (threadIdx.x == 0) atomicOr(status, LE_STATUS_BAD_POSITION);
     return;
   }
-  const int heads = num_heads + (write_kv ? 2 * num_kv_heads : 0);
   const int chunks = head_dim / VEC, half_chunks = rot / 2 / VEC, rot_chunks = rot / VEC;
   const int row = (num_heads + 2 * num_kv_heads) * head_dim;
   T *x_row = qkv + static_cast<int64_t>(t) * row;
@@ -105,32 +104,51 @@ rope_kv_vec_kernel(T *__restrict__ qkv, T *__restrict__ k_cache, T *__restrict__
   }
   const float *cs = cos_sin + static_cast<int64_t>(pos) * rot;
   const int half = rot / 2;
-  for (int item = threadIdx.x; item < heads * chunks; item += blockDim.x) {
-    const int h = item / chunks, c = item % chunks;
-    const bool is_q = h < num_heads;
-    const bool is_k = !is_q && h < num_heads + num_kv_heads;
-    T *x = x_row + static_cast<int64_t>(h) * head_dim;
-    T *dst = x;
-    if (!is_q) {
-      if (kv_base < 0) continue;
-      const int kvh = is_k ? h - num_heads : h - num_heads - num_kv_heads;
-      dst = (is_k ? k_cache : v_cache) + kv_base + static_cast<int64_t>(kvh) * page_size * head_dim;
-    }
-    if ((is_q || is_k) && c < rot_chunks) {
-      if (c >= half_chunks) continue;        // the partner chunk does both
-      const Vec16<T> lo = *reinterpret_cast<const Vec16<T> *>(x + c * VEC);
-      const Vec16<T> hi = *reinterpret_cast<const Vec16<T> *>(x + half + c * VEC);
-      Vec16<T> out_lo, out_hi;
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        const float x0 = le::to_f32(lo.v[i]), x1 = le::to_f32(hi.v[i]);
-        const float cc = cs[c * VEC + i], ss = cs[half + c * VEC + i];
-        out_lo.v[i] = le::from_f32<T>(x0 * cc - x1 * ss);
-        out_hi.v[i] = le::from_f32<T>(x1 * cc + x0 * ss);
+  // Work items, so that no thread idles: for every query and key head `half_chunks` pairs (a chunk of the low
+  // half with its partner of the high half) and the chunks beyond the rotary width; for every value head its
+  // chunks.  One pass of the block covers a token of the usual shapes, with every load in flight at once.
+  const int tail_chunks = chunks - rot_chunks;
+  const int per_qk = half_chunks + tail_chunks;
+  const int qk_items = (num_heads + (write_kv ? num_kv_heads : 0)) * per_qk;
+  const int items = qk_items + (write_kv ? num_kv_heads * chunks : 0);
+  for (int item = threadIdx.x; item < items; item += blockDim.x) {
+    if (item < qk_items) {
+      const int h = item / per_qk, j = item - h * per_qk;
+      const bool is_q = h < num_heads;
+      T *x = x_row + static_cast<int64_t>(h) * head_dim;
+      T *dst = x;
+      if (!is_q) {
+        if (kv_base < 0) continue;
+        dst = k_cache + kv_base + static_cast<int64_t>(h - num_heads) * page_size * head_dim;
       }
-      *reinterpret_cast<Vec16<T> *>(dst + c * VEC) = out_lo;
-      *reinterpret_cast<Vec16<T> *>(dst + half + c * VEC) = out_hi;
-    } else if (dst != x) {
+      if (j < half_chunks) {
+        const Vec16<T> lo = *reinterpret_cast<const Vec16<T> *>(x + j * VEC);
+        const Vec16<T> hi = *reinterpret_cast<const Vec16<T> *>(x + half + j * VEC);
+        float cc[VEC], ss[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; i += 4) {
+          *reinterpret_cast<float4 *>(cc + i) = *reinterpret_cast<const float4 *>(cs + j * VEC + i);
+          *reinterpret_cast<float4 *>(ss + i) = *reinterpret_cast<const float4 *>(cs + half + j * VEC + i);
+        }
+        Vec16<T> out_lo, out_hi;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          const float x0 = le::to_f32(lo.v[i]), x1 = le::to_f32(hi.v[i]);
+          out_lo.v[i] = le::from_f32<T>(x0 * cc[i] - x1 * ss[i]);
+          out_hi.v[i] = le::from_f32<T>(x1 * cc[i] + x0 * ss[i]);
+        }
+        *reinterpret_cast<Vec16<T> *>(dst + j * VEC) = out_lo;
+        *reinterpret_cast<Vec16<T> *>(dst + half + j * VEC) = out_hi;
+      } else if (dst != x) {
+        const int c = rot_chunks + j - half_chunks;
+        *reinterpret_cast<Vec16<T> *>(dst + c * VEC) = *reinterpret_cast<const Vec16<T> *>(x + c * VEC);
+      }
+    } else {
+      if (kv_base < 0) continue;
+      const int idx = item - qk_items;
+      const int kvh = idx / chunks, c = idx - kvh * chunks;
+      const T *x = x_row + static_cast<int64_t>(num_heads + num_kv_heads + kvh) * head_dim;
+      T *dst = v_cache + kv_base + static_cast<int64_t>(kvh) * page_size * head_dim;
       *reinterpret_cast<Vec16<T> *>(dst + c * VEC) = *reinterpret_cast<const Vec16<T> *>(x + c * VEC);
     }
   }
@@ -146,7 +164,7 @@ LE_API int le_rope_kv_write(void *qkv, int dtype, void *k_cache, void *v_cache, 
   if (rot < 0 || rot > head_dim || rot % 2) return le::invalid("le_rope_kv_write: rotary width %d must be even and at most head_dim %d", rot, head_dim);
   if (num_heads + 2 * num_kv_heads > 65535) return le::invalid("le_rope_kv_write: too many heads for one launch");
   const int vec = dtype == LE_BF16 ? 8 : 4;
-  if (head_dim % vec == 0 && (rot / 2) % vec == 0) {
+  if (head_dim % vec == 0 && (rot / 2) % vec == 0 && reinterpret_cast<uintptr_t>(cos_sin) % 16 == 0) {
     LE_DISPATCH_DTYPE(dtype, T,
                       return le::launch_chained(rope_kv_vec_kernel<T>, dim3(num_tokens), dim3(256), 0, stream,
                                                 static_cast<T *>(qkv), static_cast<T *>(k_cache), static_cast<T *>(v_cache),
