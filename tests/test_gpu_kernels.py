@@ -316,7 +316,7 @@ def test_norm_adds_partial_sums_in_order():
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 256), (200, 384, 136), (17, 515 - 3, 96), (1000, 1000, 328),
-                                   (2048, 3072, 2048), (130, 8, 8), (1100, 2600, 200), (2304, 4096, 136)])
+                                   (2048, 3072, 2048), (130, 8, 8), (1100, 2600, 200), (2304, 4096, 136), (129, 9600, 72)])
 def test_tensor_core_product(M, N, K):
     """The tcgen05 / TMA product against a float64 product of the same bfloat16 inputs."""
     o = ops()
