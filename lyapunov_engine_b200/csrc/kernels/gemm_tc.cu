@@ -105,9 +105,10 @@ __device__ __forceinline__ void tile_position(int tile, int tiles_m, int tiles_n
 
 // BN: output columns of the MMA.  GATED: the BN-row operand is BN/2 gate rows
 // and their BN/2 up rows; a tile then has BN/2 output columns.  STAGES:
-// shared-memory stages.  The kernel is persistent: block b takes tiles b,
-// b + gridDim.x, ...; two accumulators in tensor memory alternate, so the
-// epilogue of one tile runs while the tensor core works on the next.
+// shared-memory stages.  PAIR: two blocks (a cluster) per tile.  The kernel is
+// persistent: block (or pair) b takes tiles b, b + the number of blocks (or
+// pairs), ...; two accumulators in tensor memory alternate, so the epilogue of
+// one tile runs while the tensor core works on the next.
 template <int BN, bool GATED, typename TO, int STAGES, bool PAIR>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO *__restrict__ out,

@@ -293,7 +293,7 @@ def rotary_product_applies(a: torch.Tensor, w: torch.Tensor, head_dim: int, rot:
 
 def gemm_skinny_rotary(qkv, a, w, k_cache, v_cache, cos_sin, positions, request_of_token, block_table, num_heads,
                        num_kv_heads, head_dim, page_size, write_kv, status) -> None:
-    """The fused qkv projection of at most 16 rows with rotary encoding and
+    """The fused qkv projection of at most 64 rows with rotary encoding and
     cache write in its epilogue: rotated queries into ``qkv`` (its key and
     value columns are left alone), rotated keys and the values into the paged
     cache.  Same arithmetic and roundings as linear() then rope_kv_write()."""
