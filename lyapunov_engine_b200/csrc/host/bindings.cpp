@@ -173,11 +173,13 @@ PYBIND11_MODULE(_host, m) {
   m.def(
       "pack_step",
       [](const std::vector<StepEntry> &entries, const BlockSpaceManager &manager, const std::vector<int> &tile_sizes,
-         int pad_requests, const std::vector<int> &fixed_max_blocks, uintptr_t dest, int64_t capacity) {
-        return pack_step(entries, manager, tile_sizes, pad_requests, fixed_max_blocks, reinterpret_cast<int32_t *>(dest), capacity);
+         int pad_requests, const std::vector<int> &fixed_max_blocks, uintptr_t dest, int64_t capacity, int pad_first_to) {
+        return pack_step(entries, manager, tile_sizes, pad_requests, fixed_max_blocks, reinterpret_cast<int32_t *>(dest), capacity,
+                         pad_first_to);
       },
       py::arg("entries"), py::arg("manager"), py::arg("tile_sizes") = std::vector<int>{}, py::arg("pad_requests") = 0,
       py::arg("fixed_max_blocks") = std::vector<int>{}, py::arg("dest") = 0, py::arg("capacity") = 0,
+      py::arg("pad_first_to") = 0,
       "Writes the step's integers at address `dest` (room for `capacity` int32) and returns the layout.");
 
   m.def("set_log_level", [](const std::string &name) {

@@ -8,8 +8,10 @@ namespace lyapunov::host {
 
 PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceManager &manager,
                      const std::vector<int> &tile_sizes, int pad_requests,
-                     const std::vector<int> &fixed_max_blocks, int32_t *dest, int64_t capacity) {
+                     const std::vector<int> &fixed_max_blocks, int32_t *dest, int64_t capacity, int pad_first_to) {
   PackedStep p;
+  // rows entry i brings, dummy tokens after the first entry's own included
+  auto rows_of = [&](size_t i) { return i == 0 && pad_first_to > entries[0].count ? pad_first_to : entries[i].count; };
   const int groups = manager.get_num_groups();
   const int real = static_cast<int>(entries.size());
   const int B = std::max(real, pad_requests);
@@ -18,7 +20,9 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
   p.tile_sizes = tile_sizes;
 
   int T = 0;
-  for (const auto &e : entries) {
+  for (size_t i = 0; i < entries.size(); ++i) {
+    const auto &e = entries[i];
+    const int rows = rows_of(i);
     if (e.count < 1) throw std::invalid_argument("pack_step: an entry brings no token");
     if (e.ahead < 0 || e.ahead > 1) throw std::invalid_argument("pack_step: an entry is at most one step ahead");
     if (e.start != static_cast<int>(e.seq->get_num_computed_tokens()) + e.ahead)
@@ -29,10 +33,10 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
       throw std::invalid_argument("pack_step: an entry runs past the request's tokens");
     for (int32_t w : e.want)
       if (w < 0 || w >= e.count) throw std::invalid_argument("pack_step: a wanted place lies outside the entry's tokens");
-    T += e.count;
+    T += rows;
     p.num_wanted += static_cast<int>(e.want.size());
-    p.max_q_len = std::max(p.max_q_len, e.count);
-    p.max_context = std::max(p.max_context, e.start + e.count);
+    p.max_q_len = std::max(p.max_q_len, rows);
+    p.max_context = std::max(p.max_context, e.start + rows);
   }
   T += B - real;
   if (B > real) {
@@ -45,7 +49,7 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
   for (int g = 0; g < groups; ++g) {
     const int bs = manager.get_block_size(g);
     int need = 1;
-    for (const auto &e : entries) need = std::max(need, (e.start + e.count + bs - 1) / bs);
+    for (size_t i = 0; i < entries.size(); ++i) need = std::max(need, (entries[i].start + rows_of(i) + bs - 1) / bs);
     if (g < static_cast<int>(fixed_max_blocks.size()) && fixed_max_blocks[g] > 0) {
       if (need > fixed_max_blocks[g]) throw std::invalid_argument("pack_step: a request needs more pages than the fixed table width");
       need = fixed_max_blocks[g];
@@ -61,17 +65,20 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
   p.off_cu_q = take(B + 1);
   p.off_ctx_before = take(B);
   p.off_state_slots = take(B);
-  p.off_wanted_rows = take(std::max(p.num_wanted, 1));
+  // room for one row per request as well: a step of fixed shape asks for the logits of every row it has,
+  // dummy requests included, and writes that list here itself
+  p.off_wanted_rows = take(std::max({p.num_wanted, B, 1}));
   for (int g = 0; g < groups; ++g) p.off_block_tables.push_back(take(static_cast<int64_t>(B) * p.max_blocks[g]));
   p.num_decode = B - real;
-  for (const auto &e : entries) p.num_decode += e.count == 1;
+  for (size_t i = 0; i < entries.size(); ++i) p.num_decode += rows_of(i) == 1;
   p.off_decode_requests = take(std::max(p.num_decode, 1));
   for (int ts : tile_sizes) {
     if (ts < 1) throw std::invalid_argument("pack_step: tile sizes must be >= 1");
     int n = B - real, multi = 0;
-    for (const auto &e : entries) {
-      n += (e.count + ts - 1) / ts;
-      if (e.count > 1) multi += (e.count + ts - 1) / ts;
+    for (size_t i = 0; i < entries.size(); ++i) {
+      const int rows = rows_of(i);
+      n += (rows + ts - 1) / ts;
+      if (rows > 1) multi += (rows + ts - 1) / ts;
     }
     p.num_tiles.push_back(n);
     p.num_tiles_multi.push_back(multi);
@@ -90,7 +97,8 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
   for (int b = 0; b < B; ++b) {
     if (b < real) {
       const auto &e = entries[b];
-      for (int j = 0; j < e.count; ++j) {
+      const int rows = rows_of(static_cast<size_t>(b));
+      for (int j = 0; j < rows; ++j) {
         // (a token the host does not know yet is written by the device before the step runs)
         const size_t at = static_cast<size_t>(e.start + j);
         tok[t + j] = at < e.seq->get_total_len() ? e.seq->token_at(at) : 0;
@@ -100,7 +108,7 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
       for (int32_t x : e.want) want[w++] = t + x;
       ctx[b] = e.start;
       slots[b] = e.seq->get_state_slot();
-      t += e.count;
+      t += rows;
     } else {
       tok[t] = 0; pos[t] = 0; req[t] = b;
       ctx[b] = 0;
@@ -131,7 +139,7 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
     int32_t *dec = dest + p.off_decode_requests;
     int n = 0;
     for (int b = 0; b < B; ++b)
-      if ((b < real ? entries[b].count : 1) == 1) dec[n++] = b;
+      if ((b < real ? rows_of(static_cast<size_t>(b)) : 1) == 1) dec[n++] = b;
     if (n == 0) dec[0] = 0;
   }
   for (size_t k = 0; k < tile_sizes.size(); ++k) {
@@ -139,7 +147,7 @@ PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceMana
     int n = 0;
     for (int pass = 0; pass < 2; ++pass) {   // requests with several tokens first, then single tokens
       for (int b = 0; b < B; ++b) {
-        const int count = b < real ? entries[b].count : 1;
+        const int count = b < real ? rows_of(static_cast<size_t>(b)) : 1;
         if ((pass == 0) != (count > 1)) continue;
         for (int q0 = 0; q0 < count; q0 += tile_sizes[k]) { tr[n] = b; tq[n] = q0; ++n; }
       }

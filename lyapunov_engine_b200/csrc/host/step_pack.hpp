@@ -40,10 +40,16 @@ struct PackedStep {
 // start+count-1).  `pad_requests` > number of entries adds one-token dummy
 // requests that write to `null_pages[g]` (a page outside the manager's range)
 // so that the batch has a fixed shape; `fixed_max_blocks[g]` > 0 fixes the
-// width of group g's table.  Returns the layout; throws if `capacity` is too
-// small.  `dest` may be null to compute the layout only.
+// width of group g's table.  `pad_first_to` > the first entry's count lets
+// that entry bring dummy tokens after its own, up to that many rows: they
+// continue its positions, carry token 0 and write where the block table
+// points (the request's own last page, which its later tokens overwrite
+// before anyone reads them, and the page nobody owns beyond it), so a prompt
+// portion too can have a fixed shape.  Returns the layout; throws if
+// `capacity` is too small.  `dest` may be null to compute the layout only.
 PackedStep pack_step(const std::vector<StepEntry> &entries, const BlockSpaceManager &manager,
                      const std::vector<int> &tile_sizes, int pad_requests,
-                     const std::vector<int> &fixed_max_blocks, int32_t *dest, int64_t capacity);
+                     const std::vector<int> &fixed_max_blocks, int32_t *dest, int64_t capacity,
+                     int pad_first_to = 0);
 
 }  // namespace lyapunov::host

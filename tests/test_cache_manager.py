@@ -196,6 +196,17 @@ def test_pack_step_layout():
     assert buf[p.off_tile_q0[0]:p.off_tile_q0[0] + 5].tolist() == [0, 2, 0, 0, 0]
     assert buf[p.off_tile_request[1]:p.off_tile_request[1] + 4].tolist() == [1, 0, 2, 3]
     assert buf[p.off_decode_requests:p.off_decode_requests + 2].tolist() == [2, 3]
+    # a step padded to a fixed shape lists one wanted row per request, dummy requests included: there is room
+    assert p.off_block_tables[0] - p.off_wanted_rows >= p.num_requests
+    nine = []
+    for i in range(9):
+        s = host.Sequence(10 + i, [1, 2], host.SamplingParams())
+        bm.grow(s, 1); s.set_num_computed_tokens(1); bm.grow(s, 2)
+        nine.append(s)
+    p9 = host.pack_step([host.StepEntry(s, 1, 1, [0]) for s in nine], bm, [16], 16, [6], buf.ctypes.data, buf.size)
+    assert p9.num_requests == 16 and p9.off_block_tables[0] - p9.off_wanted_rows >= 16
+    for s in nine:
+        bm.free(s)
     # single-token requests come after the others in the tile lists
     c = host.Sequence(2, [1, 2, 3], host.SamplingParams())
     bm.grow(c, 2); c.set_num_computed_tokens(2); bm.grow(c, 3)

@@ -96,6 +96,24 @@ def test_temperature_sampling_is_seeded_and_batch_independent(folders):
     assert other[0].output_tokens != together[0] and all(0 <= t < cfg["vocab_size"] for t in other[0].output_tokens)
 
 
+@pytest.mark.parametrize("count", [3, 9, 11, 21])
+def test_decode_graphs_of_partly_filled_buckets(folders, count):
+    """Decode steps run as captured graphs of the next power-of-two batch; the
+    rows between the live requests and the bucket are dummies.  With 9 to 12
+    (or 17 to 28) live requests the list of wanted rows is longer than the
+    live requests' own, and must not reach into the block tables behind it:
+    every request's tokens equal the plain implementation's."""
+    cfg, w, d32, _ = folders["a"]
+    engine = LLMEngine.from_pretrained(d32, dtype="float32", num_blocks=count * 20, block_size=fixtures.TINY_A_PAGE,
+                                       max_num_seqs=32, max_num_batched_tokens=256)
+    prompts = [fixtures.random_ids(cfg, 21 + 2 * i, 700 + i) for i in range(count)]
+    outs = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    assert engine.stats()["graph_steps"] >= 5
+    for i in (0, 1, count - 1):
+        assert outs[i].output_tokens == plain_llama.plain_greedy_generate(cfg, w, prompts[i], 10), i
+    assert engine.block_manager.audit() == ""
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_steps_launched_ahead_give_the_same_tokens(folders, dtype):
     """The engine launches a decode step before it has read the tokens of the
