@@ -9,7 +9,11 @@ T = sum(count) rows.  The host sends one block of integers per step
 
 Steps that hold single decoded tokens only can run as a captured CUDA graph of
 fixed shape (the batch padded to the next bucket), which removes the launch
-cost of the ~10 kernels per layer.
+cost of the ~10 kernels per layer.  So can a step with one prompt portion of up
+to PROMPT_GRAPH_MAX_TOKENS tokens, alone or beside decoded tokens: the portion
+is padded with dummy tokens to a multiple of 64 (128 above 512) and the decoded
+tokens with dummy requests, which fixes every shape; launched one by one, such
+a step would be bound by the host (some 135 launches) rather than by the device.
 
 The reference's step (python/lyapunov_engine/engine/llm_engine.py:219-312)
 runs whole prompts one by one or one token per request, never a mix.
@@ -17,12 +21,25 @@ runs whole prompts one by one or one token per request, never a mix.
 from __future__ import annotations
 
 import gc
+import os
 
 import numpy as np
 import torch
 
 from .. import build, ops
 from ..parts import attention_kernels
+
+
+# Prompt portions of at most this many tokens run as captured graphs; longer ones keep the device busy for longer
+# than the host takes to launch them.  LYAPUNOV_PROMPT_GRAPHS=0 leaves them all to single launches.
+PROMPT_GRAPH_MAX_TOKENS = 1024
+PROMPT_GRAPHS = os.environ.get("LYAPUNOV_PROMPT_GRAPHS", "1") not in ("0", "")
+MAX_PROMPT_GRAPHS = 64
+
+
+def prompt_bucket(tokens: int) -> int:
+    step = 64 if tokens <= 512 else 128
+    return (tokens + step - 1) // step * step
 
 
 class StepContext:
@@ -51,6 +68,8 @@ class ModelRunner:
         self._ring_pos = 0
         self._device_ints = None
         self._graphs: dict[int, "_DecodeGraph"] = {}
+        self._prompt_graphs: dict[tuple, "_PromptGraph"] = {}
+        self._prompt_workspace = None
         self.num_steps = 0
         self.num_graph_steps = 0
         self._reserve(self._upper_bound(max_num_batched_tokens, max_num_seqs))
@@ -72,27 +91,33 @@ class ModelRunner:
             ev.record()
         self._device_ints = torch.empty(n, dtype=torch.int32, device=self.runtime.device)
         self._graphs.clear()  # they point into the old buffer
+        self._prompt_graphs.clear()
 
-    def _pack(self, entries, pad_requests=0, fixed=False, all_wanted=False, device_tokens=None):
+    def _pack(self, entries, pad_requests=0, fixed=False, all_wanted=False, device_tokens=None, pad_first_to=0,
+              wanted_rows=None):
         fixed_blocks = self.fixed_max_blocks if fixed else []
         pinned, event = self._ring[self._ring_pos]
         self._ring_pos = (self._ring_pos + 1) % len(self._ring)
         event.synchronize()
         try:
             layout = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks,
-                                         pinned.data_ptr(), self._capacity)
+                                         pinned.data_ptr(), self._capacity, pad_first_to)
         except ValueError:
             # more integers than the buffers hold (it does not happen within the limits given at construction):
             # size them for this step and pack again
-            need = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks, 0, 0).total
+            need = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks, 0, 0,
+                                       pad_first_to).total
             self._reserve(int(need * 1.5))
             pinned, event = self._ring[self._ring_pos]
             self._ring_pos = (self._ring_pos + 1) % len(self._ring)
             layout = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks,
-                                         pinned.data_ptr(), self._capacity)
+                                         pinned.data_ptr(), self._capacity, pad_first_to)
         if all_wanted:
             n = layout.num_requests
             pinned.numpy()[layout.off_wanted_rows:layout.off_wanted_rows + n] = np.arange(n, dtype=np.int32)
+        if wanted_rows is not None:     # a step of fixed shape: one row per request (the layout has room for that)
+            assert len(wanted_rows) <= layout.num_requests
+            pinned.numpy()[layout.off_wanted_rows:layout.off_wanted_rows + len(wanted_rows)] = wanted_rows
         self._device_ints[:layout.total].copy_(pinned[:layout.total], non_blocking=True)
         event.record(torch.cuda.current_stream(self._device_index))
         if device_tokens is not None:
@@ -145,8 +170,13 @@ class ModelRunner:
         if len(entries) > self.max_num_seqs:
             raise ValueError(f"the step brings {len(entries)} requests, max_num_seqs is {self.max_num_seqs}")
         decode_only = all(e.count == 1 for e in entries)
+        plan = None
+        if self.use_cuda_graphs and not decode_only and PROMPT_GRAPHS and device_tokens is None:
+            plan = self._prompt_graph_plan(entries, total)
         if self.use_cuda_graphs and decode_only:
             logits = self._graph_step(entries, device_tokens)
+        elif plan is not None:
+            logits = self._prompt_graph_step(entries, *plan)
         else:
             layout = self._pack(entries, device_tokens=device_tokens)
             ctx = self._context(layout, self.runtime.workspace)
@@ -176,6 +206,99 @@ class ModelRunner:
         if len(rows) == len(entries):
             return logits[:len(entries)]
         return logits[torch.tensor(rows, device=logits.device)]
+
+
+    # ---- steps with one prompt portion as CUDA graphs
+    def _prompt_graph_plan(self, entries, total):
+        """(index of the portion's entry, its padded length, the bucket of the
+        decoded tokens beside it) when the step can run as a graph of fixed
+        shape, else None.  Dummy tokens after the portion would also pass
+        through per-request state, so models that keep such state are left out."""
+        multi = [i for i, e in enumerate(entries) if e.count > 1]
+        if len(multi) != 1 or self.model.states:
+            return None
+        m = multi[0]
+        e = entries[m]
+        if e.ahead or len(e.want) > 1 or e.count > PROMPT_GRAPH_MAX_TOKENS:
+            return None
+        padded = prompt_bucket(e.count)
+        singles = len(entries) - 1
+        bucket = self._bucket(singles) if singles else 0
+        if e.start + padded > self.max_model_len or 1 + bucket > self.max_num_seqs:
+            return None                                   # positions past the tables, or more rows than the buffers hold
+        if padded + bucket > self.max_num_batched_tokens:
+            return None
+        if any(x.ahead for x in entries):
+            return None
+        if (padded, bucket) not in self._prompt_graphs and len(self._prompt_graphs) >= MAX_PROMPT_GRAPHS:
+            return None
+        return m, padded, bucket
+
+    def _prompt_graph_step(self, entries, m, padded, bucket):
+        key = (padded, bucket)
+        graph = self._prompt_graphs.get(key)
+        if graph is None:
+            from .runtime import Workspace
+            if self._prompt_workspace is None:
+                self._prompt_workspace = Workspace(self.runtime.device, pin_old=True)
+            graph = _PromptGraph(self, padded, bucket, self._prompt_workspace)
+            self._prompt_graphs[key] = graph
+        # the portion first, the decoded tokens behind it; the wanted rows are listed in the entries' own order,
+        # so the first rows of the result are the caller's
+        ordered = [entries[m]] + [e for i, e in enumerate(entries) if i != m]
+        rows = []
+        single = 0
+        for i, e in enumerate(entries):
+            if i == m:
+                rows.extend(int(w) for w in e.want)
+            else:
+                if len(e.want):
+                    rows.append(padded + single)
+                single += 1
+        self.num_graph_steps += 1
+        logits = graph.run(ordered, rows)
+        return logits[:len(rows)] if rows else None
+
+
+class _PromptGraph:
+    """One captured step of fixed shape: a prompt portion of ``padded`` rows
+    (its own tokens, then dummies) and ``bucket`` single-token requests."""
+
+    def __init__(self, runner: ModelRunner, padded: int, bucket: int, workspace):
+        self.runner, self.padded, self.bucket = runner, padded, bucket
+        self.workspace = workspace
+        self.capacity_at_capture = runner._capacity
+        self.graph = None
+        self.logits = None
+
+    def run(self, entries, rows):
+        r = self.runner
+        n = 1 + self.bucket
+        wanted = np.zeros(n, dtype=np.int32)
+        wanted[:len(rows)] = rows
+        layout = r._pack(entries, pad_requests=n, fixed=True, pad_first_to=self.padded, wanted_rows=wanted)
+        if r._capacity != self.capacity_at_capture:
+            raise RuntimeError("the integer buffer moved after a step graph was captured")
+        if self.graph is None:
+            ctx = r._context(layout, self.workspace, num_wanted=n)
+            ctx.context_bound = r.max_model_len      # a captured step serves every later context length
+            if self.logits is None:
+                self.logits = r.model.forward(ctx, r.cache)   # eager warm-up on the real data
+                return self.logits
+            torch.cuda.synchronize()
+            gc.collect()
+            was_enabled = gc.isenabled()
+            gc.disable()
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self.logits = r.model.forward(ctx, r.cache)
+            finally:
+                if was_enabled:
+                    gc.enable()
+            self.graph = graph
+        self.graph.replay()
+        return self.logits
 
 
 class _DecodeGraph:

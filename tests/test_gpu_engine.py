@@ -114,6 +114,39 @@ def test_decode_graphs_of_partly_filled_buckets(folders, count):
     assert engine.block_manager.audit() == ""
 
 
+def test_prompt_portions_as_graphs_of_fixed_shape(folders):
+    """A step with one prompt portion (alone or beside decoded tokens) runs as a
+    captured graph: the portion padded with dummy tokens to a multiple of 64,
+    the decoded tokens with dummy requests.  The dummies write behind the
+    request's own tokens and into the page nobody owns; every request's
+    tokens equal the plain implementation's, with pages used again."""
+    cfg, w, d32, _ = folders["b"]
+    engine = LLMEngine.from_pretrained(d32, dtype="float32", num_blocks=48, block_size=fixtures.TINY_B_PAGE,
+                                       max_num_seqs=4, max_num_batched_tokens=128, max_prefill_chunk=48)
+    lens = (40, 97, 8, 61, 33, 70, 52, 19)
+    prompts = [fixtures.random_ids(cfg, n, 900 + n) for n in lens]
+    # a request arrives when the one before has had its whole prompt run, so a step holds one portion at most
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    done, nxt, calls = {}, 0, 0
+    while nxt < len(prompts) or engine.has_unfinished_requests():
+        waiting_for_prompt = any(seq.get_output_len() == 0 for seq, _, _ in engine.active_sequences.values())
+        if nxt < len(prompts) and not waiting_for_prompt and len(engine.active_sequences) < 4:
+            engine.add_request(str(nxt), prompts[nxt], sp)
+            nxt += 1
+        for o in engine.step():
+            if o.finished:
+                done[int(o.request_id)] = o
+        calls += 1
+        assert calls < 500
+    outs = [done[i] for i in range(len(prompts))]
+    graphs = engine.runner._prompt_graphs
+    assert any(g.graph is not None for g in graphs.values()), "no prompt step was captured"
+    assert any(bucket > 0 for _, bucket in graphs), "no mixed step went through a graph"
+    for p, o in zip(prompts, outs):
+        assert o.output_tokens == plain_llama.plain_greedy_generate(cfg, w, p, 12)
+    assert engine.block_manager.audit() == "" and engine.stats()["free_blocks"] == 48
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_steps_launched_ahead_give_the_same_tokens(folders, dtype):
     """The engine launches a decode step before it has read the tokens of the
