@@ -256,7 +256,7 @@ def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
                                a.stride(0), w.stride(0), out.stride(0), _stream()), "le_gemm_simt")
 
 
-SKINNY_ROWS = 32          # up to this many rows a product streams weights through the package's own kernel (64: slower than the library)
+SKINNY_ROWS = 16          # up to this many rows a product streams weights through the package's own kernel (17..32 rows: 3-7 % slower per decode step than the library and the tcgen05 kernel, measured at three model sizes)
 SKINNY_BLOCKS = 512       # blocks worth having in flight on a B200 (4 slices of K for 2048 columns: measured best of 1..8)
 
 
