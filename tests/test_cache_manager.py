@@ -207,6 +207,21 @@ def test_pack_step_layout():
     assert p9.num_requests == 16 and p9.off_block_tables[0] - p9.off_wanted_rows >= 16
     for s in nine:
         bm.free(s)
+    # the first entry padded with dummy tokens to a fixed number of rows: they continue its positions, carry
+    # token 0 and point at the request's own pages, then at the page nobody owns
+    pp = host.pack_step([host.StepEntry(b, 0, 3, [2]), host.StepEntry(a, 5, 1, [0])], bm, [2, 16], 4, [6], buf.ctypes.data,
+                        buf.size, pad_first_to=8)
+    assert (pp.num_tokens, pp.num_requests, pp.num_wanted, pp.max_q_len, pp.max_context, pp.num_decode) == (11, 4, 2, 8, 8, 3)
+    assert buf[pp.off_token_ids:pp.off_token_ids + 11].tolist() == [20, 21, 22, 0, 0, 0, 0, 0, 15, 0, 0]
+    assert buf[pp.off_positions:pp.off_positions + 11].tolist() == [0, 1, 2, 3, 4, 5, 6, 7, 5, 0, 0]
+    assert buf[pp.off_request_of_token:pp.off_request_of_token + 11].tolist() == [0] * 8 + [1, 2, 3]
+    assert buf[pp.off_cu_q:pp.off_cu_q + 5].tolist() == [0, 8, 9, 10, 11]
+    assert buf[pp.off_wanted_rows:pp.off_wanted_rows + 2].tolist() == [2, 8]
+    table = buf[pp.off_block_tables[0]:pp.off_block_tables[0] + 4 * 6].reshape(4, 6)
+    assert table[0].tolist() == b.get_block_table() + [20] * 5     # positions 4..7 of the dummies: nobody's page
+    assert pp.num_tiles == [4 + 3, 1 + 3] and pp.num_tiles_multi == [4, 1]
+    with pytest.raises(ValueError, match="runs past"):
+        host.pack_step([host.StepEntry(b, 0, 4, [])], bm, [], 0, [], 0, 0, pad_first_to=8)
     # single-token requests come after the others in the tile lists
     c = host.Sequence(2, [1, 2, 3], host.SamplingParams())
     bm.grow(c, 2); c.set_num_computed_tokens(2); bm.grow(c, 3)
