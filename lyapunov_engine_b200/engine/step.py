@@ -72,7 +72,10 @@ class ModelRunner:
         self._prompt_workspace = None
         self.num_steps = 0
         self.num_graph_steps = 0
-        self._reserve(self._upper_bound(max_num_batched_tokens, max_num_seqs))
+        # room for the rows and requests that padding to a fixed shape adds to a step within the caller's limits
+        self._most_rows = max_num_batched_tokens + 128 + max_num_seqs
+        self._most_requests = max_num_seqs + 1
+        self._reserve(self._upper_bound(self._most_rows, self._most_requests))
 
     # ---- integer buffers
     def _upper_bound(self, tokens: int, requests: int) -> int:
@@ -224,10 +227,10 @@ class ModelRunner:
         padded = prompt_bucket(e.count)
         singles = len(entries) - 1
         bucket = self._bucket(singles) if singles else 0
-        if e.start + padded > self.max_model_len or 1 + bucket > self.max_num_seqs:
-            return None                                   # positions past the tables, or more rows than the buffers hold
-        if padded + bucket > self.max_num_batched_tokens:
-            return None
+        if e.start + padded > self.max_model_len:
+            return None                                   # the dummies' positions would run past the tables
+        if 1 + bucket > self._most_requests or padded + bucket > self._most_rows:
+            return None                                   # more rows than the step's integers have room for
         if any(x.ahead for x in entries):
             return None
         if (padded, bucket) not in self._prompt_graphs and len(self._prompt_graphs) >= MAX_PROMPT_GRAPHS:
