@@ -220,6 +220,10 @@ class ModelRunner:
         multi = [i for i, e in enumerate(entries) if e.count > 1]
         if len(multi) != 1 or self.model.states:
             return None
+        if total <= ops.SKINNY_ROWS:
+            # so few rows run on the weight-streaming kernels, as decode steps do, and those give a row the same
+            # bits whatever the number of rows; padded, the step would go to other kernels with other roundings
+            return None
         m = multi[0]
         e = entries[m]
         if e.ahead or len(e.want) > 1 or e.count > PROMPT_GRAPH_MAX_TOKENS:
@@ -263,73 +267,26 @@ class ModelRunner:
         return logits[:len(rows)] if rows else None
 
 
-class _PromptGraph:
-    """One captured step of fixed shape: a prompt portion of ``padded`` rows
-    (its own tokens, then dummies) and ``bucket`` single-token requests."""
+class _StepGraph:
+    """A step of fixed shape.  The first call runs eagerly (it warms every
+    kernel and library up with the real entries, so nothing is computed
+    twice), the second is captured, later ones replay the capture."""
 
-    def __init__(self, runner: ModelRunner, padded: int, bucket: int, workspace):
-        self.runner, self.padded, self.bucket = runner, padded, bucket
-        self.workspace = workspace
+    def __init__(self, runner: ModelRunner, workspace, num_wanted: int):
+        self.runner, self.workspace, self.num_wanted = runner, workspace, num_wanted
         self.capacity_at_capture = runner._capacity
         self.graph = None
         self.logits = None
 
-    def run(self, entries, rows):
+    def _launch(self, layout):
         r = self.runner
-        n = 1 + self.bucket
-        wanted = np.zeros(n, dtype=np.int32)
-        wanted[:len(rows)] = rows
-        layout = r._pack(entries, pad_requests=n, fixed=True, pad_first_to=self.padded, wanted_rows=wanted)
         if r._capacity != self.capacity_at_capture:
             raise RuntimeError("the integer buffer moved after a step graph was captured")
         if self.graph is None:
-            ctx = r._context(layout, self.workspace, num_wanted=n)
+            ctx = r._context(layout, self.workspace, num_wanted=self.num_wanted)
             ctx.context_bound = r.max_model_len      # a captured step serves every later context length
             if self.logits is None:
                 self.logits = r.model.forward(ctx, r.cache)   # eager warm-up on the real data
-                return self.logits
-            torch.cuda.synchronize()
-            gc.collect()
-            was_enabled = gc.isenabled()
-            gc.disable()
-            try:
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    self.logits = r.model.forward(ctx, r.cache)
-            finally:
-                if was_enabled:
-                    gc.enable()
-            self.graph = graph
-        self.graph.replay()
-        return self.logits
-
-
-class _DecodeGraph:
-    """One captured decode step for a fixed number of rows."""
-
-    def __init__(self, runner: ModelRunner, bucket: int, entries):
-        from .runtime import Workspace
-
-        self.runner, self.bucket = runner, bucket
-        self.workspace = Workspace(runner.runtime.device, pin_old=True)
-        self.capacity_at_capture = runner._capacity
-        # The first call runs eagerly (it warms every kernel and library up
-        # with the real entries, so nothing is computed twice), the second is
-        # captured.
-        self.graph = None
-        self.logits = None
-
-    def run(self, entries, device_tokens=None):
-        r = self.runner
-        layout = r._pack(entries, pad_requests=self.bucket, fixed=True, all_wanted=True, device_tokens=device_tokens)
-        if r._capacity != self.capacity_at_capture:
-            raise RuntimeError("the integer buffer moved after a decode graph was captured")
-        if self.graph is None:
-            ctx = r._context(layout, self.workspace, num_wanted=self.bucket)
-            ctx.context_bound = r.max_model_len      # a captured step serves every later context length
-            if self.logits is None:
-                self.logits = r.model.forward(ctx, r.cache)   # eager warm-up on the real data
-                self._warm = True
                 return self.logits
             # Capture.  The step's integers are already on the device; the
             # captured kernels read them from the same addresses every time.
@@ -350,3 +307,33 @@ class _DecodeGraph:
             # Capturing does not run the kernels: replay for this step's result.
         self.graph.replay()
         return self.logits
+
+
+class _PromptGraph(_StepGraph):
+    """A prompt portion of ``padded`` rows (its own tokens, then dummies) and
+    ``bucket`` single-token requests."""
+
+    def __init__(self, runner: ModelRunner, padded: int, bucket: int, workspace):
+        super().__init__(runner, workspace, 1 + bucket)
+        self.padded, self.bucket = padded, bucket
+
+    def run(self, entries, rows):
+        n = self.num_wanted
+        wanted = np.zeros(n, dtype=np.int32)
+        wanted[:len(rows)] = rows
+        return self._launch(self.runner._pack(entries, pad_requests=n, fixed=True, pad_first_to=self.padded,
+                                              wanted_rows=wanted))
+
+
+class _DecodeGraph(_StepGraph):
+    """A decode step for a fixed number of rows."""
+
+    def __init__(self, runner: ModelRunner, bucket: int, entries):
+        from .runtime import Workspace
+
+        super().__init__(runner, Workspace(runner.runtime.device, pin_old=True), bucket)
+        self.bucket = bucket
+
+    def run(self, entries, device_tokens=None):
+        return self._launch(self.runner._pack(entries, pad_requests=self.bucket, fixed=True, all_wanted=True,
+                                              device_tokens=device_tokens))
