@@ -197,8 +197,10 @@ def test_steps_launched_ahead_give_the_same_tokens(folders, dtype):
 def test_random_traffic_with_and_without_steps_ahead(folders, seed):
     """Random arrivals, lengths, sampling options, end-of-sequence tokens,
     aborts and page pools small enough to pre-empt: the same tokens and finish
-    reasons whether or not steps are launched ahead.  float32, whose logits do
-    not depend on what else is in a batch, so every token must agree."""
+    reasons with every step launched kernel by kernel and read before the next
+    is scheduled, and with steps captured as graphs of padded shape and
+    launched ahead.  float32, whose logits do not depend on what else is in a
+    batch, so every token must agree."""
     import json
     import random
     import shutil
@@ -211,7 +213,8 @@ def test_random_traffic_with_and_without_steps_ahead(folders, seed):
         for ahead in (False, True):
             rng = random.Random(seed)
             engine = LLMEngine.from_pretrained(d, dtype="float32", num_blocks=rng.choice([12, 20, 48]), block_size=8, max_num_seqs=4,
-                                               max_num_batched_tokens=rng.choice([16, 48]), lookahead=ahead, max_model_len=160)
+                                               max_num_batched_tokens=rng.choice([16, 48]), lookahead=ahead, max_model_len=160,
+                                               use_cuda_graphs=ahead)
             plan = [(rng.randint(0, 60), f"r{i}", fixtures.random_ids(cfg, rng.randint(1, 40), seed * 100 + i),
                      SamplingParams(temperature=rng.choice([0.0, 0.0, 0.7]), top_p=rng.choice([1.0, 0.9]), top_k=rng.choice([-1, 20]),
                                     max_tokens=rng.randint(1, 30), ignore_eos=rng.random() < 0.3, seed=i)) for i in range(14)]
@@ -231,6 +234,7 @@ def test_random_traffic_with_and_without_steps_ahead(folders, seed):
             results.append((done, engine.stats()))
     assert results[0][0] == results[1][0] and len(results[0][0]) >= 11
     assert results[0][1]["steps_ahead"] == 0 and results[1][1]["steps_ahead"] > 0
+    assert results[0][1]["graph_steps"] == 0 and results[1][1]["graph_steps"] > 0
     assert results[0][1]["preemptions"] == results[1][1]["preemptions"]
 
 
