@@ -364,9 +364,9 @@ def run_ours(args):
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     d2h = (engine.d2h_bytes - d2h0) / e2e_steps
-    layout = host.pack_step([host.StepEntry(seq, seq.get_num_computed_tokens(), 1, [0]) for seq, _, _ in
-                             engine.active_sequences.values()], manager, runner.tile_sizes, batch,
-                            runner.fixed_max_blocks, 0, 0)
+    live = [host.StepEntry(seq, seq.get_num_computed_tokens(), 1, [0]) for seq, _, _ in engine.active_sequences.values()]
+    width = runner._table_width(CONTEXT)                           # as the runner packs a captured decode step
+    layout = host.pack_step(live, manager, runner.tile_sizes, batch, [min(width, w) for w in runner.fixed_max_blocks], 0, 0)
     h2d = 4 * layout.total
     while engine.has_unfinished_requests():
         engine.step()

@@ -67,7 +67,7 @@ class ModelRunner:
         self._ring: list = []
         self._ring_pos = 0
         self._device_ints = None
-        self._graphs: dict[int, "_DecodeGraph"] = {}
+        self._graphs: dict[tuple, "_DecodeGraph"] = {}
         self._prompt_graphs: dict[tuple, "_PromptGraph"] = {}
         self._prompt_workspace = None
         self.num_steps = 0
@@ -96,9 +96,10 @@ class ModelRunner:
         self._graphs.clear()  # they point into the old buffer
         self._prompt_graphs.clear()
 
-    def _pack(self, entries, pad_requests=0, fixed=False, all_wanted=False, device_tokens=None, pad_first_to=0,
+    def _pack(self, entries, pad_requests=0, fixed=0, all_wanted=False, device_tokens=None, pad_first_to=0,
               wanted_rows=None):
-        fixed_blocks = self.fixed_max_blocks if fixed else []
+        """``fixed``: width of every group's block table (0: as wide as the step needs)."""
+        fixed_blocks = [min(fixed, w) for w in self.fixed_max_blocks] if fixed else []
         pinned, event = self._ring[self._ring_pos]
         self._ring_pos = (self._ring_pos + 1) % len(self._ring)
         event.synchronize()
@@ -189,6 +190,17 @@ class ModelRunner:
         return logits
 
     # ---- decode steps as CUDA graphs
+    def _table_width(self, tokens: int) -> int:
+        """Block-table width of a captured step whose longest request holds
+        ``tokens``: the next power of two of the pages that takes (16 at
+        least), so that a graph serves a range of contexts and the step's
+        integers do not carry tables as wide as the longest request allowed."""
+        need = (tokens + self.cache.block_size - 1) // self.cache.block_size
+        width = 16
+        while width < need:
+            width *= 2
+        return min(width, max(self.fixed_max_blocks)) if self.fixed_max_blocks else width
+
     def _bucket(self, n: int) -> int:
         b = 1
         while b < n:
@@ -197,10 +209,11 @@ class ModelRunner:
 
     def _graph_step(self, entries, device_tokens=None):
         bucket = self._bucket(len(entries))
-        graph = self._graphs.get(bucket)
+        width = self._table_width(max(e.start for e in entries) + 1)
+        graph = self._graphs.get((bucket, width))
         if graph is None:
-            graph = _DecodeGraph(self, bucket, entries)
-            self._graphs[bucket] = graph
+            graph = _DecodeGraph(self, bucket, width)
+            self._graphs[(bucket, width)] = graph
         self.num_graph_steps += 1
         logits = graph.run(entries, device_tokens)
         rows = [i for i, e in enumerate(entries) if len(e.want)]
@@ -237,18 +250,19 @@ class ModelRunner:
             return None                                   # more rows than the step's integers have room for
         if any(x.ahead for x in entries):
             return None
-        if (padded, bucket) not in self._prompt_graphs and len(self._prompt_graphs) >= MAX_PROMPT_GRAPHS:
+        width = self._table_width(max([e.start + padded] + [x.start + 1 for x in entries]))
+        if (padded, bucket, width) not in self._prompt_graphs and len(self._prompt_graphs) >= MAX_PROMPT_GRAPHS:
             return None
-        return m, padded, bucket
+        return m, padded, bucket, width
 
-    def _prompt_graph_step(self, entries, m, padded, bucket):
-        key = (padded, bucket)
+    def _prompt_graph_step(self, entries, m, padded, bucket, width):
+        key = (padded, bucket, width)
         graph = self._prompt_graphs.get(key)
         if graph is None:
             from .runtime import Workspace
             if self._prompt_workspace is None:
                 self._prompt_workspace = Workspace(self.runtime.device, pin_old=True)
-            graph = _PromptGraph(self, padded, bucket, self._prompt_workspace)
+            graph = _PromptGraph(self, padded, bucket, width, self._prompt_workspace)
             self._prompt_graphs[key] = graph
         # the portion first, the decoded tokens behind it; the wanted rows are listed in the entries' own order,
         # so the first rows of the result are the caller's
@@ -272,8 +286,8 @@ class _StepGraph:
     kernel and library up with the real entries, so nothing is computed
     twice), the second is captured, later ones replay the capture."""
 
-    def __init__(self, runner: ModelRunner, workspace, num_wanted: int):
-        self.runner, self.workspace, self.num_wanted = runner, workspace, num_wanted
+    def __init__(self, runner: ModelRunner, workspace, num_wanted: int, width: int):
+        self.runner, self.workspace, self.num_wanted, self.width = runner, workspace, num_wanted, width
         self.capacity_at_capture = runner._capacity
         self.graph = None
         self.logits = None
@@ -284,7 +298,8 @@ class _StepGraph:
             raise RuntimeError("the integer buffer moved after a step graph was captured")
         if self.graph is None:
             ctx = r._context(layout, self.workspace, num_wanted=self.num_wanted)
-            ctx.context_bound = r.max_model_len      # a captured step serves every later context length
+            # a captured step serves every context its block tables can hold
+            ctx.context_bound = min(r.max_model_len, self.width * r.cache.block_size)
             if self.logits is None:
                 self.logits = r.model.forward(ctx, r.cache)   # eager warm-up on the real data
                 return self.logits
@@ -313,27 +328,27 @@ class _PromptGraph(_StepGraph):
     """A prompt portion of ``padded`` rows (its own tokens, then dummies) and
     ``bucket`` single-token requests."""
 
-    def __init__(self, runner: ModelRunner, padded: int, bucket: int, workspace):
-        super().__init__(runner, workspace, 1 + bucket)
+    def __init__(self, runner: ModelRunner, padded: int, bucket: int, width: int, workspace):
+        super().__init__(runner, workspace, 1 + bucket, width)
         self.padded, self.bucket = padded, bucket
 
     def run(self, entries, rows):
         n = self.num_wanted
         wanted = np.zeros(n, dtype=np.int32)
         wanted[:len(rows)] = rows
-        return self._launch(self.runner._pack(entries, pad_requests=n, fixed=True, pad_first_to=self.padded,
+        return self._launch(self.runner._pack(entries, pad_requests=n, fixed=self.width, pad_first_to=self.padded,
                                               wanted_rows=wanted))
 
 
 class _DecodeGraph(_StepGraph):
     """A decode step for a fixed number of rows."""
 
-    def __init__(self, runner: ModelRunner, bucket: int, entries):
+    def __init__(self, runner: ModelRunner, bucket: int, width: int):
         from .runtime import Workspace
 
-        super().__init__(runner, Workspace(runner.runtime.device, pin_old=True), bucket)
+        super().__init__(runner, Workspace(runner.runtime.device, pin_old=True), bucket, width)
         self.bucket = bucket
 
     def run(self, entries, device_tokens=None):
-        return self._launch(self.runner._pack(entries, pad_requests=self.bucket, fixed=True, all_wanted=True,
+        return self._launch(self.runner._pack(entries, pad_requests=self.bucket, fixed=self.width, all_wanted=True,
                                               device_tokens=device_tokens))
