@@ -273,3 +273,10 @@ def test_nothing_is_scheduled_ahead_of_an_admission_or_without_pages():
         sched.post_step(sched.schedule(), [9])
     step = sched.schedule()
     assert shape(step) == [(0, 11, 1, [0])] and not sched.schedule_ahead(step).entries and bm.audit() == ""
+
+
+def test_padded_lengths_of_prompt_portions():
+    """Portions run as graphs of padded shape: multiples of 64 up to 512, of 128 above."""
+    from lyapunov_engine_b200.engine.step import prompt_bucket
+    assert [prompt_bucket(n) for n in (2, 64, 65, 500, 512, 513, 640, 1000, 1024)] == [64, 64, 128, 512, 512, 640, 640, 1024, 1024]
+
