@@ -346,11 +346,16 @@ def run_ours(args):
                "frac": round(flops / (pre_ms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)}
 
     # ---- end to end through the entry point: host tokens in, host tokens out
+    # The requests live past the timed window (it holds K steps of all `batch` requests and nothing else); they
+    # end afterwards four steps apart, and that drain (8 requests down to none, smaller batch buckets) is timed
+    # by itself.
     e2e_steps, e2e_warm = args.steps, args.warmup
-    prompt_len = CONTEXT - (e2e_steps + e2e_warm) - 1
-    sp = SamplingParams(temperature=0.0, max_tokens=e2e_steps + e2e_warm + 1, ignore_eos=True)
+    ahead_of_window = 8                      # steps in which requests get their first tokens one after the other
+    prompt_len = CONTEXT - (e2e_steps + e2e_warm) - ahead_of_window - 1   # the window ends at CONTEXT at the latest
     for i in range(batch):
+        sp = SamplingParams(temperature=0.0, max_tokens=e2e_steps + e2e_warm + ahead_of_window + 4 * (i + 1), ignore_eos=True)
         engine.add_request(f"bench-{i}", torch.randint(0, vocab, (prompt_len,), generator=gen).tolist(), sp)
+    engine.warm_up(contexts=[CONTEXT], batches=[1, 2, 4, batch])   # as a server does before its first request
     while any(seq.get_output_len() == 0 for seq, _, _ in engine.active_sequences.values()):
         engine.step()                               # prefill (portions under the token budget)
     for _ in range(e2e_warm):
@@ -359,19 +364,30 @@ def run_ours(args):
     d2h0 = engine.d2h_bytes
     t0 = time.perf_counter()
     produced = 0
+    slowest = 0.0
     for _ in range(e2e_steps):
+        t1 = time.perf_counter()
         produced += len(engine.step())
+        slowest = max(slowest, time.perf_counter() - t1)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    assert produced == batch * e2e_steps, (produced, batch, e2e_steps)
     d2h = (engine.d2h_bytes - d2h0) / e2e_steps
     live = [host.StepEntry(seq, seq.get_num_computed_tokens(), 1, [0]) for seq, _, _ in engine.active_sequences.values()]
-    width = runner._table_width(CONTEXT)                           # as the runner packs a captured decode step
+    width = runner._table_width(max(e.start for e in live) + 1)    # as the runner packs a captured decode step
     layout = host.pack_step(live, manager, runner.tile_sizes, batch, [min(width, w) for w in runner.fixed_max_blocks], 0, 0)
     h2d = 4 * layout.total
+    t0 = time.perf_counter()
+    drain_steps = drain_tokens = 0
     while engine.has_unfinished_requests():
-        engine.step()
+        drain_tokens += len(engine.step())
+        drain_steps += 1
+    torch.cuda.synchronize()
+    drain_s = time.perf_counter() - t0
     e2e = {"value": round(produced / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-           "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_s * 1000 / e2e_steps, 4)}
+           "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_s * 1000 / e2e_steps, 4),
+           "slowest_step_ms": round(slowest * 1000, 3),
+           "drain": {"steps": drain_steps, "tokens": drain_tokens, "ms_per_step": round(drain_s * 1000 / max(drain_steps, 1), 4)}}
     clocks.stop()
 
     # the timed steps run at contexts CONTEXT - steps + 1 .. CONTEXT: count the bytes of their mean

@@ -67,7 +67,37 @@ __global__ void convert_kernel(TO *__restrict__ out, const TI *__restrict__ in, 
   if (i < n) out[i] = le::from_f32<TO>(le::to_f32(in[i]));
 }
 
+// One block per request of the step: a request none of whose tokens are in the
+// cache yet (ctx_before == 0) gets its row of a per-request state buffer
+// zeroed.  Rows that stand for no request (slot < 0) are skipped.
+__global__ void zero_fresh_state_kernel(uint32_t *__restrict__ state, int64_t row_words, int num_rows,
+                                        const int32_t *__restrict__ slots, const int32_t *__restrict__ ctx_before) {
+  const int b = blockIdx.x;
+  const int slot = slots[b];
+  if (slot < 0 || slot >= num_rows || ctx_before[b] != 0) return;
+  uint32_t *row = state + static_cast<int64_t>(slot) * row_words;
+  for (int64_t i = threadIdx.x; i < row_words; i += blockDim.x) row[i] = 0u;
+}
+
 }  // namespace
+
+// How many multiprocessors the current device has (grids are sized by it).
+LE_API int le_sm_count() {
+  int device = 0, count = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return -1;
+  if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return -1;
+  return count;
+}
+
+// state: [num_rows, row_bytes] bytes, row_bytes a multiple of 4.
+LE_API int le_zero_fresh_state(void *state, int64_t row_bytes, int num_rows, const int32_t *slots,
+                               const int32_t *ctx_before, int num_requests, cudaStream_t stream) {
+  if (num_requests <= 0 || row_bytes <= 0) return 0;
+  if (row_bytes % 4) return le::invalid("le_zero_fresh_state: rows of %lld bytes are not a multiple of 4", (long long)row_bytes);
+  zero_fresh_state_kernel<<<num_requests, 256, 0, stream>>>(static_cast<uint32_t *>(state), row_bytes / 4, num_rows, slots,
+                                                            ctx_before);
+  return le::launched();
+}
 
 LE_API int le_embed(float *out, const void *table, int table_dtype, const int32_t *ids, int num_tokens, int hidden,
                     int vocab, int *status, cudaStream_t stream) {

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import collections
 import contextlib
+import gc
 import os
 
 import torch
@@ -37,7 +38,8 @@ class EngineConfig:
     def __init__(self, model_config=None, num_blocks: int = 1024, num_gpu_blocks: int | None = None,
                  block_size: int = 16, max_num_seqs: int = 64, max_num_batched_tokens: int = 2048,
                  dtype=torch.bfloat16, device: str = "cuda:0", max_model_len: int | None = None,
-                 max_prefill_chunk: int = 0, use_cuda_graphs: bool = True, seed: int = 0, lookahead: bool | None = None):
+                 max_prefill_chunk: int = 0, use_cuda_graphs: bool = True, seed: int = 0, lookahead: bool | None = None,
+                 freeze_gc: bool = False):
         self.model_config = model_config
         self.num_blocks = num_gpu_blocks if num_gpu_blocks is not None else num_blocks
         self.block_size = block_size
@@ -51,6 +53,13 @@ class EngineConfig:
         self.seed = seed
         # launch the next decode step before the result of the one before has been read (see LLMEngine.step)
         self.lookahead = (os.environ.get("LYAPUNOV_LOOKAHEAD", "1") not in ("0", "")) if lookahead is None else bool(lookahead)
+        # A full collection of the interpreter's heap walks every object that torch and the model made (measured
+        # 23-32 ms) and lands in whichever step allocates the object that triggers it, while a decode step takes
+        # one millisecond.  With this set, the engine moves the objects that exist once it is built into the
+        # collector's permanent generation (gc.freeze()): they are still freed when their last reference goes, but
+        # no longer searched for cycles, so an engine that is dropped later may keep its memory.  For a process
+        # that serves with one engine until it exits; off by default.
+        self.freeze_gc = bool(freeze_gc)
 
 
 class _LaunchedStep:
@@ -154,6 +163,22 @@ class LLMEngine:
         self.num_steps_ahead = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        if config.freeze_gc:
+            gc.collect()
+            gc.freeze()
+
+    def warm_up(self, contexts=None, batches=None) -> int:
+        """Captures the decode steps' graphs ahead of the first request (every
+        batch bucket up to ``max_num_seqs`` at every doubling of the context up
+        to ``max_model_len``, or those that serve the given ``contexts`` and
+        ``batches``), so that no request waits for a capture.  Returns how
+        many were captured.  Without it each shape is captured at its first use."""
+        with self._on_device():
+            n = self.runner.warm_up(contexts, batches)
+        if self.config.freeze_gc:
+            gc.collect()
+            gc.freeze()
+        return n
 
     # ---- construction in one call
     @classmethod
@@ -320,6 +345,7 @@ class LLMEngine:
         s = self.scheduler.get_stats()
         return {"steps": s.steps, "prefill_tokens": s.prefill_tokens, "decode_tokens": s.decode_tokens,
                 "preemptions": s.preemptions, "failed": s.failed, "graph_steps": self.runner.num_graph_steps,
-                "steps_ahead": self.num_steps_ahead,
+                "graphs": len(self.runner._graphs) + len(self.runner._prompt_graphs),
+                "graph_bytes": self.runner.graph_bytes(), "steps_ahead": self.num_steps_ahead,
                 "free_blocks": self.block_manager.get_num_free_blocks() if self.loaded.model.groups else 0,
                 "cache_bytes": self.cache.bytes()}

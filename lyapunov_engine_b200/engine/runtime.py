@@ -54,6 +54,9 @@ class Runtime:
         if dtype not in (torch.bfloat16, torch.float32):
             raise ValueError(f"dtype must be torch.bfloat16 or torch.float32, got {dtype}")
         self.dtype = dtype
+        # Library products (bfloat16 with many rows) must add up in 32 bits whatever algorithm the library picks;
+        # its default lets split-K partial sums pass through bfloat16.
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         self.max_model_len = max_model_len
         self.shared: dict = {}
         self.workspace = Workspace(self.device)

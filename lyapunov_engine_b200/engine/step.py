@@ -27,7 +27,7 @@ import numpy as np
 import torch
 
 from .. import build, ops
-from ..parts import attention_kernels
+from .runtime import Workspace
 
 
 # Prompt portions of at most this many tokens run as captured graphs; longer ones keep the device busy for longer
@@ -35,6 +35,13 @@ from ..parts import attention_kernels
 PROMPT_GRAPH_MAX_TOKENS = 1024
 PROMPT_GRAPHS = os.environ.get("LYAPUNOV_PROMPT_GRAPHS", "1") not in ("0", "")
 MAX_PROMPT_GRAPHS = 64
+# Decode graphs are keyed by (rows, width of the block tables): at most this many are kept, the one used longest
+# ago makes room for a new one.
+MAX_DECODE_GRAPHS = 96
+
+
+class StepTooLarge(ValueError):
+    """The step's integers do not fit the buffers they are packed into."""
 
 
 def prompt_bucket(tokens: int) -> int:
@@ -59,7 +66,7 @@ class ModelRunner:
         self.max_num_batched_tokens, self.max_num_seqs, self.max_model_len = max_num_batched_tokens, max_num_seqs, max_model_len
         self.use_cuda_graphs = use_cuda_graphs
         self.check_status = check_status
-        self.tile_sizes = attention_kernels.tile_sizes()
+        self.tile_sizes = list(model.tile_sizes)     # query-tile lists that the model's mixers ask for
         dev = torch.device(runtime.device)
         self._device_index = dev.index if dev.index is not None else torch.cuda.current_device()
         self.fixed_max_blocks = [(max_model_len + cache.block_size - 1) // cache.block_size for _ in model.groups]
@@ -67,11 +74,16 @@ class ModelRunner:
         self._ring: list = []
         self._ring_pos = 0
         self._device_ints = None
-        self._graphs: dict[tuple, "_DecodeGraph"] = {}
+        self._graphs: dict[tuple, "_DecodeGraph"] = {}       # in the order of their last use
         self._prompt_graphs: dict[tuple, "_PromptGraph"] = {}
-        self._prompt_workspace = None
+        # every captured step has its activations in this one workspace (steps run one after the other) and its
+        # capture-time allocations in this one pool
+        self._graph_workspace = None
+        self._graph_pool = None
+        self._warmed: set = set()                             # shapes whose kernels have run once outside a capture
         self.num_steps = 0
         self.num_graph_steps = 0
+        self.num_captures = 0
         # room for the rows and requests that padding to a fixed shape adds to a step within the caller's limits
         self._most_rows = max_num_batched_tokens + 128 + max_num_seqs
         self._most_requests = max_num_seqs + 1
@@ -96,26 +108,32 @@ class ModelRunner:
         self._graphs.clear()  # they point into the old buffer
         self._prompt_graphs.clear()
 
+    def _may_overflow(self, entries, pad_requests, pad_first_to) -> bool:
+        """Whether the step could need more integers than the buffers were sized for."""
+        rows = sum(e.count for e in entries) + max(0, pad_requests - len(entries)) + pad_first_to
+        longest = max((e.start + max(e.count, pad_first_to) for e in entries), default=0)
+        return (rows > self._most_rows or max(len(entries), pad_requests) > self._most_requests
+                or longest > self.max_model_len)
+
     def _pack(self, entries, pad_requests=0, fixed=0, all_wanted=False, device_tokens=None, pad_first_to=0,
-              wanted_rows=None):
-        """``fixed``: width of every group's block table (0: as wide as the step needs)."""
+              wanted_rows=None, may_reserve=True):
+        """``fixed``: width of every group's block table (0: as wide as the step needs).
+        ``may_reserve`` False: a step that does not fit raises StepTooLarge instead
+        of moving the buffers (captured graphs point into them)."""
         fixed_blocks = [min(fixed, w) for w in self.fixed_max_blocks] if fixed else []
         pinned, event = self._ring[self._ring_pos]
         self._ring_pos = (self._ring_pos + 1) % len(self._ring)
         event.synchronize()
-        try:
-            layout = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks,
-                                         pinned.data_ptr(), self._capacity, pad_first_to)
-        except ValueError:
-            # more integers than the buffers hold (it does not happen within the limits given at construction):
-            # size them for this step and pack again
-            need = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks, 0, 0,
-                                       pad_first_to).total
+        args = (entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks)
+        need = self.host.pack_step(*args, 0, 0, pad_first_to).total if self._may_overflow(entries, pad_requests, pad_first_to) else 0
+        if need > self._capacity:
+            # more integers than the buffers hold (it does not happen within the limits given at construction)
+            if not may_reserve:
+                raise StepTooLarge(f"the step needs {need} integers, the buffers hold {self._capacity}")
             self._reserve(int(need * 1.5))
             pinned, event = self._ring[self._ring_pos]
             self._ring_pos = (self._ring_pos + 1) % len(self._ring)
-            layout = self.host.pack_step(entries, self.cache.manager, self.tile_sizes, pad_requests, fixed_blocks,
-                                         pinned.data_ptr(), self._capacity, pad_first_to)
+        layout = self.host.pack_step(*args, pinned.data_ptr(), self._capacity, pad_first_to)
         if all_wanted:
             n = layout.num_requests
             pinned.numpy()[layout.off_wanted_rows:layout.off_wanted_rows + n] = np.arange(n, dtype=np.int32)
@@ -182,12 +200,14 @@ class ModelRunner:
         elif plan is not None:
             logits = self._prompt_graph_step(entries, *plan)
         else:
-            layout = self._pack(entries, device_tokens=device_tokens)
-            ctx = self._context(layout, self.runtime.workspace)
-            logits = self.model.forward(ctx, self.cache)
+            logits = self._eager_step(entries, device_tokens)
         if self.check_status:
             ops.check_status(self.runtime.status)
         return logits
+
+    def _eager_step(self, entries, device_tokens=None):
+        layout = self._pack(entries, device_tokens=device_tokens)
+        return self.model.forward(self._context(layout, self.runtime.workspace), self.cache)
 
     # ---- decode steps as CUDA graphs
     def _table_width(self, tokens: int) -> int:
@@ -207,15 +227,33 @@ class ModelRunner:
             b *= 2
         return min(b, max(self.max_num_seqs, n))
 
+    def _workspace_for_graphs(self):
+        if self._graph_workspace is None:
+            self._graph_workspace = Workspace(self.runtime.device, pin_old=True)
+        return self._graph_workspace
+
+    def _decode_graph(self, bucket: int, width: int) -> "_DecodeGraph":
+        key = (bucket, width)
+        graph = self._graphs.pop(key, None)
+        if graph is None:
+            while len(self._graphs) >= MAX_DECODE_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))        # the one used longest ago
+            graph = _DecodeGraph(self, bucket, width)
+        self._graphs[key] = graph                                  # (now the one used last)
+        return graph
+
     def _graph_step(self, entries, device_tokens=None):
         bucket = self._bucket(len(entries))
         width = self._table_width(max(e.start for e in entries) + 1)
-        graph = self._graphs.get((bucket, width))
-        if graph is None:
-            graph = _DecodeGraph(self, bucket, width)
-            self._graphs[(bucket, width)] = graph
+        graph = self._decode_graph(bucket, width)
         self.num_graph_steps += 1
-        logits = graph.run(entries, device_tokens)
+        try:
+            logits = graph.run(entries, device_tokens)
+        except StepTooLarge:
+            # beyond the limits the buffers were sized for: this step runs launch by launch (which may move the
+            # buffers, and then drops the graphs that point into them)
+            self.num_graph_steps -= 1
+            return self._eager_step(entries, device_tokens)
         rows = [i for i, e in enumerate(entries) if len(e.want)]
         if not rows:
             return None
@@ -223,6 +261,39 @@ class ModelRunner:
             return logits[:len(entries)]
         return logits[torch.tensor(rows, device=logits.device)]
 
+    def warm_up(self, contexts=None, buckets=None) -> int:
+        """Captures the decode graphs a server will need before the first
+        request arrives, so that no request pays for a first use: one graph
+        per batch bucket (powers of two up to ``max_num_seqs``) and per width
+        of the block tables (one for every doubling of the context up to
+        ``max_model_len``, or those that hold the given ``contexts``).  The
+        steps it runs hold dummy requests only: they read and write the page
+        that belongs to nobody.  Returns the number of graphs captured."""
+        if not self.use_cuda_graphs:
+            return 0
+        if buckets is None:
+            buckets, b = [], 1
+            while b < self.max_num_seqs:
+                buckets.append(b)
+                b *= 2
+            buckets.append(self.max_num_seqs)
+        if contexts is None:
+            contexts, c = [], 16 * self.cache.block_size
+            while c < self.max_model_len:
+                contexts.append(c)
+                c *= 2
+            contexts.append(self.max_model_len)
+        widths = sorted({self._table_width(min(int(c), self.max_model_len)) for c in contexts})
+        before = self.num_captures
+        for bucket in sorted({self._bucket(int(b)) for b in buckets}, reverse=True):
+            for width in widths:
+                if (bucket, width) not in self._graphs and len(self._graphs) < MAX_DECODE_GRAPHS:
+                    self._decode_graph(bucket, width).run([], None)
+        return self.num_captures - before
+
+    def graph_bytes(self) -> int:
+        """Device memory of the captured steps' activations."""
+        return self._graph_workspace.bytes() if self._graph_workspace is not None else 0
 
     # ---- steps with one prompt portion as CUDA graphs
     def _prompt_graph_plan(self, entries, total):
@@ -259,10 +330,7 @@ class ModelRunner:
         key = (padded, bucket, width)
         graph = self._prompt_graphs.get(key)
         if graph is None:
-            from .runtime import Workspace
-            if self._prompt_workspace is None:
-                self._prompt_workspace = Workspace(self.runtime.device, pin_old=True)
-            graph = _PromptGraph(self, padded, bucket, width, self._prompt_workspace)
+            graph = _PromptGraph(self, padded, bucket, width)
             self._prompt_graphs[key] = graph
         # the portion first, the decoded tokens behind it; the wanted rows are listed in the entries' own order,
         # so the first rows of the result are the caller's
@@ -277,17 +345,30 @@ class ModelRunner:
                     rows.append(padded + single)
                 single += 1
         self.num_graph_steps += 1
-        logits = graph.run(ordered, rows)
+        try:
+            logits = graph.run(ordered, rows)
+        except StepTooLarge:
+            self.num_graph_steps -= 1
+            return self._eager_step(entries)
         return logits[:len(rows)] if rows else None
 
 
 class _StepGraph:
-    """A step of fixed shape.  The first call runs eagerly (it warms every
-    kernel and library up with the real entries, so nothing is computed
-    twice), the second is captured, later ones replay the capture."""
+    """A step of fixed shape, captured at its first use.  Kernels and
+    libraries must have run once before they are captured (modules load at a
+    first launch, the library sets itself up): the first step of a shape whose
+    kernels have not run yet therefore runs launch by launch on its real
+    entries and is captured straight after (capturing runs nothing); a shape
+    whose kernels are warm is captured at once and replayed.  With
+    ``capture_at_first_use`` False the capture waits for the second use (shapes
+    that are many and often seen only once: prompt portions).  All captured
+    steps share one workspace and one memory pool."""
 
-    def __init__(self, runner: ModelRunner, workspace, num_wanted: int, width: int):
-        self.runner, self.workspace, self.num_wanted, self.width = runner, workspace, num_wanted, width
+    def __init__(self, runner: ModelRunner, num_wanted: int, width: int, warm_key, capture_at_first_use=True):
+        self.runner, self.num_wanted, self.width, self.warm_key = runner, num_wanted, width, warm_key
+        self.capture_at_first_use = capture_at_first_use
+        self.uses = 0
+        self.workspace = runner._workspace_for_graphs()
         self.capacity_at_capture = runner._capacity
         self.graph = None
         self.logits = None
@@ -295,32 +376,42 @@ class _StepGraph:
     def _launch(self, layout):
         r = self.runner
         if r._capacity != self.capacity_at_capture:
-            raise RuntimeError("the integer buffer moved after a step graph was captured")
-        if self.graph is None:
-            ctx = r._context(layout, self.workspace, num_wanted=self.num_wanted)
-            # a captured step serves every context its block tables can hold
-            ctx.context_bound = min(r.max_model_len, self.width * r.cache.block_size)
-            if self.logits is None:
-                self.logits = r.model.forward(ctx, r.cache)   # eager warm-up on the real data
-                return self.logits
-            # Capture.  The step's integers are already on the device; the
-            # captured kernels read them from the same addresses every time.
-            # No garbage collection while capturing: destroying an older graph
-            # (or freeing device memory) during capture invalidates it.
-            torch.cuda.synchronize()
-            gc.collect()
-            was_enabled = gc.isenabled()
-            gc.disable()
-            try:
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    self.logits = r.model.forward(ctx, r.cache)
-            finally:
-                if was_enabled:
-                    gc.enable()
-            self.graph = graph
-            # Capturing does not run the kernels: replay for this step's result.
-        self.graph.replay()
+            raise RuntimeError("the integer buffer moved after a step graph was made")
+        if self.graph is not None:
+            self.graph.replay()
+            return self.logits
+        ctx = r._context(layout, self.workspace, num_wanted=self.num_wanted)
+        # a captured step serves every context its block tables can hold
+        ctx.context_bound = min(r.max_model_len, self.width * r.cache.block_size)
+        ran = False
+        self.uses += 1
+        if self.warm_key not in r._warmed or (self.uses == 1 and not self.capture_at_first_use):
+            eager = r.model.forward(ctx, r.cache)          # on the real data: nothing is computed twice
+            r._warmed.add(self.warm_key)
+            ran = True
+            if not self.capture_at_first_use and self.uses == 1:
+                return eager
+        # Capture.  The step's integers are already on the device; the captured kernels read them from the same
+        # addresses every time.  No garbage collection while capturing: destroying an older graph (or freeing
+        # device memory) during capture invalidates it.
+        torch.cuda.synchronize()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            if r._graph_pool is None:
+                r._graph_pool = torch.cuda.graph_pool_handle()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=r._graph_pool):
+                self.logits = r.model.forward(ctx, r.cache)
+        finally:
+            if was_enabled:
+                gc.enable()
+        self.graph = graph
+        r.num_captures += 1
+        if ran:
+            assert eager is None or self.logits is None or eager.data_ptr() == self.logits.data_ptr()
+        else:
+            self.graph.replay()                            # capturing does not run the kernels
         return self.logits
 
 
@@ -328,8 +419,8 @@ class _PromptGraph(_StepGraph):
     """A prompt portion of ``padded`` rows (its own tokens, then dummies) and
     ``bucket`` single-token requests."""
 
-    def __init__(self, runner: ModelRunner, padded: int, bucket: int, width: int, workspace):
-        super().__init__(runner, workspace, 1 + bucket, width)
+    def __init__(self, runner: ModelRunner, padded: int, bucket: int, width: int):
+        super().__init__(runner, 1 + bucket, width, ("prompt", padded, bucket), capture_at_first_use=False)
         self.padded, self.bucket = padded, bucket
 
     def run(self, entries, rows):
@@ -337,18 +428,16 @@ class _PromptGraph(_StepGraph):
         wanted = np.zeros(n, dtype=np.int32)
         wanted[:len(rows)] = rows
         return self._launch(self.runner._pack(entries, pad_requests=n, fixed=self.width, pad_first_to=self.padded,
-                                              wanted_rows=wanted))
+                                              wanted_rows=wanted, may_reserve=False))
 
 
 class _DecodeGraph(_StepGraph):
     """A decode step for a fixed number of rows."""
 
     def __init__(self, runner: ModelRunner, bucket: int, width: int):
-        from .runtime import Workspace
-
-        super().__init__(runner, Workspace(runner.runtime.device, pin_old=True), bucket, width)
+        super().__init__(runner, bucket, width, ("decode", bucket))
         self.bucket = bucket
 
     def run(self, entries, device_tokens=None):
         return self._launch(self.runner._pack(entries, pad_requests=self.bucket, fixed=self.width, all_wanted=True,
-                                              device_tokens=device_tokens))
+                                              device_tokens=device_tokens, may_reserve=False))

@@ -5,7 +5,9 @@ and defaults (python/lyapunov_engine/entrypoints/cli.py:82-98): --model,
 --prompt, --max-tokens 64, --temperature 0.7, --top-p 1.0, --block-size 16,
 --num-blocks 512, --max-num-seqs 16, --max-batched-tokens 2048.  Added:
 --prompt-ids (token ids, no tokenizer needed), --top-k, --dtype, --seed,
---ignore-eos, --device.  The text tokenizer, as in the reference, is the one
+--ignore-eos, --device, and --random-weights (``--model`` then names a
+config.json, or a folder that holds one, and the weights are drawn from
+--seed; nothing is read from or written to the folder).  The text tokenizer, as in the reference, is the one
 ``transformers.AutoTokenizer`` finds in the model folder; it is loaded only
 when --prompt is given.
 
@@ -42,10 +44,19 @@ def run_generate(args) -> int:
     if not torch.cuda.is_available():
         print("lyapunov generate: no CUDA device; this engine has no CPU path", file=sys.stderr)
         return 1
-    print(f"Loading weights: {args.model}")
     config = EngineConfig(block_size=args.block_size, num_gpu_blocks=args.num_blocks, max_num_seqs=args.max_num_seqs,
                           max_num_batched_tokens=args.max_batched_tokens, dtype=args.dtype, device=args.device)
-    loaded = load_model(args.model, config.dtype, args.device)
+    if args.random_weights:
+        import os
+
+        path = os.path.join(args.model, "config.json") if os.path.isdir(args.model) else args.model
+        with open(path, "r", encoding="utf-8") as f:
+            raw = json.load(f)
+        print(f"Random weights (seed {args.seed}) for {path}")
+        loaded = load_model(config=raw, random_seed=args.seed, dtype=config.dtype, device=args.device)
+    else:
+        print(f"Loading weights: {args.model}")
+        loaded = load_model(args.model, config.dtype, args.device)
     config.model_config = loaded.spec
     engine = LLMEngine(loaded, config)
     sampling = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
@@ -97,6 +108,8 @@ def build_parser() -> argparse.ArgumentParser:
     gen.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     gen.add_argument("--seed", type=int, default=0)
     gen.add_argument("--ignore-eos", action="store_true")
+    gen.add_argument("--random-weights", action="store_true",
+                     help="--model names a config.json (or a folder with one); weights are drawn from --seed")
     gen.add_argument("--device", type=str, default="cuda:0")
 
     rnd = sub.add_parser("random-weights", help="Write a model folder with seeded random weights")

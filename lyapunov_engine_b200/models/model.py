@@ -9,6 +9,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+from .. import ops
 from ..parts.base import (BLOCKS, EMBEDDINGS, HEADS, NORMS, KVNeed, ModelSpec, ResidualStream, StateNeed,
                           TensorDecl)
 
@@ -43,6 +44,8 @@ class Model:
         self.states: list[StateNeed] = []
         self.runs: list[RunPlan] = []
         self._plan_cache()
+        # query-tile sizes that the mixers' kernels want listed in every step's integers
+        self.tile_sizes: list[int] = sorted({int(t) for b in self.blocks for t in b.mixer.tile_sizes()})
 
     # ---- what the cache must hold
     def _plan_cache(self) -> None:
@@ -104,6 +107,9 @@ class Model:
     def forward(self, ctx, cache):
         """Logits [wanted rows, vocab] float32 (None when nothing is wanted).
         ``cache.binding(run_index)`` gives each run its pages and state."""
+        for state in cache.states:
+            # a request whose first tokens are in this step starts from zero state, whoever held its slot before
+            ops.zero_fresh_state(state, ctx.state_slots, ctx.ctx_before, ctx.num_requests)
         resid = self.embedding.forward(ctx)
         stream = ResidualStream(resid)
         for index, run in enumerate(self.runs):

@@ -65,6 +65,8 @@ _attention: dict[int, ctypes.CDLL] = {}
 
 _CORE_SIGNATURES = {
     "le_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "le_zero_fresh_state": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "le_sm_count": [],
     "le_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "le_convert": [c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p],
     "le_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_float, c_int,
@@ -180,6 +182,31 @@ def embed(out_resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, statu
                            _ptr(status), _stream()), "le_embed")
 
 
+def zero_fresh_state(state: torch.Tensor, state_slots: torch.Tensor, ctx_before: torch.Tensor, num_requests: int) -> None:
+    """Zeroes row ``state_slots[b]`` of ``state`` [rows, ...] for every request b
+    of the step that has nothing in the cache yet (``ctx_before[b]`` == 0)."""
+    _need_cuda(state, state_slots, ctx_before)
+    assert state.is_contiguous() and state_slots.dtype == torch.int32 and ctx_before.dtype == torch.int32
+    row_bytes = state[0].numel() * state.element_size()
+    _check(core().le_zero_fresh_state(_ptr(state), row_bytes, state.shape[0], _ptr(state_slots), _ptr(ctx_before),
+                                      num_requests, _stream()), "le_zero_fresh_state")
+
+
+_sm_count: dict[int, int] = {}
+
+
+def sm_count() -> int:
+    """Multiprocessors of the current device (148 on a B200)."""
+    dev = torch.cuda.current_device()
+    n = _sm_count.get(dev)
+    if n is None:
+        n = int(core().le_sm_count())
+        if n <= 0:
+            raise KernelError("the device's multiprocessor count could not be read")
+        _sm_count[dev] = n
+    return n
+
+
 def swiglu(out: torch.Tensor, gate_up: torch.Tensor) -> None:
     """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
     _need_cuda(out, gate_up)
@@ -257,7 +284,7 @@ def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
 
 
 SKINNY_ROWS = 16          # up to this many rows a product streams weights through the package's own kernel (17..32 rows: 3-7 % slower per decode step than the library and the tcgen05 kernel, measured at three model sizes)
-SKINNY_BLOCKS = 512       # blocks worth having in flight on a B200 (4 slices of K for 2048 columns: measured best of 1..8)
+SKINNY_BLOCKS_PER_SM = 512 / 148   # blocks worth having in flight per multiprocessor (512 on a B200: 4 slices of K for 2048 columns, measured best of 1..8)
 
 
 def skinny_applies(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -365,7 +392,8 @@ def tc_fills_the_gpu(m: int, n: int) -> bool:
 def split_k_for(n_out: int, k: int) -> int:
     """How many slices of K give a product enough blocks to fill the GPU."""
     blocks = (n_out + 15) // 16
-    return max(1, min((SKINNY_BLOCKS + blocks - 1) // blocks, k // 512, 16))
+    in_flight = int(SKINNY_BLOCKS_PER_SM * sm_count() + 0.5)
+    return max(1, min((in_flight + blocks - 1) // blocks, k // 512, 16))
 
 
 def linear_for_residual(a: torch.Tensor, w: torch.Tensor, workspace, key: str, status=None):

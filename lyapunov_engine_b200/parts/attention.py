@@ -42,6 +42,9 @@ class AttentionMixer(Mixer):
     def cache_need(self):
         return KVNeed(self.num_kv_heads, self.head_dim, self.window)
 
+    def tile_sizes(self):
+        return attention_kernels.tile_sizes()
+
     def tensors(self):
         q, k, v, o = self.names
         H, nh, nkv, hd = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim

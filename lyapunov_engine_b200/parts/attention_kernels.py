@@ -23,7 +23,7 @@ PREFILL_TILE = 128
 DECODE_KEYS_PER_SPLIT = 256     # a split is worth its launch from about four tiles of keys
 DECODE_MAX_SPLITS = 64
 USE_TC_ATTENTION = os.environ.get("LYAPUNOV_TC_ATTENTION", "1") not in ("0", "")
-RESIDENT_BLOCKS = 2 * 148       # blocks of the decode kernel that are resident at once on a B200
+DECODE_BLOCKS_PER_SM = 2        # blocks of the decode kernel that a multiprocessor holds at once (by their shared memory)
 
 
 def tile_sizes() -> list[int]:
@@ -44,8 +44,9 @@ def decode_splits(num_requests: int, num_heads: int, num_kv_heads: int, context_
     by_keys = max(1, (context_bound + DECODE_KEYS_PER_SPLIT - 1) // DECODE_KEYS_PER_SPLIT)
     limit = max(1, min(by_keys, DECODE_MAX_SPLITS))
     best, best_fill = 1, 0.0
+    resident = DECODE_BLOCKS_PER_SM * ops.sm_count()
     for splits in range(1, limit + 1):
-        waves = blocks * splits / RESIDENT_BLOCKS
+        waves = blocks * splits / resident
         fill = waves / -(-waves // 1)        # waves / ceil(waves)
         if fill >= 0.85:
             return splits

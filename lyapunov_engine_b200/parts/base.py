@@ -23,6 +23,16 @@ Interfaces (all tensors are CUDA tensors; T tokens in the step, H width):
     say what the cache manager must hold for it; ``forward(x, ctx, cache) ->
     y`` mixes the tokens of the step (x, y: [T, H] activations) using
     ``cache.kv`` (pages) and/or ``cache.state`` (one row per state slot).
+    State: request b of the step owns row ``ctx.state_slots[b]`` of
+    ``cache.state``.  Before the step's first layer the framework zeroes the
+    rows of requests whose ``ctx.ctx_before[b]`` is 0 (a new request, or one
+    recomputed after pre-emption), so a mixer reads its row unconditionally
+    and writes it back.  Rows of a step that stand for no request (padding of a
+    fixed-shape batch) carry slot -1: a kernel uses the buffer's last row for
+    them, which belongs to nobody, or skips them.  Steps of a model whose
+    mixers keep state are never padded with dummy tokens behind a request's
+    own.  ``tile_sizes()`` names the query-tile sizes its kernels want listed
+    in the step's integers (``ctx.tiles``).
 ``FeedForward``
     ``forward(x, ctx) -> y``.
 ``Block``
@@ -136,6 +146,13 @@ class Mixer(Part):
 
     def state_need(self) -> StateNeed | None:
         return None
+
+    def tile_sizes(self) -> list[int]:
+        """Query-tile sizes its kernels want: for each, ``ctx.tiles[size]`` lists
+        (request of each tile, first query token of the tile within the
+        request, number of tiles, how many of them belong to requests that
+        bring several tokens), those of several tokens first."""
+        return []
 
     def forward(self, x, ctx, cache):
         raise NotImplementedError

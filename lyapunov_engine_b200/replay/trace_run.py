@@ -15,7 +15,9 @@ as little-endian float32 in the order of the entries and of ``want``.  After
 every step ``done <step>`` is printed and flushed.
 
 The cache pool holds ``--max-tokens`` tokens (in pages of ``--block-size``),
-so pages are used again as requests end.
+so pages are used again as requests end.  At exit ``DIR/pages.json`` says how
+the pool was used: pages in the pool, pages handed out in all, how many of
+those had been used before, and the most that were held at once.
 """
 from __future__ import annotations
 
@@ -68,6 +70,7 @@ def main(argv=None) -> int:
         manager = cache.manager
         live: dict[str, object] = {}
         next_id = 0
+        peak_used = 0
         vocab = loaded.spec.vocab_size
         for line in sys.stdin:
             line = line.strip()
@@ -99,6 +102,8 @@ def main(argv=None) -> int:
                                      f"({manager.get_num_free_blocks()} free pages of {args.block_size} tokens); "
                                      f"raise --max-tokens")
                 entries.append(host.StepEntry(seq, start, len(tokens), want))
+            if loaded.model.groups:
+                peak_used = max(peak_used, max(manager.get_num_used_blocks(g) for g in range(manager.get_num_groups())))
             logits = runner.step(entries) if entries else None
             if logits is not None:
                 data = logits.detach().to("cpu", torch.float32).contiguous().numpy()
@@ -118,6 +123,10 @@ def main(argv=None) -> int:
                     manager.free(seq)
             sys.stdout.write(f"done {number}\n")
             sys.stdout.flush()
+        with open(os.path.join(args.out, "pages.json"), "w", encoding="utf-8") as f:
+            json.dump({"pool_pages": num_blocks, "block_size": args.block_size,
+                       "allocations": manager.get_num_allocations(), "reuses": manager.get_num_reuses(),
+                       "peak_used_pages": peak_used, "steps": runner.num_steps, "graph_steps": runner.num_graph_steps}, f)
         problem = manager.audit()
         if problem:
             print(f"trace_run: cache audit failed: {problem}", file=sys.stderr)
