@@ -786,6 +786,17 @@ LE_API int le_attention_decode_bf16_static(void *out, int64_t out_stride, const 
 
 #else  // head sizes above 128 use the generic kernel
 
+#include "attention_static_scratch.h"
+
 LE_API int le_attention_mma_available() { return 0; }
+
+// There is no split-key kernel for this head size: the no-allocation entry
+// point exists so that a caller can link against it, and refuses every call.
+LE_API int le_attention_decode_bf16_static(void *, int64_t, const void *, int64_t, const void *, const void *, const int32_t *,
+                                           int, const int32_t *, const int32_t *, const int32_t *, int, int, int, int, int,
+                                           int, float, int, int *, cudaStream_t) {
+  return le::invalid("le_attention_decode_bf16_static: this library was built for head size %d; the split-key decode "
+                     "attention exists for head sizes up to 128", LE_HEAD_DIM);
+}
 
 #endif

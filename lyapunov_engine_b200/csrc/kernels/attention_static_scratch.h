@@ -14,19 +14,33 @@
  * library itself, in a fixed array in device memory.
  *
  * What to know before using it:
- *   - The array holds LE_STATIC_SCRATCH_FLOATS floats (4 MiB).  Every GPU on
- *     which the library is loaded keeps that much until the process exits.
+ *   - The array holds LE_STATIC_SCRATCH_FLOATS floats (4 MiB).  The attention
+ *     kernels are built as one library per head size, and each of them has
+ *     an array of its own: every GPU on which such a library is loaded keeps
+ *     4 MiB for it until the process exits.
+ *   - Libraries for head sizes above 128 have no split-key kernel; there the
+ *     symbol exists and refuses every call with LE_INVALID.
  *   - A call whose partial results do not fit is refused with LE_INVALID
  *     (le_last_error() names the size asked for and the limit); nothing is
  *     launched.  The size needed is
  *     le_attention_decode_scratch_floats(num_requests, num_heads, num_splits).
  *   - The first call on each device looks the array's address up (with that
  *     device current).  Make that first call outside any stream capture.
+ *     The driver may also load the library's kernels and place the array on
+ *     the device at that first call (it loads modules lazily unless
+ *     CUDA_MODULE_LOADING=EAGER is set), which takes device memory once: a
+ *     caller with a window in which nothing may be allocated makes one call
+ *     before that window opens.
+ *   - The address is remembered per device ordinal.  After cudaDeviceReset
+ *     (or anything else that destroys the device's primary context) it is
+ *     stale; this entry point is not for processes that reset a device and
+ *     carry on.
  *   - All calls on a device share the one array and it keeps what the last
  *     call left.  The kernels write every slot they later read, so nothing
  *     needs clearing, but two calls that overlap on the GPU (different
  *     streams, or the same call from two threads) race on it: order them.
- *   - Neither this function nor anything it calls allocates or frees memory.
+ *   - Apart from that first call, neither this function nor anything it
+ *     calls allocates or frees memory.
  *
  * Arguments and result are those of le_attention_decode_bf16 without the
  * scratch pointer.

@@ -16,8 +16,9 @@ every step ``done <step>`` is printed and flushed.
 
 The cache pool holds ``--max-tokens`` tokens (in pages of ``--block-size``),
 so pages are used again as requests end.  At exit ``DIR/pages.json`` says how
-the pool was used: pages in the pool, pages handed out in all, how many of
-those had been used before, and the most that were held at once.
+the pool was used (pages in the pool, pages handed out in all, how many of
+those had been used before, the most that were held at once) and how many
+steps ran as captured graphs.
 """
 from __future__ import annotations
 
@@ -126,7 +127,9 @@ def main(argv=None) -> int:
         with open(os.path.join(args.out, "pages.json"), "w", encoding="utf-8") as f:
             json.dump({"pool_pages": num_blocks, "block_size": args.block_size,
                        "allocations": manager.get_num_allocations(), "reuses": manager.get_num_reuses(),
-                       "peak_used_pages": peak_used, "steps": runner.num_steps, "graph_steps": runner.num_graph_steps}, f)
+                       "peak_used_pages": peak_used, "steps": runner.num_steps, "graph_steps": runner.num_graph_steps,
+                       "decode_graphs_captured": sum(g.graph is not None for g in runner._graphs.values()),
+                       "prompt_graphs_captured": sum(g.graph is not None for g in runner._prompt_graphs.values())}, f)
         problem = manager.audit()
         if problem:
             print(f"trace_run: cache audit failed: {problem}", file=sys.stderr)

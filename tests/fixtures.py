@@ -69,6 +69,12 @@ TINY_B = {
 }
 TINY_B_PAGE = 8
 
+# tiny-B with every number as the baseline's configuration list states it (vocabulary 512, feed-forward 320;
+# weights N(0, 0.02), see the replay tests).  TINY_B above departs from it on purpose: a vocabulary and a
+# feed-forward width that are no multiples of 8 or 16, and larger weights with peaked attention, which make a wrong
+# key, position or page show.
+TINY_B_STATED = dict(TINY_B, vocab_size=512, intermediate_size=320)
+
 # A third shape for long contexts: head size 64 as in the 1B model, more
 # groups, a width that is a multiple of 8 only.
 TINY_C = {

@@ -112,14 +112,16 @@ def plain_rotate_half(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> 
     return x * cos + rotated * sin
 
 
-def plain_attention(q, k, v, window: int | None = None, prob_dtype=None) -> torch.Tensor:
+def plain_attention(q, k, v, window: int | None = None, prob_dtype=None, prob_shift: float = 0.0) -> torch.Tensor:
     """Causal grouped-query attention over a whole sequence
     (python/lyapunov_engine/ops.py:100-121): scale 1/sqrt(hd), kv heads
     repeated for their group, keys after the query masked, softmax, times V.
     q: [nh, T, hd]; k, v: [nkv, T, hd].  ``window`` (not in the reference):
     a query at p sees keys p-window+1 .. p only.  ``prob_dtype`` models a
     pipeline that stores exp(score - max) in that type before it multiplies by
-    V (and still divides by the unrounded sum)."""
+    V (and still divides by the unrounded sum); ``prob_shift`` one that scales
+    its numerators by another bound than the row's true maximum, exp(score -
+    max - shift): the same mathematics, other roundings."""
     nh, T, hd = q.shape
     nkv = k.shape[0]
     scale = 1.0 / (hd ** 0.5)
@@ -133,7 +135,7 @@ def plain_attention(q, k, v, window: int | None = None, prob_dtype=None) -> torc
         mask |= torch.tril(torch.ones(T, T, dtype=torch.bool), diagonal=-window)
     scores = scores.masked_fill(mask, float("-inf"))
     if prob_dtype is not None:
-        p = torch.exp(scores - scores.max(dim=-1, keepdim=True).values)
+        p = torch.exp(scores - scores.max(dim=-1, keepdim=True).values - prob_shift)
         return torch.matmul(rounded(p, prob_dtype), v) / p.sum(dim=-1, keepdim=True)
     probs = torch.softmax(scores, dim=-1)
     return torch.matmul(probs, v)
@@ -147,7 +149,8 @@ def rounded(x: torch.Tensor, act_dtype) -> torch.Tensor:
     return x if act_dtype is None else x.to(act_dtype).to(x.dtype)
 
 
-def plain_attention_layer(x, wq, wk, wv, wo, nh, nkv, hd, cos, sin, window=None, act_dtype=None, prob_dtype=None):
+def plain_attention_layer(x, wq, wk, wv, wo, nh, nkv, hd, cos, sin, window=None, act_dtype=None, prob_dtype=None,
+                          prob_shift=0.0):
     """q/k/v projections, head split, RoPE on q and k, attention, o projection
     (python/lyapunov_engine/models/llama.py:61-106)."""
     T = x.shape[0]
@@ -156,7 +159,7 @@ def plain_attention_layer(x, wq, wk, wv, wo, nh, nkv, hd, cos, sin, window=None,
     v = rounded(x @ wv.T, act_dtype).view(T, nkv, hd).transpose(0, 1)
     q = rounded(plain_rotate_half(q, cos, sin), act_dtype)
     k = rounded(plain_rotate_half(k, cos, sin), act_dtype)
-    o = rounded(plain_attention(q, k, v, window, prob_dtype), act_dtype)
+    o = rounded(plain_attention(q, k, v, window, prob_dtype, prob_shift), act_dtype)
     o = o.transpose(0, 1).contiguous().view(T, nh * hd)
     return rounded(o @ wo.T, act_dtype)
 
@@ -173,7 +176,8 @@ def plain_mlp(x, w_gate, w_up, w_down, act_dtype=None) -> torch.Tensor:
     return rounded(rounded(act, act_dtype) @ w_down.T, act_dtype)
 
 
-def plain_block(h, w: dict, prefix: str, cfg: dict, cos, sin, window=None, act_dtype=None, prob_dtype=None):
+def plain_block(h, w: dict, prefix: str, cfg: dict, cos, sin, window=None, act_dtype=None, prob_dtype=None,
+                prob_shift=0.0):
     """Pre-norm residual block (python/lyapunov_engine/models/llama.py:136-165)."""
     eps = float(cfg["rms_norm_eps"])
     nh = cfg["num_attention_heads"]
@@ -186,7 +190,7 @@ def plain_block(h, w: dict, prefix: str, cfg: dict, cos, sin, window=None, act_d
         w[prefix + "self_attn.k_proj.weight"],
         w[prefix + "self_attn.v_proj.weight"],
         w[prefix + "self_attn.o_proj.weight"],
-        nh, nkv, hd, cos, sin, window, act_dtype, prob_dtype,
+        nh, nkv, hd, cos, sin, window, act_dtype, prob_dtype, prob_shift,
     )
     h = h + a
     n = rounded(plain_rmsnorm(h, w[prefix + "post_attention_layernorm.weight"], eps), act_dtype)
@@ -200,7 +204,7 @@ def plain_block(h, w: dict, prefix: str, cfg: dict, cos, sin, window=None, act_d
     return h + m
 
 
-def plain_forward(cfg: dict, w: dict, ids, windows=None, act_dtype=None, prob_dtype=None) -> torch.Tensor:
+def plain_forward(cfg: dict, w: dict, ids, windows=None, act_dtype=None, prob_dtype=None, prob_shift=0.0) -> torch.Tensor:
     """Logits [T, V] of one whole sequence starting at position 0
     (python/lyapunov_engine/models/llama.py:196-225).  The output head is
     ``lm_head.weight`` when the folder has it, else the embedding matrix
@@ -216,7 +220,7 @@ def plain_forward(cfg: dict, w: dict, ids, windows=None, act_dtype=None, prob_dt
     cos, sin = cos.to(dtype), sin.to(dtype)
     for i in range(cfg["num_hidden_layers"]):
         window = windows[i] if windows is not None else None
-        h = plain_block(h, w, f"model.layers.{i}.", cfg, cos, sin, window, act_dtype, prob_dtype)
+        h = plain_block(h, w, f"model.layers.{i}.", cfg, cos, sin, window, act_dtype, prob_dtype, prob_shift)
     n = rounded(plain_rmsnorm(h, w["model.norm.weight"], float(cfg["rms_norm_eps"])), act_dtype)
     head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
     return n @ head.T

@@ -89,6 +89,25 @@ def run_trace(trace: Trace, model_dir: str, dtype: str, out_dir: str, max_tokens
     return out
 
 
+def peak_pool_tokens(trace: Trace, page: int) -> int:
+    """The fewest tokens (a multiple of 64) whose pages hold what the trace's
+    live requests hold at their peak, each request in whole pages."""
+    held, peak = {}, 0
+    for step in trace.steps:
+        for e in step["entries"]:
+            held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+        peak = max(peak, sum((n + page - 1) // page for n in held.values()))
+        for rid in step["end"]:
+            held.pop(rid, None)
+    return (peak * page + 63) // 64 * 64
+
+
+def read_pages(out_dir: str) -> dict:
+    """What trace_run wrote about its page pool at exit."""
+    with open(os.path.join(out_dir, "pages.json"), "r", encoding="utf-8") as f:
+        return json.load(f)
+
+
 def whole_trace(requests: dict) -> Trace:
     """Each request alone and whole, one step each."""
     t = Trace()
@@ -174,3 +193,67 @@ def compare(got: dict, reference: dict, atol: float, rtol: float, what: str):
                                  f"(|diff| {err[i]:.3e} > {bound[i]:.3e}); max |diff| at this place {err.max():.3e}")
         worst = max(worst, float(err.max()))
     return worst
+
+
+# --------------------------------------------------------------------------
+# bfloat16: what "equal up to rounding" means, measured
+# --------------------------------------------------------------------------
+BF16_RMS_ALL = 1.25     # the root mean square of all differences, in units of the noise's
+BF16_RMS_ROW = 2.5      # the root mean square over one place's logits
+BF16_MAX_ABS = 1.6      # the largest single difference, in units of the noise's largest
+
+
+def bf16_references(cfg, weights, requests, plain_forward):
+    """The plain implementation with the pipeline's bfloat16 roundings (weights,
+    activations between products, softmax numerators), and how far a second,
+    equally valid evaluation of the same pipeline lies from it: sums in 64
+    bits instead of 32, and the numerators scaled by exp(-0.5) before they are
+    rounded (a kernel that keeps a running or lazy maximum rounds numerators
+    that are scaled by another bound than the row's final maximum).  The two
+    runs differ in nothing but which way roundings fall, as the engine does
+    from either; their distance is the unit the engine's is measured in.
+    Returns (reference logits per request, {"rms": ..., "max": ...})."""
+    rounded = {k: v.to(torch.bfloat16).float() for k, v in weights.items()}
+    wide = {k: v.double() for k, v in rounded.items()}
+    bf = torch.bfloat16
+    ref = {r: plain_forward(cfg, rounded, ids, act_dtype=bf, prob_dtype=bf) for r, ids in requests.items()}
+    square, count, largest = 0.0, 0, 0.0
+    for r, ids in requests.items():
+        other = plain_forward(cfg, wide, ids, act_dtype=bf, prob_dtype=bf, prob_shift=0.5).float()
+        d = (other - ref[r]).double()
+        square += float(d.pow(2).sum())
+        count += d.numel()
+        largest = max(largest, float(d.abs().max()))
+    return ref, {"rms": (square / max(count, 1)) ** 0.5, "max": largest}
+
+
+def compare_bf16(got: dict, reference: dict, noise: dict, what: str):
+    """Three bounds in units of the measured noise (see bf16_references): the
+    root mean square of all differences (the float32 model's logits lie 1.6 to
+    2.3 units from the bfloat16 model's and fail it), the root mean square at
+    every single place (a wrong key, position or page moves one place's logits
+    by 5 to 50 units), and the largest single difference."""
+    square, count = 0.0, 0
+    for (rid, p) in sorted(got):
+        ref = reference[rid][p].numpy().astype(np.float64)
+        row = got[(rid, p)].astype(np.float64)
+        if not np.all(np.isfinite(row)):
+            raise AssertionError(f"{what}: request {rid!r} position {p}: logits are not finite")
+        d = row - ref
+        row_rms = float(np.sqrt(np.mean(d * d)))
+        if row_rms > BF16_RMS_ROW * noise["rms"]:
+            raise AssertionError(f"{what}: request {rid!r} position {p}: the logits lie {row_rms:.3e} (rms) from the plain "
+                                 f"implementation's, {row_rms / noise['rms']:.2f} units of rounding noise "
+                                 f"(allowed {BF16_RMS_ROW})")
+        worst = float(np.abs(d).max())
+        if worst > BF16_MAX_ABS * noise["max"]:
+            i = int(np.argmax(np.abs(d)))
+            raise AssertionError(f"{what}: request {rid!r} position {p}: logit {i} is {row[i]!r}, plain says {ref[i]!r} "
+                                 f"(|diff| {worst:.3e} > {BF16_MAX_ABS * noise['max']:.3e})")
+        square += float(np.sum(d * d))
+        count += d.size
+    total = (square / max(count, 1)) ** 0.5
+    if total > BF16_RMS_ALL * noise["rms"]:
+        raise AssertionError(f"{what}: all logits together lie {total:.3e} (rms) from the plain implementation's, "
+                             f"{total / noise['rms']:.2f} units of rounding noise (allowed {BF16_RMS_ALL})")
+    return total / noise["rms"]

@@ -163,6 +163,37 @@ def test_linear_bf16(M, N, K):
     torch.testing.assert_close(out16.float().cpu(), want, atol=0.05, rtol=1e-2)
 
 
+@pytest.mark.parametrize("M", [17, 64, 2048])
+def test_linear_bf16_long_sums_keep_32_bits(M):
+    """Products with more than 16 rows go to the library.  Over K = 8192 its
+    result must be the 64-bit product of the same bfloat16 inputs rounded once:
+    partial sums that passed through bfloat16 (the library's default for
+    split-K reductions, which the runtime switches off) would lose bits of
+    every slice.  The bound is one rounding of the output, not a percentage."""
+    import lyapunov_engine_b200.engine.runtime as runtime
+
+    runtime.Runtime(DEV, torch.bfloat16)        # (building a runtime is what sets the library's accumulation mode)
+    assert torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction is False
+    K, N = 8192, 2048
+    g = torch.Generator().manual_seed(M)
+    # inputs with a common sign, so that the sums grow with K and a lost low-order bit shows
+    a = (torch.rand(M, K, generator=g) + 0.5).bfloat16()
+    w = (torch.rand(N, K, generator=g) + 0.5).bfloat16()
+    want = a.double() @ w.double().t()
+    out32 = torch.empty(M, N, device=DEV)
+    ops().linear(out32, a.to(DEV), w.to(DEV))
+    # 32-bit accumulation of 8192 terms of one sign.  The tensor cores' adders truncate instead of rounding to
+    # nearest, which shows as a common shortfall of 2.5e-5 here; partial sums rounded to bfloat16 would show as
+    # 1e-3 and more (2^-9 per slice of K).
+    assert float(((out32.cpu().double() - want) / want).abs().max()) < 1e-4
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops().linear(out16, a.to(DEV), w.to(DEV))
+    # one rounding to bfloat16: at most half a unit in the last place of the result (8 significant bits: a unit
+    # is 2^(exponent - 7)), plus the sum's own error
+    half_unit = torch.exp2(torch.floor(torch.log2(want)) - 8)
+    assert bool(((out16.cpu().double() - want).abs() <= half_unit + 1e-4 * want).all())
+
+
 @pytest.mark.parametrize("vocab,scratch", [(1003, False), (1003, True), (128256, True), (20001, True)])
 def test_argmax_first_of_equal_maxima(vocab, scratch):
     logits = torch.randn(6, vocab)

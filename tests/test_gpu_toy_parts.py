@@ -21,7 +21,9 @@ DECAY = 0.8
 @register_mixer("toy_decay")
 class ToyDecayMixer(Mixer):
     """s_t = decay * s_{t-1} + x_t W_in^T;  y_t = s_t W_out^T.  The state s of
-    each request lives in its state slot between steps."""
+    each request lives in its state slot between steps.  It never clears a
+    slot itself: the framework hands a request's first step a zeroed row,
+    whoever held the slot before."""
 
     def __init__(self, hidden_size, decay, in_name, out_name):
         self.hidden_size, self.decay, self.names = hidden_size, decay, (in_name, out_name)
@@ -37,13 +39,13 @@ class ToyDecayMixer(Mixer):
         self.runtime = runtime
 
     def forward(self, x, ctx, cache):
-        cu, before, slots = ctx.cu_q.tolist(), ctx.ctx_before.tolist(), ctx.state_slots.tolist()
+        cu, slots = ctx.cu_q.tolist(), ctx.state_slots.tolist()
         u = (x.float() @ self.w_in.float().t())
         y = torch.empty_like(u)
         for b in range(ctx.num_requests):
             if slots[b] < 0:
                 continue
-            s = cache.state[slots[b]] if before[b] > 0 else torch.zeros(self.hidden_size, device=x.device)
+            s = cache.state[slots[b]]
             for t in range(cu[b], cu[b + 1]):
                 s = self.decay * s + u[t]
                 y[t] = s
@@ -193,9 +195,10 @@ def test_toy_model_steps_through_the_framework(toy):
 
 def test_toy_model_generates_through_the_entry_point(toy):
     folder, w = toy
-    engine = LLMEngine.from_pretrained(folder, dtype="float32", num_blocks=24, block_size=4, max_num_seqs=3,
+    # two state slots for five requests: the later ones get slots that others have left their state in
+    engine = LLMEngine.from_pretrained(folder, dtype="float32", num_blocks=24, block_size=4, max_num_seqs=2,
                                        max_num_batched_tokens=16, use_cuda_graphs=False, max_model_len=96)
-    prompts = [fixtures.random_ids({"vocab_size": V}, n, 40 + n) for n in (3, 19, 26)]
+    prompts = [fixtures.random_ids({"vocab_size": V}, n, 40 + n) for n in (3, 19, 26, 1, 11)]
     outs = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=7, ignore_eos=True))
     for p, o in zip(prompts, outs):
         ids, want = list(p), []

@@ -62,7 +62,7 @@ def test_static_scratch_entry_point_equals_the_ordinary_one_twice_in_a_row():
         assert rc == 0, lib.le_last_error().decode()
         torch.cuda.synchronize()
         ops.check_status(status)
-        torch.testing.assert_close(static.float().cpu(), ordinary.float().cpu(), atol=2e-2, rtol=2e-2)
+        assert torch.equal(static, ordinary)      # the same kernels on the same inputs: bit for bit
         torch.testing.assert_close(static.float().cpu(), case["want"], atol=2e-2, rtol=2e-2)
 
 
@@ -83,3 +83,10 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     assert call_static(fn, case, nh, nkv, hd, page, 1, out, status) == 0   # one split needs no scratch at all
     torch.cuda.synchronize()
     torch.testing.assert_close(out.float().cpu(), case["want"], atol=2e-2, rtol=2e-2)
+
+
+def test_static_scratch_entry_point_of_a_large_head_library_refuses():
+    """Libraries for head sizes above 128 export the symbol and refuse the call."""
+    lib, fn = symbol(256)
+    assert fn(None, 0, None, 0, None, None, None, 0, None, None, None, 1, 4, 2, 16, 8, 0, 1.0, 2, None, None) == -1
+    assert "head sizes up to 128" in lib.le_last_error().decode()
