@@ -411,9 +411,11 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
                         const bf16 *__restrict__ v_cache, const int32_t *__restrict__ block_table, int max_blocks,
                         const int32_t *__restrict__ cu_q, const int32_t *__restrict__ ctx_before,
                         const int32_t *__restrict__ requests, int num_heads, int num_kv_heads, int page_size,
-                        int page_shift, int num_pages, int window, float scale, int num_splits, int *__restrict__ status) {
+                        int page_shift, int num_pages, int window, float scale, int num_splits, int cluster_merge,
+                        int *__restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  le::wait_for_predecessor();
+  // (the kernel before this one wrote the queries and the newest key and value of every request; what is
+  // read before wait_for_predecessor() below is older than that: the step's integers and keys of earlier steps)
   const int split = blockIdx.x;
   const int group = num_heads / num_kv_heads;
   const int row_tiles = (group + 15) / 16;
@@ -442,6 +444,37 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
   auto v_stage = [&](int s) { return my_smem + s * 2 * DC_TILE * HD + DC_TILE * HD; };
   auto tile_start = [&](int i) { return k_begin + (warp + i * DC_WARPS) * DC_TILE; };
 
+  ScoreOffsets<DC_TILE / 8> k_at;
+  ValueOffsets<DC_TILE / 16> v_at;
+  k_at.init(lane);
+  v_at.init(lane);
+  // pages that divide a tile and tiles that start on a page boundary take the cheap loader
+  const bool paged_tiles = page_shift >= 0 && page_size <= DC_TILE && (k_begin & (page_size - 1)) == 0;
+  auto load_tile = [&](int stage, int i) {
+    if (paged_tiles) load_kv_tile_warp32(k_stage(stage), v_stage(stage), kv, tile_start(i), k_end, lane, status);
+    else load_kv_tile<DC_TILE>(k_stage(stage), v_stage(stage), kv, tile_start(i), k_end, lane, 32, status);
+  };
+  // The first tiles are asked for while the kernel before this one still runs, unless they hold the key at
+  // position p, which that kernel writes.
+  auto older_than_this_step = [&](int i) { return tile_start(i) + DC_TILE <= p; };
+  bool late = false;
+#pragma unroll
+  for (int s = 0; s < DC_STAGES - 1; ++s) {
+    if (s < my_tiles) {
+      if (older_than_this_step(s)) load_tile(s, s);
+      else late = true;
+    }
+    cp_async_commit();
+  }
+  le::wait_for_predecessor();
+  if (late) {                                 // (only the warps at the very end of a request's keys)
+#pragma unroll
+    for (int s = 0; s < DC_STAGES - 1; ++s)
+      if (s < my_tiles && !older_than_this_step(s)) load_tile(s, s);
+    cp_async_commit();
+    cp_async_wait<0>();                       // so that the order of the groups below stays what the loop expects
+  }
+
   // query fragments straight from global memory: rows are the group's heads
   uint32_t qf[KSTEPS][4];
 #pragma unroll
@@ -454,10 +487,6 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
     }
   }
 
-  ScoreOffsets<DC_TILE / 8> k_at;
-  ValueOffsets<DC_TILE / 16> v_at;
-  k_at.init(lane);
-  v_at.init(lane);
   float o[NT_O][4];
 #pragma unroll
   for (int nt = 0; nt < NT_O; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
@@ -465,17 +494,6 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
   const float sl2 = scale * LOG2E;
   const bool upper_rows = heads_here > 8;     // rows 8..15 of the MMA are padding for small groups
 
-  // pages that divide a tile and tiles that start on a page boundary take the cheap loader
-  const bool paged_tiles = page_shift >= 0 && page_size <= DC_TILE && (k_begin & (page_size - 1)) == 0;
-  auto load_tile = [&](int stage, int i) {
-    if (paged_tiles) load_kv_tile_warp32(k_stage(stage), v_stage(stage), kv, tile_start(i), k_end, lane, status);
-    else load_kv_tile<DC_TILE>(k_stage(stage), v_stage(stage), kv, tile_start(i), k_end, lane, 32, status);
-  };
-#pragma unroll
-  for (int s = 0; s < DC_STAGES - 1; ++s) {
-    if (s < my_tiles) load_tile(s, s);
-    cp_async_commit();
-  }
   for (int it = 0; it < my_tiles; ++it) {
     cp_async_wait<DC_STAGES - 2>();
     __syncwarp();                          // tile `it` has landed for every lane; stage of it - 1 is free
@@ -566,6 +584,12 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
     }
   }
   __syncthreads();
+  // with `cluster_merge` the splits of a (request, kv head) are the blocks of one cluster: each leaves its partial
+  // result in its own shared memory, and after the cluster has met the blocks share out the heads' columns and
+  // add the splits up from there, so no partial result goes through global memory and no merge kernel follows
+  float *cl_o = sm_l + DC_WARPS * 16;                           // [16 rows][HD]
+  float *cl_m = cl_o + 16 * HD;                                 // [16]
+  float *cl_l = cl_m + 16;                                      // [16]
   for (int i = tid; i < heads_here * HD; i += DC_THREADS) {
     const int row = i / HD, d = i % HD;
     float m = -INFINITY;
@@ -582,6 +606,12 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
     const int head = h0 + row;
     if (num_splits == 1) {
       out[tok * out_stride + head * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    } else if (cluster_merge) {
+      cl_o[row * HD + d] = acc;
+      if (d == 0) {
+        cl_m[row] = m * sl2;                  // in log2 units (-inf stays -inf)
+        cl_l[row] = l;
+      }
     } else {
       const int64_t slot = (static_cast<int64_t>(blockIdx.z) * num_heads + head) * num_splits + split;
       part_o[slot * HD + d] = acc;
@@ -590,6 +620,25 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
         part_ml[slot * 2 + 1] = l;
       }
     }
+  }
+  if (num_splits > 1 && cluster_merge) {
+    le::cluster_sync();
+    // block `split` of the cluster takes every num_splits-th column
+    for (int i = tid * num_splits + split; i < heads_here * HD; i += DC_THREADS * num_splits) {
+      const int row = i / HD, d = i % HD;
+      float m = -INFINITY;
+      for (int s2 = 0; s2 < num_splits; ++s2) m = fmaxf(m, le::cluster_peer_f32(cl_m + row, s2));
+      float acc = 0.0f, l = 0.0f;
+      for (int s2 = 0; s2 < num_splits; ++s2) {
+        const float ms = le::cluster_peer_f32(cl_m + row, s2);
+        if (ms == -INFINITY) continue;                          // a split without keys
+        const float f = le::fast_exp2(ms - m);
+        acc += f * le::cluster_peer_f32(cl_o + row * HD + d, s2);
+        l += f * le::cluster_peer_f32(cl_l + row, s2);
+      }
+      out[tok * out_stride + (h0 + row) * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    }
+    le::cluster_sync();                       // nobody leaves while another still reads its shared memory
   }
 }
 
@@ -687,9 +736,49 @@ LE_API int64_t le_attention_decode_scratch_floats(int num_requests, int num_head
   return num_splits <= 1 ? 0 : static_cast<int64_t>(num_requests) * num_heads * num_splits * (HD + 2);
 }
 
+// Up to this many splits are merged inside the attention kernel, by the blocks of a thread-block cluster;
+// beyond it the partial results go through scratch memory to a merge kernel.  By default up to 8 (clusters of
+// 16 need the non-portable size and were slower than the merge kernel at batches of 1 and 2);
+// LYAPUNOV_CLUSTER_MERGE=<n> sets another limit up to 16, 0 switches it off.
+constexpr int DC_MAX_CLUSTER = 16;
+
+// Whether the device can hold a cluster of `num_splits` of the decode kernel's blocks (asked once per size).
+static bool cluster_splits_fit(int num_splits, size_t smem) {
+  static const int limit = [] {
+    const char *env = getenv("LYAPUNOV_CLUSTER_MERGE");
+    const int n = env == nullptr ? 8 : atoi(env);
+    return n < 0 ? 0 : (n > DC_MAX_CLUSTER ? DC_MAX_CLUSTER : n);
+  }();
+  if (num_splits < 2 || num_splits > limit) return false;
+  static int known[DC_MAX_CLUSTER + 1] = {};            // 0: not asked yet, 1: fits, -1: does not
+  if (known[num_splits] == 0) {
+    bool fits = true;
+    if (num_splits > 8)
+      fits = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+    if (fits) {
+      cudaLaunchConfig_t config = {};
+      config.gridDim = dim3(num_splits, 1, 1);
+      config.blockDim = dim3(DC_THREADS);
+      config.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = static_cast<unsigned>(num_splits);
+      attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
+      config.attrs = attr;
+      config.numAttrs = 1;
+      int clusters = 0;
+      fits = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel, &config) == cudaSuccess && clusters > 0;
+    }
+    cudaGetLastError();                                  // a refusal above is an answer, not an error of the caller
+    known[num_splits] = fits ? 1 : -1;
+  }
+  return known[num_splits] > 0;
+}
+
 // `requests` (optional): the indices of the batch's decode requests; without
 // it requests 0 .. num_requests-1 are taken.  `scratch` holds
-// le_attention_decode_scratch_floats(...) floats.
+// le_attention_decode_scratch_floats(...) floats; it is used when the keys are
+// cut into more splits than a thread-block cluster merges by itself.
 LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratch, const void *q, int64_t q_stride,
                                     const void *k_cache, const void *v_cache, const int32_t *block_table, int max_blocks,
                                     const int32_t *cu_q, const int32_t *ctx_before, const int32_t *requests,
@@ -698,25 +787,35 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
   if (num_requests <= 0) return 0;
   if (num_kv_heads <= 0 || num_heads % num_kv_heads) return le::invalid("le_attention_decode_bf16: %d heads do not divide into %d groups", num_heads, num_kv_heads);
   if (num_splits < 1 || num_splits > MERGE_MAX_SPLITS) return le::invalid("le_attention_decode_bf16: %d splits (1..%d)", num_splits, MERGE_MAX_SPLITS);
-  if (num_splits > 1 && scratch == nullptr) return le::invalid("le_attention_decode_bf16: splitting the keys needs scratch memory");
-  if (reinterpret_cast<uintptr_t>(scratch) % 8) return le::invalid("le_attention_decode_bf16: the scratch memory must start on an 8-byte boundary");
   const int group = num_heads / num_kv_heads;
   const int row_tiles = (group + 15) / 16;
   if (num_kv_heads * row_tiles > 65535 || num_requests > 65535) return le::invalid("le_attention_decode_bf16: the batch is too large for one launch");
   size_t smem = static_cast<size_t>(DC_WARPS) * DC_WARP_SMEM * sizeof(bf16);
-  const size_t merge = static_cast<size_t>(DC_WARPS * 16 * HD + 2 * DC_WARPS * 16) * sizeof(float);
+  // the warps' partial results, and behind them the block's own for the merge across a cluster
+  const size_t merge = static_cast<size_t>(DC_WARPS * 16 * HD + 2 * DC_WARPS * 16 + 16 * HD + 32) * sizeof(float);
   if (merge > smem) smem = merge;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return le::invalid("le_attention_decode_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   }
+  dim3 grid(num_splits, num_kv_heads * row_tiles, num_requests);
+  if (cluster_splits_fit(num_splits, smem)) {
+    // the splits of a (request, kv head) as one cluster: merged through shared memory, no scratch, no second kernel
+    return le::launch_chained_cluster(attention_decode_kernel, grid, dim3(DC_THREADS), smem, stream, num_splits,
+                                      static_cast<bf16 *>(out), out_stride, static_cast<float *>(nullptr),
+                                      static_cast<float *>(nullptr), static_cast<const bf16 *>(q), q_stride,
+                                      static_cast<const bf16 *>(k_cache), static_cast<const bf16 *>(v_cache), block_table,
+                                      max_blocks, cu_q, ctx_before, requests, num_heads, num_kv_heads, page_size,
+                                      page_shift_of(page_size), num_pages, window, scale, num_splits, 1, status);
+  }
+  if (num_splits > 1 && scratch == nullptr) return le::invalid("le_attention_decode_bf16: splitting the keys %d ways needs scratch memory", num_splits);
+  if (reinterpret_cast<uintptr_t>(scratch) % 8) return le::invalid("le_attention_decode_bf16: the scratch memory must start on an 8-byte boundary");
   float *part_o = scratch;
   float *part_ml = scratch ? scratch + static_cast<int64_t>(num_requests) * num_heads * num_splits * HD : nullptr;
-  dim3 grid(num_splits, num_kv_heads * row_tiles, num_requests);
   int rc = le::launch_chained(attention_decode_kernel, grid, dim3(DC_THREADS), smem, stream, static_cast<bf16 *>(out), out_stride,
                               part_o, part_ml, static_cast<const bf16 *>(q), q_stride, static_cast<const bf16 *>(k_cache),
                               static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before, requests, num_heads,
-                              num_kv_heads, page_size, page_shift_of(page_size), num_pages, window, scale, num_splits, status);
+                              num_kv_heads, page_size, page_shift_of(page_size), num_pages, window, scale, num_splits, 0, status);
   if (rc != 0 || num_splits == 1) return rc;
   dim3 mgrid(num_heads, num_requests);
   return le::launch_chained(attention_merge_kernel, mgrid, dim3(HD < 32 ? 32 : (HD > 128 ? 128 : HD)),

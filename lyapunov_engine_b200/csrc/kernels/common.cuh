@@ -90,6 +90,50 @@ inline int launch_chained(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, 
   return launched();
 }
 
+// The same for a kernel whose blocks form thread-block clusters of `cluster_x`
+// blocks along x (they are scheduled together and can read one another's shared
+// memory); more than 8 to a cluster needs the kernel's non-portable attribute.
+template <typename... KernelArgs, typename... Args>
+inline int launch_chained_cluster(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  int cluster_x, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(cluster_x);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = chaining_enabled() ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+  if (e != cudaSuccess) {
+    snprintf(error_buffer(), 512, "CUDA: %s", cudaGetErrorString(e));
+    return static_cast<int>(e);
+  }
+  return launched();
+}
+
+// Every thread of every block of the cluster arrives; returns when all have.
+// What a block wrote to its shared memory before is visible to the others after.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// A float at the same shared-memory address in block `rank` of the cluster.
+__device__ __forceinline__ float cluster_peer_f32(const float *mine, unsigned rank) {
+  const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(mine));
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T x);
 template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }

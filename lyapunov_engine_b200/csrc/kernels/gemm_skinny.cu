@@ -73,7 +73,8 @@ struct RotaryArgs {
 template <int MT, bool GATED, typename TO, int BK, int STAGES, bool ROTARY>
 __global__ void __launch_bounds__(THREADS)
 gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 *__restrict__ w, int M, int N, int K,
-                   int64_t ldx, int64_t ldw, int64_t ldo, int k_per_split, int64_t split_stride, RotaryArgs rotary) {
+                   int64_t ldx, int64_t ldw, int64_t ldo, int k_per_split, int64_t split_stride, int early_successor,
+                   RotaryArgs rotary) {
   constexpr int WSETS = GATED ? 2 : 1;
   constexpr int CPR = BK / 8;                      // 16-byte chunks per row of a tile
   constexpr int W_STAGE = WSETS * BN * BK;         // elements
@@ -126,6 +127,12 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
     }
   };
 
+  // When all of this kernel's blocks run at once, the kernel after it may start its own preamble at once too
+  // (the next product its first weight tiles, the attention kernel after the rotary form the keys of earlier
+  // steps) in whatever room the multiprocessors have left or gain as blocks end; it waits for this kernel's
+  // results where it needs them.  A grid of several waves keeps the room for its own blocks and lets the
+  // successor start when its main loop is through.
+  if (early_successor) le::let_successor_start();
   // the first weight tiles do not depend on the kernel before this one
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
@@ -231,7 +238,7 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
   }
   cp_wait<0>();
   __syncthreads();
-  le::let_successor_start();   // only the reduction and the stores are left
+  if (!early_successor) le::let_successor_start();   // only the reduction and the stores are left
 
   // the four warps hold partial sums over their k-steps: add them in warp order
   float *red = reinterpret_cast<float *>(smem_raw);          // [WARPS][WSETS * MT * 4][32]
@@ -293,6 +300,17 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
   }
 }
 
+// Which forms let their successor start at once when their blocks all run at once: bit 0 the rotary form,
+// bit 1 the gated form, bit 2 split-K partial sums, bit 3 the plain form.  LYAPUNOV_EARLY_TRIGGER=<mask>;
+// 0: every form lets its successor start after its main loop.
+inline int early_trigger_mask() {
+  static const int mask = [] {
+    const char *env = getenv("LYAPUNOV_EARLY_TRIGGER");
+    return env == nullptr ? 3 : atoi(env);
+  }();
+  return mask;
+}
+
 template <int MT, bool GATED, typename TO, bool ROTARY = false>
 int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int splits,
            int64_t split_stride, cudaStream_t stream, const RotaryArgs &rotary = RotaryArgs{}) {
@@ -313,8 +331,20 @@ int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t
   int k_per_split = (K + splits - 1) / splits;
   k_per_split = (k_per_split + BK - 1) / BK * BK;
   dim3 grid((n_out + BN - 1) / BN, splits);
+  // how many blocks of this form the device holds at once (asked once)
+  static const int64_t resident = [&] {
+    int per_sm = 0, device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, smem) != cudaSuccess) {
+      cudaGetLastError();
+      return int64_t{0};
+    }
+    return static_cast<int64_t>(per_sm) * sms;
+  }();
+  const int form = ROTARY ? 1 : (GATED ? 2 : (splits > 1 ? 4 : 8));
+  const int early = (early_trigger_mask() & form) && static_cast<int64_t>(grid.x) * grid.y <= resident ? 1 : 0;
   return le::launch_chained(kernel, grid, dim3(THREADS), smem, stream, static_cast<TO *>(out), static_cast<const bf16 *>(x),
-                            static_cast<const bf16 *>(w), M, N, K, ldx, ldw, ldo, k_per_split, split_stride, rotary);
+                            static_cast<const bf16 *>(w), M, N, K, ldx, ldw, ldo, k_per_split, split_stride, early, rotary);
 }
 
 template <bool GATED, typename TO>

@@ -123,7 +123,9 @@ def test_tensor_core_kernels(case):
     status = ops.new_status(DEV)
     multi = [b for b, n in enumerate(q_lens) if n > 1]
     single = [b for b, n in enumerate(q_lens) if n == 1]
-    variants = [(1, ops.attention_prefill_bf16), (3, ops.attention_prefill_bf16), (16, ops.attention_prefill_bf16)]
+    # 3 and 16 splits are merged inside the decode kernel by a cluster of blocks, 24 through scratch memory
+    variants = [(1, ops.attention_prefill_bf16), (3, ops.attention_prefill_bf16), (16, ops.attention_prefill_bf16),
+                (24, ops.attention_prefill_bf16)]
     if ops.attention_tc_available(hd, page):
         variants.append((2, ops.attention_prefill_tc_bf16))      # the tcgen05 kernel for the requests with several tokens
     for splits, prefill in variants:
