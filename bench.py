@@ -351,16 +351,22 @@ def run_ours(args):
     # by itself.
     e2e_steps, e2e_warm = args.steps, args.warmup
     ahead_of_window = 8                      # steps in which requests get their first tokens one after the other
-    prompt_len = CONTEXT - (e2e_steps + e2e_warm) - ahead_of_window - 1   # the window ends at CONTEXT at the latest
+    # The prefill of 8 x 4,000 tokens draws the full 1 kW; for some 0.1 s afterwards the power cap holds the SM
+    # clock down (1,725 of 1,965 MHz sampled), which a decode step, bound by latencies, feels.  The window
+    # measures steady decoding, so untimed decode steps run first until that has passed.
+    settle = 200
+    prompt_len = CONTEXT - (e2e_steps + e2e_warm + settle) - ahead_of_window - 1   # the window ends at CONTEXT at the latest
     for i in range(batch):
-        sp = SamplingParams(temperature=0.0, max_tokens=e2e_steps + e2e_warm + ahead_of_window + 4 * (i + 1), ignore_eos=True)
+        sp = SamplingParams(temperature=0.0, max_tokens=e2e_steps + e2e_warm + settle + ahead_of_window + 4 * (i + 1),
+                            ignore_eos=True)
         engine.add_request(f"bench-{i}", torch.randint(0, vocab, (prompt_len,), generator=gen).tolist(), sp)
     engine.warm_up(contexts=[CONTEXT], batches=[1, 2, 4, batch])   # as a server does before its first request
     while any(seq.get_output_len() == 0 for seq, _, _ in engine.active_sequences.values()):
         engine.step()                               # prefill (portions under the token budget)
-    for _ in range(e2e_warm):
+    for _ in range(settle + e2e_warm):
         engine.step()
     torch.cuda.synchronize()
+    m2 = clocks.mark()
     d2h0 = engine.d2h_bytes
     t0 = time.perf_counter()
     produced = 0
@@ -371,6 +377,7 @@ def run_ours(args):
         slowest = max(slowest, time.perf_counter() - t1)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    m3 = clocks.mark()
     assert produced == batch * e2e_steps, (produced, batch, e2e_steps)
     d2h = (engine.d2h_bytes - d2h0) / e2e_steps
     live = [host.StepEntry(seq, seq.get_num_computed_tokens(), 1, [0]) for seq, _, _ in engine.active_sequences.values()]
@@ -386,7 +393,8 @@ def run_ours(args):
     drain_s = time.perf_counter() - t0
     e2e = {"value": round(produced / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_s * 1000 / e2e_steps, 4),
-           "slowest_step_ms": round(slowest * 1000, 3),
+           "slowest_step_ms": round(slowest * 1000, 3), "settle_steps": settle,
+           "sm_mhz": clocks.summary(m2, max(m3, m2 + 1)).get("sm_mhz"),
            "drain": {"steps": drain_steps, "tokens": drain_tokens, "ms_per_step": round(drain_s * 1000 / max(drain_steps, 1), 4)}}
     clocks.stop()
 

@@ -392,6 +392,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
 }
 
 // ---------------------------------------------------------------- decode
+constexpr int DC_MAX_CLUSTER = 16;                // the most splits a cluster of blocks merges by itself
 constexpr int DC_WARPS = 4;
 constexpr int DC_THREADS = DC_WARPS * 32;
 constexpr int DC_TILE = 32;                       // keys per warp and pipeline stage
@@ -623,18 +624,30 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
   }
   if (num_splits > 1 && cluster_merge) {
     le::cluster_sync();
-    // block `split` of the cluster takes every num_splits-th column
+    // block `split` of the cluster takes every num_splits-th column; everything a column needs of the other
+    // blocks is asked for before any of it is used (one trip through the cluster's network, not one per split)
     for (int i = tid * num_splits + split; i < heads_here * HD; i += DC_THREADS * num_splits) {
       const int row = i / HD, d = i % HD;
+      float ms[DC_MAX_CLUSTER], ls[DC_MAX_CLUSTER], os[DC_MAX_CLUSTER];
+#pragma unroll
+      for (int s2 = 0; s2 < DC_MAX_CLUSTER; ++s2) {
+        if (s2 < num_splits) {
+          ms[s2] = le::cluster_peer_f32(cl_m + row, s2);
+          ls[s2] = le::cluster_peer_f32(cl_l + row, s2);
+          os[s2] = le::cluster_peer_f32(cl_o + row * HD + d, s2);
+        } else {
+          ms[s2] = -INFINITY, ls[s2] = 0.0f, os[s2] = 0.0f;
+        }
+      }
       float m = -INFINITY;
-      for (int s2 = 0; s2 < num_splits; ++s2) m = fmaxf(m, le::cluster_peer_f32(cl_m + row, s2));
+#pragma unroll
+      for (int s2 = 0; s2 < DC_MAX_CLUSTER; ++s2) m = fmaxf(m, ms[s2]);
       float acc = 0.0f, l = 0.0f;
-      for (int s2 = 0; s2 < num_splits; ++s2) {
-        const float ms = le::cluster_peer_f32(cl_m + row, s2);
-        if (ms == -INFINITY) continue;                          // a split without keys
-        const float f = le::fast_exp2(ms - m);
-        acc += f * le::cluster_peer_f32(cl_o + row * HD + d, s2);
-        l += f * le::cluster_peer_f32(cl_l + row, s2);
+#pragma unroll
+      for (int s2 = 0; s2 < DC_MAX_CLUSTER; ++s2) {
+        const float f = ms[s2] == -INFINITY ? 0.0f : le::fast_exp2(ms[s2] - m);     // a split without keys counts nothing
+        acc += f * os[s2];
+        l += f * ls[s2];
       }
       out[tok * out_stride + (h0 + row) * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
     }
@@ -740,7 +753,7 @@ LE_API int64_t le_attention_decode_scratch_floats(int num_requests, int num_head
 // beyond it the partial results go through scratch memory to a merge kernel.  By default up to 8 (clusters of
 // 16 need the non-portable size and were slower than the merge kernel at batches of 1 and 2);
 // LYAPUNOV_CLUSTER_MERGE=<n> sets another limit up to 16, 0 switches it off.
-constexpr int DC_MAX_CLUSTER = 16;
+
 
 // Whether the device can hold a cluster of `num_splits` of the decode kernel's blocks (asked once per size).
 static bool cluster_splits_fit(int num_splits, size_t smem) {

@@ -311,40 +311,65 @@ inline int early_trigger_mask() {
   return mask;
 }
 
+// Blocks of one form of the kernel that the device holds at once (asked once per form).
+template <typename Kernel>
+int64_t resident_blocks(Kernel kernel, size_t smem) {
+  int per_sm = 0, device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, smem) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return static_cast<int64_t>(per_sm) * sms;
+}
+
+template <int MT, bool GATED, typename TO, bool ROTARY, int STAGES>
+struct Form {
+  static constexpr int WSETS = GATED ? 2 : 1;
+  static constexpr int BK = 128;
+  static size_t smem() {
+    const size_t pipeline = static_cast<size_t>(STAGES) * (WSETS * BN * BK + MT * 8 * BK) * sizeof(bf16);
+    const size_t reduce = static_cast<size_t>(WARPS) * WSETS * MT * 4 * 32 * sizeof(float);
+    return reduce > pipeline ? reduce : pipeline;
+  }
+  // 0 when the form cannot get its shared memory
+  static int64_t resident() {
+    static const int64_t n = [] {
+      auto kernel = gemm_skinny_kernel<MT, GATED, TO, BK, STAGES, ROTARY>;
+      if (smem() >= 48 * 1024 &&
+          cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem())) != cudaSuccess) {
+        cudaGetLastError();
+        return int64_t{0};
+      }
+      return resident_blocks(kernel, smem());
+    }();
+    return n;
+  }
+  static int go(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int splits,
+                int64_t split_stride, cudaStream_t stream, const RotaryArgs &rotary) {
+    if (resident() <= 0) return le::invalid("le_gemm_skinny: cannot get %zu bytes of shared memory", smem());
+    const int n_out = GATED ? N / 2 : N;
+    int k_per_split = (K + splits - 1) / splits;
+    k_per_split = (k_per_split + BK - 1) / BK * BK;
+    dim3 grid((n_out + BN - 1) / BN, splits);
+    const int form = ROTARY ? 1 : (GATED ? 2 : (splits > 1 ? 4 : 8));
+    const int early = (early_trigger_mask() & form) && static_cast<int64_t>(grid.x) * grid.y <= resident() ? 1 : 0;
+    return le::launch_chained(gemm_skinny_kernel<MT, GATED, TO, BK, STAGES, ROTARY>, grid, dim3(THREADS), smem(), stream,
+                              static_cast<TO *>(out), static_cast<const bf16 *>(x), static_cast<const bf16 *>(w), M, N, K, ldx, ldw,
+                              ldo, k_per_split, split_stride, early, rotary);
+  }
+};
+
 template <int MT, bool GATED, typename TO, bool ROTARY = false>
 int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int splits,
            int64_t split_stride, cudaStream_t stream, const RotaryArgs &rotary = RotaryArgs{}) {
-  constexpr int WSETS = GATED ? 2 : 1;
-  constexpr int BK = 128;
   // Few rows leave shared memory for a deeper pipeline: more bytes in flight per block (3 % of a decode step).
   // Not for the gated form: with two weight tiles per stage its 512 blocks no longer fit the GPU all at once.
   constexpr int STAGES = (MT <= 2 && !GATED) ? 8 : 4;
-  size_t smem = static_cast<size_t>(STAGES) * (WSETS * BN * BK + MT * 8 * BK) * sizeof(bf16);
-  const size_t reduce = static_cast<size_t>(WARPS) * WSETS * MT * 4 * 32 * sizeof(float);
-  if (reduce > smem) smem = reduce;
-  auto kernel = gemm_skinny_kernel<MT, GATED, TO, BK, STAGES, ROTARY>;
-  if (smem >= 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return le::invalid("le_gemm_skinny: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-  }
-  const int n_out = GATED ? N / 2 : N;
-  int k_per_split = (K + splits - 1) / splits;
-  k_per_split = (k_per_split + BK - 1) / BK * BK;
-  dim3 grid((n_out + BN - 1) / BN, splits);
-  // how many blocks of this form the device holds at once (asked once)
-  static const int64_t resident = [&] {
-    int per_sm = 0, device = 0, sms = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, smem) != cudaSuccess) {
-      cudaGetLastError();
-      return int64_t{0};
-    }
-    return static_cast<int64_t>(per_sm) * sms;
-  }();
-  const int form = ROTARY ? 1 : (GATED ? 2 : (splits > 1 ? 4 : 8));
-  const int early = (early_trigger_mask() & form) && static_cast<int64_t>(grid.x) * grid.y <= resident ? 1 : 0;
-  return le::launch_chained(kernel, grid, dim3(THREADS), smem, stream, static_cast<TO *>(out), static_cast<const bf16 *>(x),
-                            static_cast<const bf16 *>(w), M, N, K, ldx, ldw, ldo, k_per_split, split_stride, early, rotary);
+  // (17 stages for the rotary form, so that a block has asked for all of a K of 2048 before it waits for the norm
+  // before it, made the step slower, 0.809 -> 0.826 ms at batch 8: the blocks' 96 KB keep the attention kernel
+  // that follows from starting beside them and fetching its keys early.)
+  return Form<MT, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary);
 }
 
 template <bool GATED, typename TO>

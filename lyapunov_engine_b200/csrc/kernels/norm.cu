@@ -53,7 +53,9 @@ __device__ __forceinline__ void store_vec(T *p, const float (&src)[VEC]) {
 
 // PER_THREAD > 0: the row fits in PER_THREAD vectors of VEC values per thread, which stay in registers
 // between the sum of squares and the scaling (one pass over memory).  0: any width, two passes.
-template <typename TO, typename TD, int VEC, int PER_THREAD>
+// PARTIALS > 0: `num_partials` is this number, known when compiling, so that every load of a thread is asked
+// for before the first is used (a decode step's norm is one round trip to memory, not one per partial sum).
+template <typename TO, typename TD, int VEC, int PER_THREAD, int PARTIALS>
 __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, const TD *__restrict__ delta,
                                int num_partials, int64_t partial_stride, const float *__restrict__ weight,
                                const int32_t *__restrict__ rows, float eps, int hidden) {
@@ -66,6 +68,49 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
   TO *o = out + static_cast<int64_t>(blockIdx.x) * hidden;
   const bool write_back = (d != nullptr) && (rows == nullptr);
 
+  if constexpr (PER_THREAD > 0 && PARTIALS > 0) {
+    float val[PER_THREAD][VEC], add[PER_THREAD][PARTIALS][VEC], w[PER_THREAD][VEC];
+#pragma unroll
+    for (int it = 0; it < PER_THREAD; ++it) {
+      const int i = (it * blockDim.x + threadIdx.x) * VEC;
+      if (i < hidden) {
+        load_vec<float, VEC>(val[it], x + i);
+        if (d) {
+#pragma unroll
+          for (int p = 0; p < PARTIALS; ++p) load_vec<TD, VEC>(add[it][p], d + p * partial_stride + i);
+        }
+        load_vec<float, VEC>(w[it], weight + i);
+      }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int it = 0; it < PER_THREAD; ++it) {
+      const int i = (it * blockDim.x + threadIdx.x) * VEC;
+      if (i < hidden) {
+        if (d) {
+#pragma unroll
+          for (int p = 0; p < PARTIALS; ++p)       // in the partial sums' order, as the general form adds them
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) val[it][v] += add[it][p][v];
+        }
+        if (write_back) store_vec<float, VEC>(x + i, val[it]);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) ss += val[it][v] * val[it][v];
+      }
+    }
+    ss = le::block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / static_cast<float>(hidden) + eps);
+#pragma unroll
+    for (int it = 0; it < PER_THREAD; ++it) {
+      const int i = (it * blockDim.x + threadIdx.x) * VEC;
+      if (i < hidden) {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) w[it][v] = val[it][v] * inv * w[it][v];
+        store_vec<TO, VEC>(o + i, w[it]);
+      }
+    }
+    return;
+  }
   if constexpr (PER_THREAD > 0) {
     float val[PER_THREAD][VEC];
     float ss = 0.0f;
@@ -131,10 +176,19 @@ int launch(void *out, float *resid, const void *delta, int num_partials, int64_t
            const int32_t *rows, float eps, int num_rows, int hidden, cudaStream_t stream) {
   int threads = 32;
   while (threads < 512 && threads * 8 < hidden) threads *= 2;
-#define LE_NORM(VEC, PER)                                                                                               \
-  return le::launch_chained(rmsnorm_kernel<TO, TD, VEC, PER>, dim3(num_rows), dim3(threads), 0, stream,                \
+#define LE_NORM_P(VEC, PER, PARTIALS)                                                                                  \
+  return le::launch_chained(rmsnorm_kernel<TO, TD, VEC, PER, PARTIALS>, dim3(num_rows), dim3(threads), 0, stream,      \
                             static_cast<TO *>(out), resid, static_cast<const TD *>(delta), num_partials, partial_stride, \
                             weight, rows, eps, hidden)
+#define LE_NORM(VEC, PER)                                                                                               \
+  do {                                                                                                                  \
+    if (PER > 0 && PER <= 2) {                                                                                          \
+      if (delta == nullptr || num_partials == 1) LE_NORM_P(VEC, PER, 1);                                                \
+      if (num_partials == 2) LE_NORM_P(VEC, PER, 2);                                                                    \
+      if (num_partials == 4) LE_NORM_P(VEC, PER, 4);                                                                    \
+    }                                                                                                                   \
+    LE_NORM_P(VEC, PER, 0);                                                                                             \
+  } while (0)
   const bool aligned = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(resid) | reinterpret_cast<uintptr_t>(delta) |
                          reinterpret_cast<uintptr_t>(weight)) & 15) == 0 && partial_stride % 4 == 0;
   if (hidden % 4 == 0 && aligned) {
@@ -145,6 +199,7 @@ int launch(void *out, float *resid, const void *delta, int num_partials, int64_t
   }
   LE_NORM(1, 0);
 #undef LE_NORM
+#undef LE_NORM_P
 }
 
 }  // namespace
