@@ -343,7 +343,13 @@ class LLMEngine:
 
     def stats(self) -> dict:
         s = self.scheduler.get_stats()
-        return {"steps": s.steps, "prefill_tokens": s.prefill_tokens, "decode_tokens": s.decode_tokens,
+        timed = {}
+        if self.runner._timers:
+            by_kind: dict = {}
+            for t in self.runner.step_timings():
+                by_kind.setdefault(t["kind"], []).append(t["ms"])
+            timed = {"step_ms": {k: {"steps": len(v), "mean": sum(v) / len(v), "max": max(v)} for k, v in by_kind.items()}}
+        return {**timed, "steps": s.steps, "prefill_tokens": s.prefill_tokens, "decode_tokens": s.decode_tokens,
                 "preemptions": s.preemptions, "failed": s.failed, "graph_steps": self.runner.num_graph_steps,
                 "graphs": len(self.runner._graphs) + len(self.runner._prompt_graphs),
                 "graph_bytes": self.runner.graph_bytes(), "steps_ahead": self.num_steps_ahead,

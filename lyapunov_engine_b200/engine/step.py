@@ -20,6 +20,7 @@ runs whole prompts one by one or one token per request, never a mix.
 """
 from __future__ import annotations
 
+import collections
 import gc
 import os
 
@@ -84,6 +85,8 @@ class ModelRunner:
         self.num_steps = 0
         self.num_graph_steps = 0
         self.num_captures = 0
+        # LYAPUNOV_STEP_TIMERS=1: every step is bracketed by two CUDA events on its stream (see step_timings())
+        self._timers = collections.deque(maxlen=4096) if os.environ.get("LYAPUNOV_STEP_TIMERS", "0") not in ("0", "") else None
         # room for the rows and requests that padding to a fixed shape adds to a step within the caller's limits
         self._most_rows = max_num_batched_tokens + 128 + max_num_seqs
         self._most_requests = max_num_seqs + 1
@@ -192,6 +195,10 @@ class ModelRunner:
         if len(entries) > self.max_num_seqs:
             raise ValueError(f"the step brings {len(entries)} requests, max_num_seqs is {self.max_num_seqs}")
         decode_only = all(e.count == 1 for e in entries)
+        timer = None
+        if self._timers is not None:
+            timer = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            timer[0].record()
         plan = None
         if self.use_cuda_graphs and not decode_only and PROMPT_GRAPHS and device_tokens is None:
             plan = self._prompt_graph_plan(entries, total)
@@ -201,9 +208,27 @@ class ModelRunner:
             logits = self._prompt_graph_step(entries, *plan)
         else:
             logits = self._eager_step(entries, device_tokens)
+        if timer is not None:
+            timer[1].record()
+            kind = "decode" if decode_only else ("prompt graph" if plan is not None else "prompt")
+            self._timers.append((kind, total, len(entries), *timer))
         if self.check_status:
             ops.check_status(self.runtime.status)
         return logits
+
+    def enable_step_timers(self, on: bool = True) -> None:
+        """Brackets every step with two CUDA events (what LYAPUNOV_STEP_TIMERS=1 does from the start)."""
+        self._timers = collections.deque(maxlen=4096) if on else None
+
+    def step_timings(self) -> list[dict]:
+        """Device time of the last steps (up to 4,096), oldest first: kind of
+        step, tokens, requests, milliseconds between the events recorded
+        before and after its launches.  Waits for the last step to finish."""
+        if not self._timers:
+            return []
+        self._timers[-1][4].synchronize()
+        return [{"kind": kind, "tokens": tokens, "requests": requests, "ms": begin.elapsed_time(end)}
+                for kind, tokens, requests, begin, end in self._timers]
 
     def _eager_step(self, entries, device_tokens=None):
         layout = self._pack(entries, device_tokens=device_tokens)

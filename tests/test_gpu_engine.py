@@ -250,6 +250,62 @@ def test_command_line(folders):
     assert [int(t) for t in last.split()] == plain_llama.plain_greedy_generate(cfg, w, prompt, 6)
 
 
+def test_command_line_with_random_weights(folders, tmp_path):
+    """generate --random-weights: --model names a config.json (or a folder that
+    holds one); the weights are those that load_model draws from the seed."""
+    import json
+    cfg, _, _, _ = folders["b"]
+    path = str(tmp_path / "config.json")
+    with open(path, "w", encoding="utf-8") as f:
+        json.dump(cfg, f)
+    prompt = fixtures.random_ids(cfg, 7, 5)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "lyapunov"), "generate", "--model", path, "--random-weights", "--seed", "3",
+           "--prompt-ids", " ".join(map(str, prompt)), "--max-tokens", "5", "--temperature", "0", "--dtype", "float32",
+           "--block-size", "8", "--num-blocks", "16", "--max-num-seqs", "2", "--max-batched-tokens", "64", "--ignore-eos"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    got = [int(t) for t in out.stdout.strip().split("\n")[-1].split()]
+    loaded = load_model(config=cfg, random_seed=3, dtype="float32", device="cuda:0")
+    engine = LLMEngine(loaded, EngineConfig(num_blocks=16, block_size=8, max_num_seqs=2, max_num_batched_tokens=64,
+                                            dtype="float32", device="cuda:0"))
+    want = engine.generate([prompt], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))[0].output_tokens
+    assert got == want and len(got) == 5
+
+
+def test_step_timers(folders):
+    """With step timers on, every step's device time is recorded by kind."""
+    cfg, _, d32, _ = folders["a"]
+    engine = LLMEngine.from_pretrained(d32, dtype="float32", num_blocks=64, block_size=4, max_num_seqs=4,
+                                       max_num_batched_tokens=20)
+    engine.runner.enable_step_timers()
+    engine.generate([fixtures.random_ids(cfg, n, n) for n in (30, 7)], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    timings = engine.runner.step_timings()
+    assert len(timings) == engine.runner.num_steps and all(t["ms"] > 0 for t in timings)
+    assert {t["kind"] for t in timings} >= {"decode", "prompt"} and sum(t["tokens"] for t in timings) >= 37 + 2 * 5
+    summary = engine.stats()["step_ms"]
+    assert summary["decode"]["steps"] > 0 and summary["decode"]["mean"] <= summary["decode"]["max"]
+
+
+def test_warm_up_captures_the_decode_graphs_ahead(folders):
+    """After warm_up() a decode step of any batch and context it covered replays
+    a captured graph at its first use."""
+    cfg, w, d32, _ = folders["a"]
+    engine = LLMEngine.from_pretrained(d32, dtype="float32", num_blocks=64, block_size=4, max_num_seqs=4,
+                                       max_num_batched_tokens=32, max_model_len=128)
+    captured = engine.warm_up()
+    runner = engine.runner
+    assert captured == len(runner._graphs) > 0 and all(g.graph is not None for g in runner._graphs.values())
+    assert engine.block_manager.audit() == "" and engine.block_manager.get_num_free_blocks() == 64
+    before = runner.num_captures
+    prompts = [fixtures.random_ids(cfg, n, 50 + n) for n in (5, 17, 33)]
+    outs = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.output_tokens == plain_llama.plain_greedy_generate(cfg, w, p, 10)
+    decode_captures = sum(g.graph is not None for g in runner._graphs.values())
+    assert decode_captures == captured, "a decode step needed a graph that warm_up had not captured"
+    assert runner.num_captures - before == sum(g.graph is not None for g in runner._prompt_graphs.values())
+
+
 def test_no_cpu_path():
     from lyapunov_engine_b200 import ops
     with pytest.raises(ops.KernelError, match="CUDA"):
