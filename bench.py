@@ -127,28 +127,23 @@ def prefill_flops(cfg, tokens):
     return linear + attention
 
 
-def run_ours(args):
-    global BLOCK_SIZE, CONTEXT
+def make_rig(cfg, context, max_batch, page):
+    """A model of the given shapes with random weights, an engine around it with
+    room for `max_batch` requests of `context` tokens, and the three timed
+    loops (decode steps, prompts, decode steps beside a prompt portion)."""
+    import gc
+    import types
+
     import torch
-    BLOCK_SIZE = args.page
-    if args.only and args.context:
-        CONTEXT = args.context
 
     from lyapunov_engine_b200 import EngineConfig, LLMEngine, SamplingParams, build, load_model, ops
 
-    cfg = dict(SHAPES[args.shapes if args.only else "1b"])
-    layers_full = cfg["num_hidden_layers"]
-    if args.layers:
-        cfg["num_hidden_layers"] = args.layers
-    pk = peaks()
-    torch.cuda.set_device(0)
     host = build.load_host()
-    max_batch = 64 + (args.only == "mixed")   # the prompt beside 64 decoding requests holds a state slot too
-    num_blocks = (max_batch * (CONTEXT + 64) + 2 * PREFILL_TOKENS + CONTEXT) // BLOCK_SIZE
-    loaded = load_model(config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", max_model_len=CONTEXT + 64)
-    engine = LLMEngine(loaded, EngineConfig(num_blocks=num_blocks, block_size=BLOCK_SIZE, max_num_seqs=max_batch,
+    num_blocks = (max_batch * (context + 64) + 2 * PREFILL_TOKENS + context) // page
+    loaded = load_model(config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", max_model_len=context + 64)
+    engine = LLMEngine(loaded, EngineConfig(num_blocks=num_blocks, block_size=page, max_num_seqs=max_batch,
                                             max_num_batched_tokens=8192, dtype="bfloat16", device="cuda:0",
-                                            max_model_len=CONTEXT + 64))
+                                            max_model_len=context + 64))
     runner, manager, sampler = engine.runner, engine.block_manager, engine.sampler
     gen = torch.Generator().manual_seed(0)
     vocab = cfg["vocab_size"]
@@ -159,7 +154,6 @@ def run_ours(args):
             s.k.normal_(0, 1)
             s.v.normal_(0, 1)
     greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
-
     def timed_decode(batch, steps, warmup, context_end):
         """K decode steps of `batch` requests whose last step runs at
         `context_end` tokens: step function + sampler, timed on the device."""
@@ -276,6 +270,99 @@ def run_ours(args):
             manager.free(state["prompt"])
         return ms, state["keys"] / steps
 
+    def close():
+        """Gives the device memory back (the next rig may need all of it)."""
+        nonlocal engine, loaded, runner, manager, sampler
+        engine = loaded = runner = manager = sampler = None
+        rig.engine = rig.runner = rig.manager = rig.sampler = None
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    rig = types.SimpleNamespace(engine=engine, runner=runner, manager=manager, sampler=sampler, host=host, gen=gen, vocab=vocab,
+                                timed_decode=timed_decode, timed_prefill=timed_prefill, timed_mixed=timed_mixed, close=close)
+    return rig
+
+
+def leave_out(what, cfg):
+    """Replaces one kind of kernel of a decode step by nothing, so that the step
+    can be timed without it: the difference to the whole step is what the
+    kernel costs inside the chain (the rest computes on stale buffers, which
+    changes no launch and no byte moved)."""
+    from lyapunov_engine_b200 import ops
+
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    product = ops.gemm_skinny
+
+    def products_but(skip):
+        def run(out, a, w, splits=1, gated=False):
+            if not skip(w, gated):
+                product(out, a, w, splits=splits, gated=gated)
+        return run
+    if what == "norms":
+        ops.rmsnorm = lambda *a, **k: None
+    elif what == "qkv":
+        ops.gemm_skinny_rotary = lambda *a, **k: None
+    elif what == "attention":
+        ops.attention_decode_bf16 = lambda *a, **k: None
+    elif what == "o":
+        ops.gemm_skinny = products_but(lambda w, gated: not gated and tuple(w.shape) == (H, cfg["num_attention_heads"] * cfg["head_dim"]) and w.shape[0] < V)
+    elif what == "gate_up":
+        ops.gemm_skinny = products_but(lambda w, gated: gated)
+    elif what == "down":
+        ops.gemm_skinny = products_but(lambda w, gated: not gated and tuple(w.shape) == (H, I))
+    elif what == "head":
+        ops.gemm_skinny = products_but(lambda w, gated: w.shape[0] == V)
+
+
+def further_points(pk, page, context=8192, steps=24, warmup=6):
+    """Decode at batch 1, 8 and 64 and prefill of 2,048 and 8,192 tokens at the
+    3B and 8B shapes (context 8192), and the 8B mixed step (64 decoding requests
+    beside a 2,048-token portion): tokens a second, with the fraction of the
+    HBM or bfloat16 peak each reaches."""
+    out = {}
+    for name in ("3b", "8b"):
+        cfg = dict(SHAPES[name])
+        rig = make_rig(cfg, context, 65, page)
+        for b in (1, 8, 64):
+            rig.timed_decode(b, 3, 2, context - 200)          # (captures the graph)
+            ms, _, _ = rig.timed_decode(b, steps, warmup, context)
+            out[f"{name}_decode_b{b}"] = round(b * 1000.0 / ms, 1)
+            out[f"{name}_decode_b{b}_hbm_frac"] = round(decode_bytes(cfg, b, context - (steps - 1) // 2) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        for tokens in (2048, 8192):
+            ms = rig.timed_prefill(tokens, 3, 2)
+            out[f"{name}_prefill_{tokens}"] = round(tokens * 1000.0 / ms, 1)
+            out[f"{name}_prefill_{tokens}_frac"] = round(prefill_flops(cfg, tokens) / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
+        if name == "8b":
+            ms, _ = rig.timed_mixed(64, 8, 3, context, 2048)
+            out["8b_mixed_64_2048"] = round((64 + 2048) * 1000.0 / ms, 1)
+            out["8b_mixed_64_2048_ms"] = round(ms, 3)
+        rig.close()
+        del rig
+    return out
+
+
+def run_ours(args):
+    global BLOCK_SIZE, CONTEXT
+    import torch
+    BLOCK_SIZE = args.page
+    if args.only and args.context:
+        CONTEXT = args.context
+
+    from lyapunov_engine_b200 import SamplingParams, ops
+
+    cfg = dict(SHAPES[args.shapes if args.only else "1b"])
+    layers_full = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    pk = peaks()
+    torch.cuda.set_device(0)
+    max_batch = 64 + (args.only == "mixed")   # the prompt beside 64 decoding requests holds a state slot too
+    rig = make_rig(cfg, CONTEXT, max_batch, BLOCK_SIZE)
+    engine, runner, manager, sampler, host, gen, vocab = rig.engine, rig.runner, rig.manager, rig.sampler, rig.host, rig.gen, rig.vocab
+    timed_decode, timed_prefill, timed_mixed = rig.timed_decode, rig.timed_prefill, rig.timed_mixed
+
+    if args.only and args.without:
+        leave_out(args.without, cfg)
     if args.only:
         # A short run of one kind of step, for profilers: no CUDA graph, so
         # that every kernel shows as its own launch.
@@ -360,7 +447,7 @@ def run_ours(args):
         sp = SamplingParams(temperature=0.0, max_tokens=e2e_steps + e2e_warm + settle + ahead_of_window + 4 * (i + 1),
                             ignore_eos=True)
         engine.add_request(f"bench-{i}", torch.randint(0, vocab, (prompt_len,), generator=gen).tolist(), sp)
-    engine.warm_up(contexts=[CONTEXT], batches=[1, 2, 4, batch])   # as a server does before its first request
+    engine.warm_up(contexts=[CONTEXT, CONTEXT + 64], batches=[1, 2, 4, batch])   # as a server does before its first request
     while any(seq.get_output_len() == 0 for seq, _, _ in engine.active_sequences.values()):
         engine.step()                               # prefill (portions under the token budget)
     for _ in range(settle + e2e_warm):
@@ -397,6 +484,12 @@ def run_ours(args):
            "sm_mhz": clocks.summary(m2, max(m3, m2 + 1)).get("sm_mhz"),
            "drain": {"steps": drain_steps, "tokens": drain_tokens, "ms_per_step": round(drain_s * 1000 / max(drain_steps, 1), 4)}}
     clocks.stop()
+
+    # ---- further sizes: the same steps at the layer sizes of Llama-3.2-3B and Llama-3.1-8B, context 8192
+    if args.points == "all":
+        rig.close()
+        del rig, engine, runner, manager, sampler
+        points.update(further_points(pk, BLOCK_SIZE))
 
     # the timed steps run at contexts CONTEXT - steps + 1 .. CONTEXT: count the bytes of their mean
     mean_context = CONTEXT - (args.steps - 1) // 2
@@ -548,6 +641,10 @@ def main():
     p.add_argument("--tokens", type=int, default=0, help="with --only prefill or mixed: tokens of the prompt or of its portion (at most the context and 8192)")
     p.add_argument("--context", type=int, default=0, help="with --only decode: the context the last step ends at")
     p.add_argument("--no-cuda-graphs", action="store_true", help="with --only decode: launch every kernel by itself")
+    p.add_argument("--without", choices=["norms", "qkv", "attention", "o", "gate_up", "down", "head"], default=None,
+                   help="with --only decode (batches up to 16): time the step with this kind of kernel left out")
+    p.add_argument("--points", choices=["all", "1b"], default="all",
+                   help="all: also decode, prefill and the mixed step at the 3B and 8B shapes (context 8192) in `points`")
     args = p.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
