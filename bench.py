@@ -356,7 +356,8 @@ def run_ours(args):
         cfg["num_hidden_layers"] = args.layers
     pk = peaks()
     torch.cuda.set_device(0)
-    max_batch = 64 + (args.only == "mixed")   # the prompt beside 64 decoding requests holds a state slot too
+    # room for the batches the run times (the prompt beside the decoding requests of a mixed step holds a slot too)
+    max_batch = (max(args.batch, 1) + (args.only == "mixed")) if args.only else 64
     rig = make_rig(cfg, CONTEXT, max_batch, BLOCK_SIZE)
     engine, runner, manager, sampler, host, gen, vocab = rig.engine, rig.runner, rig.manager, rig.sampler, rig.host, rig.gen, rig.vocab
     timed_decode, timed_prefill, timed_mixed = rig.timed_decode, rig.timed_prefill, rig.timed_mixed

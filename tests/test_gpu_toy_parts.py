@@ -31,6 +31,9 @@ class ToyDecayMixer(Mixer):
     def state_need(self):
         return StateNeed((self.hidden_size,), torch.float32)
 
+    def tile_sizes(self):
+        return [8]       # a tile size no kernel of the package uses: the step's integers list it because this mixer asks
+
     def tensors(self):
         return [TensorDecl(n, (self.hidden_size, self.hidden_size)) for n in self.names]
 
@@ -40,6 +43,10 @@ class ToyDecayMixer(Mixer):
 
     def forward(self, x, ctx, cache):
         cu, slots = ctx.cu_q.tolist(), ctx.state_slots.tolist()
+        tile_request, tile_q0, num_tiles, _ = ctx.tiles[8]
+        assert num_tiles == sum((cu[b + 1] - cu[b] + 7) // 8 for b in range(ctx.num_requests))
+        assert sorted(zip(tile_request.tolist(), tile_q0.tolist())) == \
+            sorted((b, q0) for b in range(ctx.num_requests) for q0 in range(0, cu[b + 1] - cu[b], 8))
         u = (x.float() @ self.w_in.float().t())
         y = torch.empty_like(u)
         for b in range(ctx.num_requests):
@@ -142,6 +149,7 @@ def toy(tmp_path_factory):
     # what the cache must hold follows from the description alone
     assert [(g.window, g.num_kv_heads) for g in model.groups] == [(None, NKV), (WINDOW, NKV)]
     assert model.streams_per_group == [2, 1] and len(model.states) == 1
+    assert model.tile_sizes == [8, 16, 128]     # the toy mixer's and the attention kernels'
     assert [(r.group, r.stream, r.writes, r.state) for r in model.runs] == \
         [(0, 0, True, None), (None, None, True, 0), (1, 0, True, None), (0, 1, True, None), (0, 0, False, None)]
     _, w = plain_llama.read_model_folder(folder)
