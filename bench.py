@@ -319,9 +319,20 @@ def further_points(pk, page, context=8192, steps=24, warmup=6):
     3B and 8B shapes (context 8192), and the 8B mixed step (64 decoding requests
     beside a 2,048-token portion): tokens a second, with the fraction of the
     HBM or bfloat16 peak each reaches."""
+    import torch
+
     out = {}
     for name in ("3b", "8b"):
         cfg = dict(SHAPES[name])
+        # weights, the cache of 65 requests of `context` tokens, activations: leave the size out if it does not fit
+        H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+        nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+        weights = 2 * (L * ((nh + 2 * nkv) * hd * H + H * nh * hd + 3 * I * H) + (1 if cfg["tie_word_embeddings"] else 2) * cfg["vocab_size"] * H)
+        cache = 2 * 2 * nkv * hd * L * (65 * (context + 64) + 2 * PREFILL_TOKENS + context)
+        free, _ = torch.cuda.mem_get_info()
+        if weights + cache + (6 << 30) > free:
+            out[f"{name}_skipped"] = f"needs {(weights + cache) >> 30} GiB of device memory, {free >> 30} GiB are free"
+            continue
         rig = make_rig(cfg, context, 65, page)
         for b in (1, 8, 64):
             rig.timed_decode(b, 3, 2, context - 200)          # (captures the graph)
@@ -490,7 +501,10 @@ def run_ours(args):
     if args.points == "all":
         rig.close()
         del rig, engine, runner, manager, sampler
-        points.update(further_points(pk, BLOCK_SIZE))
+        try:
+            points.update(further_points(pk, BLOCK_SIZE))
+        except Exception as e:       # the headline does not depend on the further sizes (they need 90 GB of device memory)
+            points["further_sizes_failed"] = f"{type(e).__name__}: {str(e)[:160]}"
 
     # the timed steps run at contexts CONTEXT - steps + 1 .. CONTEXT: count the bytes of their mean
     mean_context = CONTEXT - (args.steps - 1) // 2
