@@ -80,6 +80,7 @@ class RequestOutput:
         self.is_finished = finished
         self.finish_reason = finish_reason   # "stop", "length", "abort" or "error"
         self.error = error
+        self.text = None                     # the output decoded, when the prompts were given as text
 
     def __repr__(self):
         return (f"RequestOutput(request_id={self.request_id!r}, output_tokens={self.output_tokens!r}, "
@@ -89,9 +90,10 @@ class RequestOutput:
 class LoadedModel:
     """A model with its weights on the device."""
 
-    def __init__(self, spec, model, runtime):
+    def __init__(self, spec, model, runtime, folder=None):
         self.spec, self.model, self.runtime = spec, model, runtime
         self.config = spec
+        self.folder = folder          # where the weights (and a tokenizer, if any) came from
 
 
 def load_model(folder: str | None = None, dtype=torch.bfloat16, device: str = "cuda:0", config: dict | None = None,
@@ -114,7 +116,7 @@ def load_model(folder: str | None = None, dtype=torch.bfloat16, device: str = "c
             source = FolderWeights(folder, decls, dtype, runtime.device)
         model.bind(source.get, runtime)
         source.release()
-    return LoadedModel(spec, model, runtime)
+    return LoadedModel(spec, model, runtime, folder)
 
 
 class LLMEngine:
@@ -324,11 +326,19 @@ class LLMEngine:
 
     # ---- convenience
     def generate(self, prompts, sampling_params=None) -> list[RequestOutput]:
-        """Runs every prompt (lists of token ids) to its end and returns the
-        outputs in the order of the prompts.  ``sampling_params``: one for all,
-        or one per prompt."""
-        if prompts and isinstance(prompts[0], int):
+        """Runs every prompt to its end and returns the outputs in the order of
+        the prompts.  Prompts are lists of token ids, or strings: those are
+        encoded with the tokenizer of the model's folder (the one
+        ``transformers.AutoTokenizer`` finds there, as the reference's command
+        line does, python/lyapunov_engine/entrypoints/cli.py:28-31) and the
+        outputs carry ``text``.  ``sampling_params``: one for all, or one per
+        prompt."""
+        if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
             prompts = [prompts]
+        as_text = bool(prompts) and isinstance(prompts[0], str)
+        if as_text:
+            tokenizer = self.tokenizer()
+            prompts = [tokenizer.encode(p) for p in prompts]
         if sampling_params is None or isinstance(sampling_params, SamplingParams):
             sampling_params = [sampling_params or SamplingParams()] * len(prompts)
         order = []
@@ -339,7 +349,25 @@ class LLMEngine:
             for o in self.step():
                 if o.finished and o.request_id in order:
                     done[o.request_id] = o
+        if as_text:
+            for o in done.values():
+                o.text = tokenizer.decode(o.output_tokens, skip_special_tokens=True)
         return [done[r] for r in order]
+
+    def tokenizer(self):
+        """The tokenizer of the model's folder (loaded at first use)."""
+        if getattr(self, "_tokenizer", None) is None:
+            if not self.loaded.folder:
+                raise ValueError("text prompts need a tokenizer: this model was not loaded from a folder; give token ids")
+            try:
+                from transformers import AutoTokenizer
+            except ImportError as e:
+                raise ValueError("text prompts need the transformers package for its tokenizers; give token ids") from e
+            try:
+                self._tokenizer = AutoTokenizer.from_pretrained(self.loaded.folder)
+            except Exception as e:
+                raise ValueError(f"no tokenizer could be loaded from {self.loaded.folder}: {e}; give token ids") from e
+        return self._tokenizer
 
     def stats(self) -> dict:
         s = self.scheduler.get_stats()

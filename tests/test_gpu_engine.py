@@ -250,6 +250,49 @@ def test_command_line(folders):
     assert [int(t) for t in last.split()] == plain_llama.plain_greedy_generate(cfg, w, prompt, 6)
 
 
+def test_text_prompts_through_the_folders_tokenizer(folders, tmp_path):
+    """generate() with strings: encoded by the tokenizer found in the model's
+    folder (a word-level one, made here), outputs decoded into ``text``; the
+    command line's --prompt goes the same way."""
+    import json
+    import shutil
+    tokenizers = pytest.importorskip("tokenizers")
+    pytest.importorskip("transformers")
+    cfg, w, d32, _ = folders["a"]
+    folder = str(tmp_path / "with_tokenizer")
+    shutil.copytree(d32, folder)
+    vocab = {f"w{i}": i for i in range(cfg["vocab_size"] - 1)}
+    vocab["[UNK]"] = cfg["vocab_size"] - 1
+    tok = tokenizers.Tokenizer(tokenizers.models.WordLevel(vocab, unk_token="[UNK]"))
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.Whitespace()
+    tok.save(os.path.join(folder, "tokenizer.json"))
+    with open(os.path.join(folder, "tokenizer_config.json"), "w", encoding="utf-8") as f:
+        json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "unk_token": "[UNK]"}, f)
+    ids = fixtures.random_ids(cfg, 11, 8)
+    text = " ".join(f"w{i}" for i in ids)
+    engine = LLMEngine.from_pretrained(folder, dtype="float32", num_blocks=32, block_size=4, max_num_seqs=2,
+                                       max_num_batched_tokens=64)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    by_text = engine.generate([text], sp)[0]
+    want = plain_llama.plain_greedy_generate(cfg, w, ids, 6)
+    assert by_text.prompt_tokens == ids and by_text.output_tokens == want
+    # (the unknown-word token is a special token, which decoding leaves out)
+    assert by_text.text == " ".join(f"w{i}" for i in want if i < cfg["vocab_size"] - 1)
+    assert engine.generate([ids], sp)[0].text is None
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "lyapunov"), "generate", "--model", folder, "--prompt", text,
+           "--max-tokens", "6", "--temperature", "0", "--dtype", "float32", "--block-size", "4", "--num-blocks", "32",
+           "--max-num-seqs", "2", "--max-batched-tokens", "64", "--ignore-eos"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert out.stdout.strip().split("\n")[-1] == by_text.text
+    # a model without a folder has no tokenizer to offer
+    loaded = load_model(config=cfg, random_seed=1, dtype="float32", device="cuda:0")
+    bare = LLMEngine(loaded, EngineConfig(num_blocks=16, block_size=4, max_num_seqs=2, max_num_batched_tokens=32,
+                                          dtype="float32", device="cuda:0"))
+    with pytest.raises(ValueError, match="tokenizer"):
+        bare.generate(["w1 w2"], sp)
+
+
 def test_command_line_with_random_weights(folders, tmp_path):
     """generate --random-weights: --model names a config.json (or a folder that
     holds one); the weights are those that load_model draws from the seed."""
