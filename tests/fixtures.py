@@ -108,6 +108,33 @@ TINY_C = {
 TINY_C_PAGE = 16
 
 
+# A fourth shape: a head size that is no power of two (48), six heads in three groups, a width and a feed-forward
+# that are multiples of 8 only, an odd vocabulary.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "vocab_size": 777,
+    "hidden_size": 200,
+    "intermediate_size": 296,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 6,
+    "num_key_value_heads": 3,
+    "head_dim": 48,
+    "max_position_embeddings": 512,
+    "rms_norm_eps": 1e-5,
+    "rope_theta": 10000.0,
+    "rope_scaling": None,
+    "tie_word_embeddings": False,
+    "hidden_act": "silu",
+    "attention_bias": False,
+    "mlp_bias": False,
+    "bos_token_id": 0,
+    "eos_token_id": 1,
+    "torch_dtype": "float32",
+}
+TINY_D_PAGE = 8
+
+
 def head_dim(cfg):
     return int(cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"])
 

@@ -21,11 +21,12 @@ MODELS = {
     # the stated tiny-B: N(0, 0.02) matrices, norm weights 1 + N(0, 0.1), seed 1, prompts of 1/8/40/97 tokens and
     # 24 decoded tokens each, portions of at most 16 beside decoded tokens, pages of 8
     "tiny_b_stated": (fixtures.TINY_B_STATED, fixtures.TINY_B_PAGE, 1, 0.02, 0.1, 1.0),
+    "tiny_d": (fixtures.TINY_D, fixtures.TINY_D_PAGE, 4, 0.04, 0.1, 3.0),
 }
 LENGTHS = {"tiny_a": (21, 33, 49, 70), "tiny_b": (25, 32, 64, 121), "tiny_c": (40, 65, 130, 300),
-           "tiny_b_stated": (25, 32, 64, 121)}
+           "tiny_b_stated": (25, 32, 64, 121), "tiny_d": (19, 50, 97, 180)}
 PROMPTS = {"tiny_a": (5, 17, 33, 38), "tiny_b": (1, 8, 40, 97), "tiny_c": (8, 33, 98, 268),
-           "tiny_b_stated": (1, 8, 40, 97)}
+           "tiny_b_stated": (1, 8, 40, 97), "tiny_d": (3, 18, 65, 148)}
 
 # float32: different summation orders of the same 32-bit arithmetic.
 F32_TOL = dict(atol=1e-4, rtol=1e-4)
