@@ -70,14 +70,19 @@ struct RotaryArgs {
 // BK: k per pipeline stage.
 // STAGES: depth of the cp.async pipeline.
 // ROTARY: the fused qkv projection with rotation and cache write in the epilogue.
-template <int MT, bool GATED, typename TO, int BK, int STAGES, bool ROTARY>
+// RG: groups of 16 weight rows a block takes (of the gate rows and of the up rows each, in the gated form).  One
+// for up to 16 tokens; with more tokens a block takes two or four groups, so that the slice of x it streams beside
+// its weights (every block reads all of x) stays no larger than they are.
+template <int MT, int RG, bool GATED, typename TO, int BK, int STAGES, bool ROTARY>
 __global__ void __launch_bounds__(THREADS)
 gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 *__restrict__ w, int M, int N, int K,
                    int64_t ldx, int64_t ldw, int64_t ldo, int k_per_split, int64_t split_stride, int early_successor,
                    RotaryArgs rotary) {
+  static_assert(!ROTARY || RG == 1, "the rotary form takes one group of rows a block");
   constexpr int WSETS = GATED ? 2 : 1;
+  constexpr int ROWS = BN * RG;                    // weight rows per set and block
   constexpr int CPR = BK / 8;                      // 16-byte chunks per row of a tile
-  constexpr int W_STAGE = WSETS * BN * BK;         // elements
+  constexpr int W_STAGE = WSETS * ROWS * BK;       // elements
   constexpr int X_STAGE = MT * 8 * BK;
   constexpr int KSTEPS_PER_WARP = BK / 16 / WARPS;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -87,7 +92,7 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
   auto swz = [](int r, int c) { return r * CPR + (c ^ (r & 7)); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = blockIdx.x * BN;                  // first output column of this block
+  const int n0 = blockIdx.x * ROWS;                // first output column of this block
   const int split = blockIdx.y;
   const int k_begin = split * k_per_split;
   const int k_end = min(K, k_begin + k_per_split);
@@ -102,16 +107,16 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
     const int k0 = k_begin + kt * BK;
     bf16 *dst = w_smem + stage * W_STAGE;
 #pragma unroll
-    for (int i = 0; i < WSETS * BN * CPR / THREADS; ++i) {
+    for (int i = 0; i < WSETS * ROWS * CPR / THREADS; ++i) {
       const int c = tid + i * THREADS;
-      const int set = c / (BN * CPR), rc = c % (BN * CPR);
+      const int set = c / (ROWS * CPR), rc = c % (ROWS * CPR);
       const int row = rc / CPR, chunk = rc % CPR;
       const int n = n0 + row;
       const int k = k0 + chunk * 8;
       const bool valid = n < n_out && k < k_end;
       int64_t wrow = GATED ? (set == 0 ? n : n_out + n) : n;
       if constexpr (ROTARY) wrow = rot_head * rotary.head_dim + (row < 8 ? rot_j0 + row : half + rot_j0 + row - 8);
-      cp16(dst + set * BN * BK + swz(row, chunk) * 8, w + (valid ? wrow * ldw + k : 0), valid);
+      cp16(dst + set * ROWS * BK + swz(row, chunk) * 8, w + (valid ? wrow * ldw + k : 0), valid);
     }
   };
   auto load_x = [&](int stage, int kt) {
@@ -188,11 +193,13 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
     cp_commit();
   }
 
-  float acc[WSETS][MT][4];
+  float acc[WSETS][RG][MT][4];
 #pragma unroll
   for (int a = 0; a < WSETS; ++a)
 #pragma unroll
-    for (int m = 0; m < MT; ++m) acc[a][m][0] = acc[a][m][1] = acc[a][m][2] = acc[a][m][3] = 0.0f;
+    for (int r = 0; r < RG; ++r)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[a][r][m][0] = acc[a][r][m][1] = acc[a][r][m][2] = acc[a][r][m][3] = 0.0f;
 
   const int j = lane >> 3;
   for (int kt = 0; kt < num_tiles; ++kt) {
@@ -209,28 +216,33 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
 #pragma unroll
     for (int i = 0; i < KSTEPS_PER_WARP; ++i) {
       const int ks = warp + i * WARPS;             // this warp's k-steps of the tile
-      uint32_t a[WSETS][4];
-#pragma unroll
-      for (int set = 0; set < WSETS; ++set) {
-        const int row = (j & 1) * 8 + (lane & 7);
-        ldsm4(a[set], ws + set * BN * BK + swz(row, ks * 2 + (j >> 1)) * 8);
-      }
+      // the tokens' fragments of this k-step once, for every group of weight rows
+      uint32_t b[(MT + 1) / 2][4];
       if constexpr (MT == 1) {
         // one token tile: matrices 0 and 1 are (k low, k high) of this k-step; 2 and 3 repeat them
-        uint32_t b[4];
-        ldsm4(b, xs + swz(lane & 7, ks * 2 + (j & 1)) * 8);
-#pragma unroll
-        for (int set = 0; set < WSETS; ++set) mma16816(acc[set][0], a[set], b[0], b[1]);
+        ldsm4(b[0], xs + swz(lane & 7, ks * 2 + (j & 1)) * 8);
       } else {
 #pragma unroll
         for (int m = 0; m < MT; m += 2) {
-          uint32_t b[4];
           const int row = m * 8 + (j >> 1) * 8 + (lane & 7);
-          ldsm4(b, xs + swz(row, ks * 2 + (j & 1)) * 8);
+          ldsm4(b[m / 2], xs + swz(row, ks * 2 + (j & 1)) * 8);
+        }
+      }
 #pragma unroll
-          for (int set = 0; set < WSETS; ++set) {
-            mma16816(acc[set][m], a[set], b[0], b[1]);
-            mma16816(acc[set][m + 1], a[set], b[2], b[3]);
+      for (int set = 0; set < WSETS; ++set) {
+#pragma unroll
+        for (int r = 0; r < RG; ++r) {
+          uint32_t a[4];
+          const int row = r * BN + (j & 1) * 8 + (lane & 7);
+          ldsm4(a, ws + set * ROWS * BK + swz(row, ks * 2 + (j >> 1)) * 8);
+          if constexpr (MT == 1) {
+            mma16816(acc[set][r][0], a, b[0][0], b[0][1]);
+          } else {
+#pragma unroll
+            for (int m = 0; m < MT; m += 2) {
+              mma16816(acc[set][r][m], a, b[m / 2][0], b[m / 2][1]);
+              mma16816(acc[set][r][m + 1], a, b[m / 2][2], b[m / 2][3]);
+            }
           }
         }
       }
@@ -241,19 +253,22 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
   if (!early_successor) le::let_successor_start();   // only the reduction and the stores are left
 
   // the four warps hold partial sums over their k-steps: add them in warp order
-  float *red = reinterpret_cast<float *>(smem_raw);          // [WARPS][WSETS * MT * 4][32]
-  constexpr int VALUES = WSETS * MT * 4;
+  float *red = reinterpret_cast<float *>(smem_raw);          // [WARPS][VALUES][32]
+  constexpr int VALUES = WSETS * RG * MT * 4;
+  auto value_at = [](int set, int r, int m, int e) { return ((r * MT + m) * 4 + e) * WSETS + set; };
 #pragma unroll
   for (int a = 0; a < WSETS; ++a)
 #pragma unroll
-    for (int m = 0; m < MT; ++m)
+    for (int r = 0; r < RG; ++r)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) red[(warp * VALUES + (a * MT + m) * 4 + e) * 32 + lane] = acc[a][m][e];
+      for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) red[(warp * VALUES + value_at(a, r, m, e)) * 32 + lane] = acc[a][r][m][e];
   __syncthreads();
-  if (warp != 0) return;
   // fragment (n, m): c0, c1 at (n = g, m = 2t, 2t + 1); c2, c3 at (n = g + 8, same m)
   const int g = lane >> 2, t = lane & 3;
   if constexpr (ROTARY) {
+    if (warp != 0) return;
     // c0 / c1 are the low-half values of tokens 2t / 2t + 1, c2 / c3 their partners in the high half
     const bool is_q = rot_head < rotary.num_heads;
     const bool is_k = !is_q && rot_head < rotary.num_heads + rotary.num_kv_heads;
@@ -265,8 +280,8 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
         float lo = 0.0f, hi = 0.0f;
 #pragma unroll
         for (int wi = 0; wi < WARPS; ++wi) {
-          lo += red[(wi * VALUES + m * 4 + q) * 32 + lane];
-          hi += red[(wi * VALUES + m * 4 + 2 + q) * 32 + lane];
+          lo += red[(wi * VALUES + value_at(0, 0, m, q)) * 32 + lane];
+          hi += red[(wi * VALUES + value_at(0, 0, m, 2 + q)) * 32 + lane];
         }
         if (rot_dst[m][q] < 0) continue;
         // the product's output is rounded to bfloat16 as the plain form rounds it, then rotated in 32 bits
@@ -277,9 +292,10 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
       }
     return;
   }
+  // the (group of rows, tile of tokens) pieces of the block's result are shared out over the warps
   TO *dst = out + static_cast<int64_t>(split) * split_stride;
-#pragma unroll
-  for (int m = 0; m < MT; ++m) {
+  for (int item = warp; item < RG * MT; item += WARPS) {
+    const int r = item / MT, m = item % MT;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       float v[WSETS];
@@ -287,14 +303,14 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
       for (int a = 0; a < WSETS; ++a) {
         v[a] = 0.0f;
 #pragma unroll
-        for (int wi = 0; wi < WARPS; ++wi) v[a] += red[(wi * VALUES + (a * MT + m) * 4 + e) * 32 + lane];
+        for (int wi = 0; wi < WARPS; ++wi) v[a] += red[(wi * VALUES + value_at(a, r, m, e)) * 32 + lane];
       }
-      const int n = n0 + g + (e >> 1) * 8;
+      const int n = n0 + r * BN + g + (e >> 1) * 8;
       const int row = m * 8 + 2 * t + (e & 1);
       if (n < n_out && row < M) {
-        float r = v[0];
-        if constexpr (GATED) r = r / (1.0f + expf(-r)) * v[WSETS - 1];
-        dst[row * ldo + n] = le::from_f32<TO>(r);
+        float x = v[0];
+        if constexpr (GATED) x = x / (1.0f + expf(-x)) * v[WSETS - 1];
+        dst[row * ldo + n] = le::from_f32<TO>(x);
       }
     }
   }
@@ -323,19 +339,20 @@ int64_t resident_blocks(Kernel kernel, size_t smem) {
   return static_cast<int64_t>(per_sm) * sms;
 }
 
-template <int MT, bool GATED, typename TO, bool ROTARY, int STAGES>
+template <int MT, int RG, bool GATED, typename TO, bool ROTARY, int STAGES>
 struct Form {
   static constexpr int WSETS = GATED ? 2 : 1;
   static constexpr int BK = 128;
+  static constexpr int ROWS = BN * RG;
   static size_t smem() {
-    const size_t pipeline = static_cast<size_t>(STAGES) * (WSETS * BN * BK + MT * 8 * BK) * sizeof(bf16);
-    const size_t reduce = static_cast<size_t>(WARPS) * WSETS * MT * 4 * 32 * sizeof(float);
+    const size_t pipeline = static_cast<size_t>(STAGES) * (WSETS * ROWS * BK + MT * 8 * BK) * sizeof(bf16);
+    const size_t reduce = static_cast<size_t>(WARPS) * WSETS * RG * MT * 4 * 32 * sizeof(float);
     return reduce > pipeline ? reduce : pipeline;
   }
   // 0 when the form cannot get its shared memory
   static int64_t resident() {
     static const int64_t n = [] {
-      auto kernel = gemm_skinny_kernel<MT, GATED, TO, BK, STAGES, ROTARY>;
+      auto kernel = gemm_skinny_kernel<MT, RG, GATED, TO, BK, STAGES, ROTARY>;
       if (smem() >= 48 * 1024 &&
           cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem())) != cudaSuccess) {
         cudaGetLastError();
@@ -351,10 +368,10 @@ struct Form {
     const int n_out = GATED ? N / 2 : N;
     int k_per_split = (K + splits - 1) / splits;
     k_per_split = (k_per_split + BK - 1) / BK * BK;
-    dim3 grid((n_out + BN - 1) / BN, splits);
+    dim3 grid((n_out + ROWS - 1) / ROWS, splits);
     const int form = ROTARY ? 1 : (GATED ? 2 : (splits > 1 ? 4 : 8));
     const int early = (early_trigger_mask() & form) && static_cast<int64_t>(grid.x) * grid.y <= resident() ? 1 : 0;
-    return le::launch_chained(gemm_skinny_kernel<MT, GATED, TO, BK, STAGES, ROTARY>, grid, dim3(THREADS), smem(), stream,
+    return le::launch_chained(gemm_skinny_kernel<MT, RG, GATED, TO, BK, STAGES, ROTARY>, grid, dim3(THREADS), smem(), stream,
                               static_cast<TO *>(out), static_cast<const bf16 *>(x), static_cast<const bf16 *>(w), M, N, K, ldx, ldw,
                               ldo, k_per_split, split_stride, early, rotary);
   }
@@ -363,13 +380,24 @@ struct Form {
 template <int MT, bool GATED, typename TO, bool ROTARY = false>
 int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int splits,
            int64_t split_stride, cudaStream_t stream, const RotaryArgs &rotary = RotaryArgs{}) {
-  // Few rows leave shared memory for a deeper pipeline: more bytes in flight per block (3 % of a decode step).
-  // Not for the gated form: with two weight tiles per stage its 512 blocks no longer fit the GPU all at once.
-  constexpr int STAGES = (MT <= 2 && !GATED) ? 8 : 4;
-  // (17 stages for the rotary form, so that a block has asked for all of a K of 2048 before it waits for the norm
-  // before it, made the step slower, 0.809 -> 0.826 ms at batch 8: the blocks' 96 KB keep the attention kernel
-  // that follows from starting beside them and fetching its keys early.)
-  return Form<MT, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary);
+  if constexpr (MT <= 2 || ROTARY) {
+    // Few rows leave shared memory for a deeper pipeline: more bytes in flight per block (3 % of a decode step).
+    // Not for the gated form: with two weight tiles per stage its 512 blocks no longer fit the GPU all at once.
+    // (17 stages for the rotary form, so that a block has asked for all of a K of 2048 before it waits for the norm
+    // before it, made the step slower, 0.809 -> 0.826 ms at batch 8: the blocks' 96 KB keep the attention kernel
+    // that follows from starting beside them and fetching its keys early.)
+    constexpr int STAGES = (MT <= 2 && !GATED) ? 8 : 4;
+    return Form<MT, 1, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary);
+  } else {
+    // 17 to 64 tokens: a block takes 64 weight rows where K is split (many blocks anyway), else 32 (or 32 gate and
+    // 32 up rows), with as many stages as leave two blocks a multiprocessor
+    constexpr int STAGES = MT <= 4 ? 4 : 3;
+    if constexpr (!GATED) {
+      if (splits > 1)
+        return Form<MT, 4, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary);
+    }
+    return Form<MT, 2, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary);
+  }
 }
 
 template <bool GATED, typename TO>

@@ -329,7 +329,7 @@ class ModelRunner:
         multi = [i for i, e in enumerate(entries) if e.count > 1]
         if len(multi) != 1 or self.model.states:
             return None
-        if total <= ops.SKINNY_ROWS:
+        if total <= ops.SKINNY_NARROW_ROWS:
             # so few rows run on the weight-streaming kernels, as decode steps do, and those give a row the same
             # bits whatever the number of rows; padded, the step would go to other kernels with other roundings
             return None

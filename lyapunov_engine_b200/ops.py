@@ -283,12 +283,22 @@ def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
                                a.stride(0), w.stride(0), out.stride(0), _stream()), "le_gemm_simt")
 
 
-SKINNY_ROWS = 16          # up to this many rows a product streams weights through the package's own kernel (17..32 rows: 3-7 % slower per decode step than the library and the tcgen05 kernel, measured at three model sizes)
+# Up to this many rows a product streams weights through the package's own kernel (mma.sync with the weights as
+# the 16-row operand).  Up to 16 rows of x a block takes 16 weight rows, and every product of a decode step runs
+# there.  From 17 to 32 rows a block takes 32 or 64 weight rows (so that the slice of x it streams beside them is
+# no larger than they are), and the products that are bound by their weights' bytes stay: the gated one (12.5 us
+# against 18.6 of the tcgen05 kernel and 13.2 + the activation of the library at the 1B sizes) and the split-K
+# ones that feed the residual stream (o 3.9 against 5.7 us of the library, down 9.5 against 13.1); the plain qkv
+# product goes to the library there (6.9 against 5.7).  Beyond 32 rows mma.sync is the limit (64 rows: 20.5 us
+# gated against 18.5 of the tcgen05 kernel).
+SKINNY_ROWS = int(os.environ.get("LYAPUNOV_SKINNY_ROWS", "32"))
+SKINNY_NARROW_ROWS = 16   # rows of x up to which a block takes 16 weight rows (and the qkv product its rotary epilogue)
 SKINNY_BLOCKS_PER_SM = 512 / 148   # blocks worth having in flight per multiprocessor (512 on a B200: 4 slices of K for 2048 columns, measured best of 1..8)
 
 
-def skinny_applies(a: torch.Tensor, w: torch.Tensor) -> bool:
-    return (a.dtype == torch.bfloat16 and a.shape[0] <= SKINNY_ROWS and a.shape[1] % 8 == 0 and a.stride(1) == 1
+def skinny_applies(a: torch.Tensor, w: torch.Tensor, rows: int | None = None) -> bool:
+    """``rows``: the most rows of x the caller's form is worth it for (SKINNY_ROWS by default)."""
+    return (a.dtype == torch.bfloat16 and a.shape[0] <= (SKINNY_ROWS if rows is None else rows) and a.shape[1] % 8 == 0 and a.stride(1) == 1
             and w.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
 
 
@@ -315,7 +325,7 @@ FUSE_ROTARY = os.environ.get("LYAPUNOV_FUSE_ROTARY", "1") not in ("0", "")
 
 def rotary_product_applies(a: torch.Tensor, w: torch.Tensor, head_dim: int, rot: int) -> bool:
     """Whether the qkv product, the rotation and the cache write can be one kernel."""
-    return skinny_applies(a, w) and rot == head_dim and head_dim % 16 == 0 and head_dim >= 16
+    return skinny_applies(a, w, SKINNY_NARROW_ROWS) and rot == head_dim and head_dim % 16 == 0 and head_dim >= 16
 
 
 def gemm_skinny_rotary(qkv, a, w, k_cache, v_cache, cos_sin, positions, request_of_token, block_table, num_heads,
@@ -389,8 +399,12 @@ def tc_fills_the_gpu(m: int, n: int) -> bool:
     return tiles >= 0.8 * rounds * 148
 
 
-def split_k_for(n_out: int, k: int) -> int:
+def split_k_for(n_out: int, k: int, rows: int = 1) -> int:
     """How many slices of K give a product enough blocks to fill the GPU."""
+    if rows > SKINNY_NARROW_ROWS:
+        # blocks of 64 weight rows, two to a multiprocessor
+        blocks = (n_out + 63) // 64
+        return max(1, min((2 * sm_count() + blocks - 1) // blocks, k // 256, 16))
     blocks = (n_out + 15) // 16
     in_flight = int(SKINNY_BLOCKS_PER_SM * sm_count() + 0.5)
     return max(1, min((in_flight + blocks - 1) // blocks, k // 512, 16))
@@ -402,7 +416,7 @@ def linear_for_residual(a: torch.Tensor, w: torch.Tensor, workspace, key: str, s
     few rows, float32 partial sums [S, M, N] that the next norm adds up."""
     M, N = a.shape[0], w.shape[0]
     if skinny_applies(a, w):
-        splits = split_k_for(N, a.shape[1])
+        splits = split_k_for(N, a.shape[1], M)
         out = workspace.get(key + "_partials", (splits, M, N), torch.float32)
         if splits == 1:
             gemm_skinny(out[0], a, w)
@@ -439,7 +453,7 @@ def linear(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status=None) -> 
         gemm_simt(out, a, w)
         return
     _need_cuda(out, a, w)
-    if skinny_applies(a, w):
+    if skinny_applies(a, w, SKINNY_NARROW_ROWS):
         gemm_skinny(out, a, w)
         return
     if TC_PLAIN_PRODUCTS and tc_applies(a, w) and tc_fills_the_gpu(a.shape[0], w.shape[0]):

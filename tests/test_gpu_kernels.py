@@ -281,7 +281,7 @@ def test_qkv_product_with_rotary_epilogue(M, nh, nkv, hd, page, K, write):
     ang = torch.outer(torch.arange(64).float(), inv)
     cos_sin = torch.cat([ang.cos(), ang.sin()], -1).contiguous().to(DEV)
     status = o.new_status(DEV)
-    assert o.rotary_product_applies(x, w, hd, hd) == (M <= o.SKINNY_ROWS)      # the engine's choice; the kernel takes 64 rows
+    assert o.rotary_product_applies(x, w, hd, hd) == (M <= o.SKINNY_NARROW_ROWS)      # the engine's choice; the kernel takes 64 rows
     qkv1 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
     k1 = torch.zeros(pages, nkv, page, hd, dtype=torch.bfloat16, device=DEV)
     v1 = torch.zeros_like(k1)
