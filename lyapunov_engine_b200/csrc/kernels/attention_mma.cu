@@ -755,6 +755,31 @@ LE_API int64_t le_attention_decode_scratch_floats(int num_requests, int num_head
 // LYAPUNOV_CLUSTER_MERGE=<n> sets another limit up to 16, 0 switches it off.
 
 
+static size_t decode_smem_bytes() {
+  size_t smem = static_cast<size_t>(DC_WARPS) * DC_WARP_SMEM * sizeof(bf16);
+  // the warps' partial results, and behind them the block's own for the merge across a cluster
+  const size_t merge = static_cast<size_t>(DC_WARPS * 16 * HD + 2 * DC_WARPS * 16 + 16 * HD + 32) * sizeof(float);
+  return merge > smem ? merge : smem;
+}
+
+// Clusters of `num_splits` of the decode kernel's blocks that the device holds at once; 0 if it takes none.
+static int decode_clusters_resident(int num_splits, size_t smem) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(num_splits, 1, 1);
+  config.blockDim = dim3(DC_THREADS);
+  config.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(num_splits);
+  attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  int clusters = 0;
+  const bool ok = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel, &config) == cudaSuccess;
+  cudaGetLastError();                                    // a refusal is an answer, not an error of the caller
+  return ok && clusters > 0 ? clusters : 0;
+}
+
 // Whether the device can hold a cluster of `num_splits` of the decode kernel's blocks (asked once per size).
 static bool cluster_splits_fit(int num_splits, size_t smem) {
   static const int limit = [] {
@@ -768,24 +793,34 @@ static bool cluster_splits_fit(int num_splits, size_t smem) {
     bool fits = true;
     if (num_splits > 8)
       fits = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
-    if (fits) {
-      cudaLaunchConfig_t config = {};
-      config.gridDim = dim3(num_splits, 1, 1);
-      config.blockDim = dim3(DC_THREADS);
-      config.dynamicSmemBytes = smem;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = static_cast<unsigned>(num_splits);
-      attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
-      config.attrs = attr;
-      config.numAttrs = 1;
-      int clusters = 0;
-      fits = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel, &config) == cudaSuccess && clusters > 0;
-    }
+    if (fits) fits = decode_clusters_resident(num_splits, smem) > 0;
     cudaGetLastError();                                  // a refusal above is an answer, not an error of the caller
     known[num_splits] = fits ? 1 : -1;
   }
   return known[num_splits] > 0;
+}
+
+// Blocks of the decode kernel that the device holds at once when the keys are
+// cut `num_splits` ways: whole clusters where the splits run as a cluster
+// (clusters stay inside one part of the chip, so fewer blocks fit than the
+// multiprocessors' shared memory alone would take), single blocks otherwise.
+// 0 if the device could not be asked.
+LE_API int le_attention_decode_resident_blocks(int num_splits) {
+  const size_t smem = decode_smem_bytes();
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  if (cluster_splits_fit(num_splits, smem)) return num_splits * decode_clusters_resident(num_splits, smem);
+  int device = 0, sms = 0, per_sm = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel, DC_THREADS, smem) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return sms * per_sm;
 }
 
 // `requests` (optional): the indices of the batch's decode requests; without
@@ -803,10 +838,7 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
   const int group = num_heads / num_kv_heads;
   const int row_tiles = (group + 15) / 16;
   if (num_kv_heads * row_tiles > 65535 || num_requests > 65535) return le::invalid("le_attention_decode_bf16: the batch is too large for one launch");
-  size_t smem = static_cast<size_t>(DC_WARPS) * DC_WARP_SMEM * sizeof(bf16);
-  // the warps' partial results, and behind them the block's own for the merge across a cluster
-  const size_t merge = static_cast<size_t>(DC_WARPS * 16 * HD + 2 * DC_WARPS * 16 + 16 * HD + 32) * sizeof(float);
-  if (merge > smem) smem = merge;
+  const size_t smem = decode_smem_bytes();
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return le::invalid("le_attention_decode_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));

@@ -546,6 +546,26 @@ def attention_decode_scratch_floats(head_dim: int, num_requests: int, num_heads:
     return 0 if num_splits <= 1 else num_requests * num_heads * num_splits * (head_dim + 2)
 
 
+_decode_resident: dict[tuple, int] = {}
+
+
+def attention_decode_resident_blocks(head_dim: int, num_splits: int) -> int:
+    """Blocks of the split-key decode attention that the current device holds
+    at once when the keys are cut ``num_splits`` ways (asked once per size).
+    Splits that run as a thread-block cluster come in whole clusters, and fewer
+    of those fit than twice the multiprocessor count suggests."""
+    key = (torch.cuda.current_device(), head_dim, num_splits)
+    n = _decode_resident.get(key)
+    if n is None:
+        fn = attention_lib(head_dim).le_attention_decode_resident_blocks
+        fn.restype, fn.argtypes = c_int, [c_int]
+        n = int(fn(num_splits))
+        if n <= 0:
+            raise KernelError(f"the device did not say how many decode attention blocks of head size {head_dim} it holds")
+        _decode_resident[key] = n
+    return n
+
+
 def attention_decode_bf16(out, scratch, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, requests,
                           num_requests, num_heads, num_kv_heads, head_dim, page_size, window, scale, num_splits,
                           status) -> None:

@@ -23,7 +23,12 @@ PREFILL_TILE = 128
 DECODE_KEYS_PER_SPLIT = 256     # a split is worth its launch from about four tiles of keys
 DECODE_MAX_SPLITS = 64
 USE_TC_ATTENTION = os.environ.get("LYAPUNOV_TC_ATTENTION", "1") not in ("0", "")
-DECODE_BLOCKS_PER_SM = 2        # blocks of the decode kernel that a multiprocessor holds at once (by their shared memory)
+DECODE_CLUSTER_SPLITS = 8       # up to this many splits merge inside a thread-block cluster; more need a second kernel
+DECODE_WAVE_FILL = 0.97         # the part of the resident blocks that a wave can count on inside a step
+DECODE_WAVE_US = 5.0            # a wave's fixed time
+DECODE_KEY_US = 0.0075          # a block's time per key of head size 64 (keys and values, latency-bound)
+DECODE_MERGE_US = 1.5           # the second kernel of splits beyond a cluster
+DECODE_BYTES_PER_US = 6.5e6     # what all blocks together read from memory
 
 
 def tile_sizes() -> list[int]:
@@ -36,23 +41,38 @@ def prepare(head_dim: int) -> None:
     ops.attention_lib(head_dim)
 
 
-def decode_splits(num_requests: int, num_heads: int, num_kv_heads: int, context_bound: int) -> int:
-    """The fewest splits whose blocks fill the GPU in whole waves (a last wave
-    that is mostly empty costs as much as a full one)."""
-    group = num_heads // num_kv_heads
-    blocks = num_requests * num_kv_heads * ((group + 15) // 16)
+def choose_decode_splits(blocks: int, context_bound: int, head_dim: int, resident) -> int:
+    """The number of splits with the least estimated time.
+
+    ``blocks``: thread blocks before splitting; ``resident(splits)``: blocks the
+    device holds at once at that split count.  The blocks run in waves; a wave
+    takes a fixed time plus the time of a split's keys, so more splits shorten
+    the wave until their blocks no longer fit in one, and then a second wave
+    costs more than the shorter keys save.  A step's kernels overlap at their
+    edges, so the last few places of a wave are not counted on.  The constants
+    are measured on decode steps of the 1B layer sizes at 4,096 keys (batches 1
+    to 32, every split count from 1 to 8)."""
     by_keys = max(1, (context_bound + DECODE_KEYS_PER_SPLIT - 1) // DECODE_KEYS_PER_SPLIT)
     limit = max(1, min(by_keys, DECODE_MAX_SPLITS))
-    best, best_fill = 1, 0.0
-    resident = DECODE_BLOCKS_PER_SM * ops.sm_count()
+    # however the keys are cut, all of them cross the memory bus once
+    floor = blocks * context_bound * 4 * head_dim / DECODE_BYTES_PER_US
+    best, best_cost = 1, float("inf")
     for splits in range(1, limit + 1):
-        waves = blocks * splits / resident
-        fill = waves / -(-waves // 1)        # waves / ceil(waves)
-        if fill >= 0.85:
-            return splits
-        if fill > best_fill + 1e-9:
-            best, best_fill = splits, fill
+        places = max(1, int(DECODE_WAVE_FILL * resident(splits)))
+        waves = -(-blocks * splits // places)
+        keys = -(-context_bound // splits)
+        cost = max(floor, waves * (DECODE_WAVE_US + keys * DECODE_KEY_US * head_dim / 64))
+        if splits > DECODE_CLUSTER_SPLITS:
+            cost += DECODE_MERGE_US
+        if cost < best_cost - 1e-9:          # on a tie the fewer splits stay
+            best, best_cost = splits, cost
     return best
+
+
+def decode_splits(num_requests: int, num_heads: int, num_kv_heads: int, context_bound: int, head_dim: int) -> int:
+    group = num_heads // num_kv_heads
+    blocks = num_requests * num_kv_heads * ((group + 15) // 16)
+    return choose_decode_splits(blocks, context_bound, head_dim, lambda s: ops.attention_decode_resident_blocks(head_dim, s))
 
 
 def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, window, scale) -> None:
@@ -65,7 +85,7 @@ def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, window, scale) -> 
             prefill(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0, n_multi, num_heads,
                     num_kv_heads, head_dim, kv.page_size, window, scale, ctx.status)
         if ctx.num_decode:
-            splits = decode_splits(ctx.num_decode, num_heads, num_kv_heads, ctx.context_bound)
+            splits = decode_splits(ctx.num_decode, num_heads, num_kv_heads, ctx.context_bound, head_dim)
             floats = ops.attention_decode_scratch_floats(head_dim, ctx.num_decode, num_heads, splits)
             scratch = ctx.workspace.get("attention_scratch", (floats,), torch.float32) if floats else None
             requests = None if ctx.num_decode == ctx.num_requests else ctx.decode_requests

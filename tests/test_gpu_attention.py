@@ -150,9 +150,20 @@ def test_tensor_core_kernels(case):
 
 
 def test_decode_splits_choice():
-    from lyapunov_engine_b200.parts.attention_kernels import decode_splits
-    assert decode_splits(64, 32, 8, 4096) == 1      # 512 blocks: 1.73 waves of 296
-    assert decode_splits(8, 32, 8, 4096) == 4       # 256 blocks: one wave, 86 % full
-    assert decode_splits(1, 32, 8, 4096) == 16      # as many as the keys allow
-    assert decode_splits(1, 32, 8, 100) == 1
-    assert decode_splits(1, 32, 8, 131072) == 32    # 256 blocks
+    """On this device: no choice puts more blocks into a wave than the device
+    holds, one split where the batch fills the device by itself, and never
+    fewer keys to a split than a split is worth."""
+    from lyapunov_engine_b200 import ops
+    from lyapunov_engine_b200.parts.attention_kernels import DECODE_KEYS_PER_SPLIT, decode_splits
+    for hd in (64, 128):
+        whole = ops.attention_decode_resident_blocks(hd, 1)
+        assert whole >= ops.sm_count()
+        for s in range(2, 9):
+            assert 0 < ops.attention_decode_resident_blocks(hd, s) <= whole
+        assert decode_splits(1, 32, 8, 100, hd) == 1
+        assert decode_splits(64, 32, 8, 4096, hd) == 1
+        for n in (1, 2, 3, 5, 7, 8):
+            s = decode_splits(n, 32, 8, 4096, hd)
+            assert 1 <= s <= 4096 // DECODE_KEYS_PER_SPLIT
+            if s > 1:
+                assert n * 8 * s <= ops.attention_decode_resident_blocks(hd, s), (hd, n, s)
