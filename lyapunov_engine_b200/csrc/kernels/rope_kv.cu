@@ -84,18 +84,49 @@ rope_kv_vec_kernel(T *__restrict__ qkv, T *__restrict__ k_cache, T *__restrict__
   le::let_successor_start();
   le::wait_for_predecessor();
   const int t = blockIdx.x;
+  const int chunks = head_dim / VEC, half_chunks = rot / 2 / VEC, rot_chunks = rot / VEC;
+  const int row = (num_heads + 2 * num_kv_heads) * head_dim;
+  T *x_row = qkv + static_cast<int64_t>(t) * row;
+  const int half = rot / 2;
+  // Work items, so that no thread idles: for every query and key head `half_chunks` pairs (a chunk of the low
+  // half with its partner of the high half) and the chunks beyond the rotary width; for every value head its
+  // chunks.  One pass of the block covers a token of the usual shapes.
+  const int tail_chunks = chunks - rot_chunks;
+  const int per_qk = half_chunks + tail_chunks;
+  const int qk_items = (num_heads + (write_kv ? num_kv_heads : 0)) * per_qk;
+  const int items = qk_items + (write_kv ? num_kv_heads * chunks : 0);
+  // An item's one or two chunks of the token's row.  Where they lie depends on the token alone, so they are
+  // asked for before the token's position, its page and its angles are known: the row's loads, the position's
+  // and the request's then fly together, and the page and the angles follow as one more round, where the
+  // position, the request, the page and the row used to be four rounds one after the other.
+  auto fetch = [&](int item, Vec16<T> &a, Vec16<T> &b) {
+    if (item < qk_items) {
+      const int h = item / per_qk, j = item - h * per_qk;
+      const T *x = x_row + static_cast<int64_t>(h) * head_dim;
+      if (j < half_chunks) {
+        a = *reinterpret_cast<const Vec16<T> *>(x + j * VEC);
+        b = *reinterpret_cast<const Vec16<T> *>(x + half + j * VEC);
+      } else if (h >= num_heads) {
+        a = *reinterpret_cast<const Vec16<T> *>(x + (rot_chunks + j - half_chunks) * VEC);
+      }
+    } else {
+      const int idx = item - qk_items;
+      const int kvh = idx / chunks, c = idx - kvh * chunks;
+      a = *reinterpret_cast<const Vec16<T> *>(x_row + static_cast<int64_t>(num_heads + num_kv_heads + kvh) * head_dim + c * VEC);
+    }
+  };
+  int item = threadIdx.x;
+  Vec16<T> a, b;
+  if (item < items) fetch(item, a, b);
   const int pos = positions[t];
+  const int request = write_kv ? request_of_token[t] : 0;
   if (pos < 0 || pos >= max_pos) {
     if (threadIdx.x == 0) atomicOr(status, LE_STATUS_BAD_POSITION);
     return;
   }
-  const int chunks = head_dim / VEC, half_chunks = rot / 2 / VEC, rot_chunks = rot / VEC;
-  const int row = (num_heads + 2 * num_kv_heads) * head_dim;
-  T *x_row = qkv + static_cast<int64_t>(t) * row;
   int64_t kv_base = -1;
   if (write_kv) {
-    const int b = request_of_token[t];
-    const int page = block_table[static_cast<int64_t>(b) * max_blocks + pos / page_size];
+    const int page = block_table[static_cast<int64_t>(request) * max_blocks + pos / page_size];
     if (page < 0 || page >= num_pages) {
       if (threadIdx.x == 0) atomicOr(status, LE_STATUS_BAD_PAGE);
     } else {
@@ -103,54 +134,41 @@ rope_kv_vec_kernel(T *__restrict__ qkv, T *__restrict__ k_cache, T *__restrict__
     }
   }
   const float *cs = cos_sin + static_cast<int64_t>(pos) * rot;
-  const int half = rot / 2;
-  // Work items, so that no thread idles: for every query and key head `half_chunks` pairs (a chunk of the low
-  // half with its partner of the high half) and the chunks beyond the rotary width; for every value head its
-  // chunks.  One pass of the block covers a token of the usual shapes, with every load in flight at once.
-  const int tail_chunks = chunks - rot_chunks;
-  const int per_qk = half_chunks + tail_chunks;
-  const int qk_items = (num_heads + (write_kv ? num_kv_heads : 0)) * per_qk;
-  const int items = qk_items + (write_kv ? num_kv_heads * chunks : 0);
-  for (int item = threadIdx.x; item < items; item += blockDim.x) {
+  while (item < items) {
     if (item < qk_items) {
       const int h = item / per_qk, j = item - h * per_qk;
       const bool is_q = h < num_heads;
-      T *x = x_row + static_cast<int64_t>(h) * head_dim;
-      T *dst = x;
-      if (!is_q) {
-        if (kv_base < 0) continue;
-        dst = k_cache + kv_base + static_cast<int64_t>(h - num_heads) * page_size * head_dim;
-      }
-      if (j < half_chunks) {
-        const Vec16<T> lo = *reinterpret_cast<const Vec16<T> *>(x + j * VEC);
-        const Vec16<T> hi = *reinterpret_cast<const Vec16<T> *>(x + half + j * VEC);
-        float cc[VEC], ss[VEC];
+      T *dst = x_row + static_cast<int64_t>(h) * head_dim;
+      if (!is_q) dst = kv_base < 0 ? nullptr : k_cache + kv_base + static_cast<int64_t>(h - num_heads) * page_size * head_dim;
+      if (dst != nullptr) {
+        if (j < half_chunks) {
+          float cc[VEC], ss[VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; i += 4) {
-          *reinterpret_cast<float4 *>(cc + i) = *reinterpret_cast<const float4 *>(cs + j * VEC + i);
-          *reinterpret_cast<float4 *>(ss + i) = *reinterpret_cast<const float4 *>(cs + half + j * VEC + i);
-        }
-        Vec16<T> out_lo, out_hi;
+          for (int i = 0; i < VEC; i += 4) {
+            *reinterpret_cast<float4 *>(cc + i) = *reinterpret_cast<const float4 *>(cs + j * VEC + i);
+            *reinterpret_cast<float4 *>(ss + i) = *reinterpret_cast<const float4 *>(cs + half + j * VEC + i);
+          }
+          Vec16<T> out_lo, out_hi;
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-          const float x0 = le::to_f32(lo.v[i]), x1 = le::to_f32(hi.v[i]);
-          out_lo.v[i] = le::from_f32<T>(x0 * cc[i] - x1 * ss[i]);
-          out_hi.v[i] = le::from_f32<T>(x1 * cc[i] + x0 * ss[i]);
+          for (int i = 0; i < VEC; ++i) {
+            const float x0 = le::to_f32(a.v[i]), x1 = le::to_f32(b.v[i]);
+            out_lo.v[i] = le::from_f32<T>(x0 * cc[i] - x1 * ss[i]);
+            out_hi.v[i] = le::from_f32<T>(x1 * cc[i] + x0 * ss[i]);
+          }
+          *reinterpret_cast<Vec16<T> *>(dst + j * VEC) = out_lo;
+          *reinterpret_cast<Vec16<T> *>(dst + half + j * VEC) = out_hi;
+        } else if (!is_q) {
+          *reinterpret_cast<Vec16<T> *>(dst + (rot_chunks + j - half_chunks) * VEC) = a;
         }
-        *reinterpret_cast<Vec16<T> *>(dst + j * VEC) = out_lo;
-        *reinterpret_cast<Vec16<T> *>(dst + half + j * VEC) = out_hi;
-      } else if (dst != x) {
-        const int c = rot_chunks + j - half_chunks;
-        *reinterpret_cast<Vec16<T> *>(dst + c * VEC) = *reinterpret_cast<const Vec16<T> *>(x + c * VEC);
       }
-    } else {
-      if (kv_base < 0) continue;
+    } else if (kv_base >= 0) {
       const int idx = item - qk_items;
       const int kvh = idx / chunks, c = idx - kvh * chunks;
-      const T *x = x_row + static_cast<int64_t>(num_heads + num_kv_heads + kvh) * head_dim;
       T *dst = v_cache + kv_base + static_cast<int64_t>(kvh) * page_size * head_dim;
-      *reinterpret_cast<Vec16<T> *>(dst + c * VEC) = *reinterpret_cast<const Vec16<T> *>(x + c * VEC);
+      *reinterpret_cast<Vec16<T> *>(dst + c * VEC) = a;
     }
+    item += blockDim.x;
+    if (item < items) fetch(item, a, b);
   }
 }
 
