@@ -6,11 +6,18 @@
 // head (one head where the group has an odd one left) and walks the keys in
 // tiles of 128; every tile of keys and values is fetched once for both heads.
 // Roles:
-//   warp 0      producer: its lanes look the tile's pages up in the block table
+//   warps 0..7  softmax, a group of four warps per head.  Thread (quarter,
+//               lane) owns query row r with all 128 keys of the tile: it reads
+//               the scores from tensor memory into registers, masks what the
+//               row may not see, keeps the running maximum and the sum in 32
+//               bits (exp2 with the scale folded in) and writes the
+//               probabilities as bfloat16 pairs back into tensor memory, the A
+//               operand of the next product.
+//   warp 8      producer: its lanes look the tile's pages up in the block table
 //               and each issues the TMA copies of one page's keys or values
 //               (128-byte swizzle) into a ring of key stages and one of value
 //               stages;
-//   warp 1      tensor core: one thread issues the products O += P V (128 x
+//   warp 9      tensor core: one thread issues the products O += P V (128 x
 //               head size x 128) of both heads when their probabilities are
 //               ready;
 //   warp 10     tensor core: one thread issues the scores S = Q K^T (128 x 128
@@ -19,14 +26,12 @@
 //               (Where tensor memory has no room for the probabilities beside
 //               the scores - head size 128 - they overwrite the scores they
 //               came from, the next scores must follow the product that reads
-//               them, and warp 1 issues everything in that order.)
-//   warps 2..9  softmax, a group of four warps per head.  Thread (quarter,
-//               lane) owns query row r with all 128 keys of the tile: it reads
-//               the scores from tensor memory into registers, masks what the
-//               row may not see, keeps the running maximum and the sum in 32
-//               bits (exp2 with the scale folded in) and writes the
-//               probabilities as bfloat16 pairs back into tensor memory, the A
-//               operand of the next product.
+//               them, and warp 9 issues everything in that order.)
+//   warp 11     none: it fills the third warp group.
+// A softmax thread holds its row's 128 scores in registers; the other roles
+// need few.  Registers are shared out by warp group (setmaxnreg): the third
+// group gives up what the two softmax groups take (72 and 216 a thread where
+// the launch bound gives 168 to all), which ends the softmax loop's spills.
 // The running maximum only moves when the tile's maximum exceeds it by more
 // than 2^8 in the exponent; until then probabilities up to 256 go into the
 // product and the sum (both 32-bit accumulations), which the final division
@@ -57,8 +62,12 @@ constexpr int DB = HD / 64;                 // 64-wide blocks of the head size
 constexpr int BM = 128, BN = 128;           // query rows, keys per tile
 constexpr int KS = HD == 64 ? 4 : 3;        // key stages
 constexpr int VS = HD == 64 ? 4 : 2;        // value stages
-constexpr int THREADS = 352;                // producer, products, two softmax groups of four warps, scores
-constexpr int SCORE_WARP = 10;
+// Warps 0..7: two softmax groups of four (a warp group each); warps 8..11: producer, products, scores, one idle.
+// The roles need very different numbers of registers, and a block's registers are shared out by warp group:
+// the softmax groups take what the fourth group gives up.
+constexpr int THREADS = 384;
+constexpr int PRODUCER_WARP = 8, PRODUCT_WARP = 9, SCORE_WARP = 10;
+constexpr int SOFTMAX_REGS = 216, OTHER_REGS = 72;      // 2 x 216 + 72 = 3 x 168, what the launch bound gives each thread
 constexpr int Q_BYTES = BM * HD * 2, K_BYTES = BN * HD * 2, V_BYTES = BN * HD * 2;
 constexpr uint32_t TMEM_COLS = 512;         // head g: scores at g * 128, output at 256 + g * head size
 constexpr uint32_t O_COL = 256;
@@ -158,7 +167,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   int page_now = 0, page_next = 0;
   bool producer_ok = true;
 
-  if (warp == 0) {
+  if (warp == PRODUCER_WARP) {
     if (lane == 0) {
       mbar_init(q_full, 1);
       for (int s = 0; s < KS; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
@@ -193,7 +202,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (producer_ok) values_issued = 1;
     }
   }
-  if (warp == 1) {
+  if (warp == PRODUCT_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -228,7 +237,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     tc_commit(o_done + g);                    // the head's accumulator holds tiles 0..j; its probabilities are free
   };
 
-  if (warp == 0) {
+  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(OTHER_REGS));
+  if (warp == PRODUCER_WARP) {
     // ---- producer, from where the early copies stopped
     bool ok = producer_ok;
     for (int j = 0; j < num_tiles && ok; ++j) {
@@ -252,7 +262,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int j = max(0, keys_issued - KS); j < keys_issued; ++j) mbar_wait(k_full + j % KS, (j / KS) & 1, &never);
       for (int j = max(0, values_issued - VS); j < values_issued; ++j) mbar_wait(v_full + j % VS, (j / VS) & 1, &never);
     }
-  } else if (warp == 1) {
+  } else if (warp == PRODUCT_WARP) {
     // ---- tensor-core issue: the products; and the scores too where they have to follow the products
     if (lane == 0) {
       bool ok = true;
@@ -303,10 +313,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       if (!ok) { *failed = 1; atomicOr(status, LE_STATUS_WAIT_TIMEOUT); }
     }
-  } else if (((warp - 2) >> 2) < heads_here) {
+  } else if (warp < 8 && (warp >> 2) < heads_here) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(SOFTMAX_REGS));
     // ---- softmax: thread (quarter, lane) of group g owns query row r of head head0 + g
     const int quarter = warp & 3;               // the tensor-memory lanes this warp may touch
-    const int g = (warp - 2) >> 2;
+    const int g = warp >> 2;
     const int r = quarter * 32 + lane;
     const int p_row = p0 + r;
     const int lo_row = window > 0 ? max(0, p_row - window + 1) : 0;
@@ -412,7 +423,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == PRODUCT_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
