@@ -71,8 +71,8 @@ struct RotaryArgs {
 // STAGES: depth of the cp.async pipeline.
 // ROTARY: the fused qkv projection with rotation and cache write in the epilogue.
 // RG: groups of 16 weight rows a block takes (of the gate rows and of the up rows each, in the gated form).  One
-// for up to 16 tokens; with more tokens a block takes two or four groups, so that the slice of x it streams beside
-// its weights (every block reads all of x) stays no larger than they are.
+// for up to 16 tokens (two where K is split); with more tokens a block takes two or four groups, so that the slice
+// of x it streams beside its weights (every block reads all of x) stays no larger than they are.
 template <int MT, int RG, bool GATED, typename TO, int BK, int STAGES, bool ROTARY>
 __global__ void __launch_bounds__(THREADS)
 gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 *__restrict__ w, int M, int N, int K,
@@ -377,6 +377,15 @@ struct Form {
   }
 };
 
+// LYAPUNOV_SKINNY_WIDE_SPLIT_K=0: 16 weight rows a block for up to 16 tokens in every form.
+bool wide_split_k_enabled() {
+  static const bool on = [] {
+    const char *env = getenv("LYAPUNOV_SKINNY_WIDE_SPLIT_K");
+    return env == nullptr || env[0] != '0';
+  }();
+  return on;
+}
+
 template <int MT, bool GATED, typename TO, bool ROTARY = false>
 int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int splits,
            int64_t split_stride, cudaStream_t stream, const RotaryArgs &rotary = RotaryArgs{}) {
@@ -387,6 +396,15 @@ int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t
     // before it, made the step slower, 0.809 -> 0.826 ms at batch 8: the blocks' 96 KB keep the attention kernel
     // that follows from starting beside them and fetching its keys early.)
     constexpr int STAGES = (MT <= 2 && !GATED) ? 8 : 4;
+    if constexpr (!GATED && !ROTARY) {
+      // Where K is split there are blocks enough for 32 weight rows each: the slice of x that a block streams
+      // beside its weights (from L2, every block the same rows) is then half of them (9 to 16 tokens) or a
+      // quarter, not their equal or half.  Decode at 16 requests 1.10 -> 1.01 ms, at 8 0.810 -> 0.803, at 1
+      // 0.683 -> 0.671.  (Not the gated form: no gain at 9 to 16 tokens, slower below; not the output head's
+      // unsplit product: slower up to 8 tokens; 64 rows a block: slower.)
+      if (splits > 1 && wide_split_k_enabled())
+        return Form<MT, 2, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary);
+    }
     return Form<MT, 1, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary);
   } else {
     // 17 to 64 tokens: a block takes 64 weight rows where K is split (many blocks anyway), else 32 (or 32 gate and
