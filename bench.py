@@ -368,7 +368,7 @@ def run_ours(args):
     pk = peaks()
     torch.cuda.set_device(0)
     # room for the batches the run times (the prompt beside the decoding requests of a mixed step holds a slot too)
-    max_batch = (max(args.batch, 1) + (args.only == "mixed")) if args.only else 64
+    max_batch = (max(args.batch, args.max_num_seqs, 1) + (args.only == "mixed")) if args.only else 64
     rig = make_rig(cfg, CONTEXT, max_batch, BLOCK_SIZE)
     engine, runner, manager, sampler, host, gen, vocab = rig.engine, rig.runner, rig.manager, rig.sampler, rig.host, rig.gen, rig.vocab
     timed_decode, timed_prefill, timed_mixed = rig.timed_decode, rig.timed_prefill, rig.timed_mixed
@@ -652,6 +652,9 @@ def main():
                         "requests beside one --tokens portion of a prompt in every step")
     p.add_argument("--shapes", choices=sorted(SHAPES), default="1b", help="with --only: layer sizes of Llama-3.2-1B, 3.2-3B or 3.1-8B")
     p.add_argument("--batch", type=int, default=8, help="batch of --only decode")
+    p.add_argument("--max-num-seqs", type=int, default=0,
+                   help="with --only decode: the most requests the engine is set up for (0: --batch); a smaller batch "
+                        "then runs as a partly filled step of the next power of two")
     p.add_argument("--page", type=int, default=BLOCK_SIZE, help="tokens per page of the cache")
     p.add_argument("--tokens", type=int, default=0, help="with --only prefill or mixed: tokens of the prompt or of its portion (at most the context and 8192)")
     p.add_argument("--context", type=int, default=0, help="with --only decode: the context the last step ends at")

@@ -431,6 +431,27 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
   const KvLayout kv = make_kv_layout(k_cache, v_cache, block_table + static_cast<int64_t>(b) * max_blocks, kvh,
                                      num_kv_heads, page_size, page_shift, num_pages);
 
+  // A request at position 0 whose first page is the page that nobody owns is padding of a step of fixed shape (a
+  // real request's first token has a page of its own).  Its row is left zero and the block ends at once, and with
+  // it its whole cluster, which is that request's: such blocks then pass through the multiprocessors beside the
+  // real ones without holding a place for longer than their launch.
+  if (p == 0 && kv.table[0] == num_pages - 1) {
+    const int64_t first = (static_cast<int64_t>(blockIdx.z) * num_heads + h0) * num_splits + split;
+    for (int i = tid; i < heads_here * HD; i += DC_THREADS) {
+      const int row = i / HD, d = i % HD;
+      if (num_splits == 1 || cluster_merge) {
+        if (split == 0) out[tok * out_stride + (h0 + row) * HD + d] = __float2bfloat16_rn(0.0f);
+      } else {
+        const int64_t slot = first + static_cast<int64_t>(row) * num_splits;
+        part_o[slot * HD + d] = 0.0f;
+        if (d == 0) {
+          part_ml[slot * 2] = -INFINITY;
+          part_ml[slot * 2 + 1] = 0.0f;
+        }
+      }
+    }
+    return;
+  }
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int total = p + 1 - lo;
   int per_split = (total + num_splits - 1) / num_splits;

@@ -56,7 +56,7 @@ class StepContext:
     __slots__ = ("num_tokens", "num_requests", "num_wanted", "max_q_len", "max_context", "pure_decode",
                  "token_ids", "positions", "request_of_token", "cu_q", "ctx_before", "state_slots", "wanted_rows",
                  "block_tables", "tiles", "workspace", "status", "q_lens", "decode_requests", "num_decode",
-                 "context_bound")
+                 "context_bound", "decode_fill")
 
 
 class ModelRunner:
@@ -172,6 +172,7 @@ class ModelRunner:
                    zip(layout.tile_sizes, layout.off_tile_request, layout.off_tile_q0, layout.num_tiles,
                        layout.num_tiles_multi)}
         c.num_decode = layout.num_decode
+        c.decode_fill = layout.num_decode - (layout.num_requests - layout.num_real_requests)   # the real ones among them
         c.decode_requests = d[layout.off_decode_requests:layout.off_decode_requests + max(layout.num_decode, 1)]
         c.context_bound = layout.max_context
         c.workspace = workspace
@@ -257,20 +258,26 @@ class ModelRunner:
             self._graph_workspace = Workspace(self.runtime.device, pin_old=True)
         return self._graph_workspace
 
-    def _decode_graph(self, bucket: int, width: int) -> "_DecodeGraph":
-        key = (bucket, width)
+    def _decode_graph(self, bucket: int, width: int, fill: int = 0) -> "_DecodeGraph":
+        """The captured step of ``bucket`` rows and tables ``width`` pages
+        wide for a step in which ``fill`` rows are real (0: all of them).
+        Where a mixer launches differently for a partly filled step, such
+        steps have a graph of their own."""
+        fill = fill or bucket
+        variant = self.model.decode_variant(fill, bucket, min(self.max_model_len, width * self.cache.block_size))
+        key = (bucket, width, variant)
         graph = self._graphs.pop(key, None)
         if graph is None:
             while len(self._graphs) >= MAX_DECODE_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))        # the one used longest ago
-            graph = _DecodeGraph(self, bucket, width)
+            graph = _DecodeGraph(self, bucket, width, fill)
         self._graphs[key] = graph                                  # (now the one used last)
         return graph
 
     def _graph_step(self, entries, device_tokens=None):
         bucket = self._bucket(len(entries))
         width = self._table_width(max(e.start for e in entries) + 1)
-        graph = self._decode_graph(bucket, width)
+        graph = self._decode_graph(bucket, width, len(entries))
         self.num_graph_steps += 1
         try:
             logits = graph.run(entries, device_tokens)
@@ -312,8 +319,17 @@ class ModelRunner:
         before = self.num_captures
         for bucket in sorted({self._bucket(int(b)) for b in buckets}, reverse=True):
             for width in widths:
-                if (bucket, width) not in self._graphs and len(self._graphs) < MAX_DECODE_GRAPHS:
-                    self._decode_graph(bucket, width).run([], None)
+                bound = min(self.max_model_len, width * self.cache.block_size)
+                # the full step first, then what partly filled ones launch differently (fills down to where the
+                # next smaller bucket takes over)
+                seen = set()
+                for fill in range(bucket, bucket // 2, -1):
+                    variant = self.model.decode_variant(fill, bucket, bound)
+                    if variant in seen:
+                        continue
+                    seen.add(variant)
+                    if (bucket, width, variant) not in self._graphs and len(self._graphs) < MAX_DECODE_GRAPHS:
+                        self._decode_graph(bucket, width, fill).run([], None)
         return self.num_captures - before
 
     def graph_bytes(self) -> int:
@@ -397,6 +413,7 @@ class _StepGraph:
         self.capacity_at_capture = runner._capacity
         self.graph = None
         self.logits = None
+        self.decode_fill = 0      # how many of the one-token requests the step is captured for (0: as the first step has them)
 
     def _launch(self, layout):
         r = self.runner
@@ -408,6 +425,8 @@ class _StepGraph:
         ctx = r._context(layout, self.workspace, num_wanted=self.num_wanted)
         # a captured step serves every context its block tables can hold
         ctx.context_bound = min(r.max_model_len, self.width * r.cache.block_size)
+        if self.decode_fill:
+            ctx.decode_fill = self.decode_fill             # (a warm-up step has dummy requests only)
         ran = False
         self.uses += 1
         if self.warm_key not in r._warmed or (self.uses == 1 and not self.capture_at_first_use):
@@ -447,6 +466,7 @@ class _PromptGraph(_StepGraph):
     def __init__(self, runner: ModelRunner, padded: int, bucket: int, width: int):
         super().__init__(runner, 1 + bucket, width, ("prompt", padded, bucket), capture_at_first_use=False)
         self.padded, self.bucket = padded, bucket
+        self.decode_fill = bucket
 
     def run(self, entries, rows):
         n = self.num_wanted
@@ -459,9 +479,10 @@ class _PromptGraph(_StepGraph):
 class _DecodeGraph(_StepGraph):
     """A decode step for a fixed number of rows."""
 
-    def __init__(self, runner: ModelRunner, bucket: int, width: int):
+    def __init__(self, runner: ModelRunner, bucket: int, width: int, fill: int = 0):
         super().__init__(runner, bucket, width, ("decode", bucket))
         self.bucket = bucket
+        self.decode_fill = fill or bucket
 
     def run(self, entries, device_tokens=None):
         return self._launch(self.runner._pack(entries, pad_requests=self.bucket, fixed=self.width, all_wanted=True,

@@ -104,6 +104,16 @@ class Model:
             part.bind(get, runtime)
 
     # ---- one step
+    def decode_variant(self, fill: int, num_decode: int, context_bound: int) -> tuple:
+        """The mixers' launch choices that depend on how many of a step's
+        one-token requests are real (see Mixer.decode_variant)."""
+        seen = []
+        for b in self.blocks:
+            v = b.mixer.decode_variant(fill, num_decode, context_bound)
+            if v is not None and v not in seen:
+                seen.append(v)
+        return tuple(seen)
+
     def forward(self, ctx, cache):
         """Logits [wanted rows, vocab] float32 (None when nothing is wanted).
         ``cache.binding(run_index)`` gives each run its pages and state."""

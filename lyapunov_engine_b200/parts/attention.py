@@ -45,6 +45,11 @@ class AttentionMixer(Mixer):
     def tile_sizes(self):
         return attention_kernels.tile_sizes()
 
+    def decode_variant(self, fill, num_decode, context_bound):
+        if self.runtime is None or self.runtime.dtype != torch.bfloat16:
+            return None                       # the float32 kernel takes every shape the same way
+        return attention_kernels.decode_variant(fill, self.num_heads, self.num_kv_heads, self.head_dim, context_bound)
+
     def tensors(self):
         q, k, v, o = self.names
         H, nh, nkv, hd = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim

@@ -23,6 +23,8 @@ PREFILL_TILE = 128
 DECODE_KEYS_PER_SPLIT = 256     # a split is worth its launch from about four tiles of keys
 DECODE_MAX_SPLITS = 64
 USE_TC_ATTENTION = os.environ.get("LYAPUNOV_TC_ATTENTION", "1") not in ("0", "")
+# 0: a partly filled step of fixed shape cuts the keys as the full step does (one graph per shape)
+SPLITS_BY_FILL = os.environ.get("LYAPUNOV_SPLITS_BY_FILL", "1") not in ("0", "")
 DECODE_CLUSTER_SPLITS = 8       # up to this many splits merge inside a thread-block cluster; more need a second kernel
 DECODE_WAVE_FILL = 0.97         # the part of the resident blocks that a wave can count on inside a step
 DECODE_WAVE_US = 5.0            # a wave's fixed time
@@ -75,6 +77,15 @@ def decode_splits(num_requests: int, num_heads: int, num_kv_heads: int, context_
     return choose_decode_splits(blocks, context_bound, head_dim, lambda s: ops.attention_decode_resident_blocks(head_dim, s))
 
 
+def decode_variant(fill: int, num_heads: int, num_kv_heads: int, head_dim: int, context_bound: int):
+    """The split count of a step in which ``fill`` of the one-token requests
+    are real: dummy requests finish at once, so the real ones alone fill the
+    waves (9 real requests in a step of 16 take 3 splits, 16 take 2)."""
+    if not SPLITS_BY_FILL or not ops.attention_mma_available(head_dim):
+        return None
+    return decode_splits(max(1, fill), num_heads, num_kv_heads, context_bound, head_dim)
+
+
 def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, window, scale) -> None:
     table = ctx.block_tables[kv.group]
     if out.dtype == torch.bfloat16 and ops.attention_mma_available(head_dim):
@@ -85,7 +96,8 @@ def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, window, scale) -> 
             prefill(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0, n_multi, num_heads,
                     num_kv_heads, head_dim, kv.page_size, window, scale, ctx.status)
         if ctx.num_decode:
-            splits = decode_splits(ctx.num_decode, num_heads, num_kv_heads, ctx.context_bound, head_dim)
+            real = min(ctx.decode_fill, ctx.num_decode) if SPLITS_BY_FILL else 0     # dummy requests finish at once
+            splits = decode_splits(real or ctx.num_decode, num_heads, num_kv_heads, ctx.context_bound, head_dim)
             floats = ops.attention_decode_scratch_floats(head_dim, ctx.num_decode, num_heads, splits)
             scratch = ctx.workspace.get("attention_scratch", (floats,), torch.float32) if floats else None
             requests = None if ctx.num_decode == ctx.num_requests else ctx.decode_requests

@@ -154,6 +154,15 @@ class Mixer(Part):
         bring several tokens), those of several tokens first."""
         return []
 
+    def decode_variant(self, fill: int, num_decode: int, context_bound: int):
+        """What of this mixer's launches depends on how many of a step's
+        ``num_decode`` one-token requests are real (``fill``; the others pad
+        the step to a fixed shape): any hashable, None if nothing.  Steps of
+        fixed shape that are captured once and replayed are kept apart by it;
+        ``forward`` finds the same number in ``ctx.decode_fill`` and must make
+        the same choice from it."""
+        return None
+
     def forward(self, x, ctx, cache):
         raise NotImplementedError
 

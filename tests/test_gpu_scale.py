@@ -167,6 +167,42 @@ def test_decode_batches_beyond_the_weight_streaming_kernels(small, batch, tmp_pa
     assert pages["graph_steps"] >= steps, pages
 
 
+def test_partly_filled_decode_steps_have_graphs_of_their_own(small, tmp_path):
+    """Five and then three requests decode in steps captured for eight and for
+    four rows, at contexts beyond 1,024 keys: the attention kernel cuts the keys
+    of five real requests into more splits than those of eight (the dummy
+    requests that pad the step finish at once), so these steps get a graph of
+    their own beside the full step's, and their logits are the plain
+    implementation's all the same."""
+    cfg = small["cfg"]
+    lengths = [1030 + 9 * i for i in range(5)]
+    steps = 6
+    requests = {f"f{i}": fixtures.random_ids(cfg, n + steps, 760 + i) for i, n in enumerate(lengths)}
+    m = with_references(small, requests, noise_from=("f0", "f1"))
+    t = ru.Trace()
+    names = list(requests)
+    for r, n in zip(names, lengths):
+        t.step([(r, requests[r][:n], [n - 1])])
+    for s in range(steps):
+        live = names if s < 3 else names[:3]                 # two requests end half-way
+        t.step([(r, requests[r][n + s:n + s + 1], [0]) for r, n in zip(names, lengths) if r in live],
+               end=names[3:] if s == 2 else (names[:3] if s == steps - 1 else []))
+    pool = sum((n + steps + 63) // 64 * 64 for n in lengths)
+    check(m, t, "bfloat16", tmp_path, 0, f"{small['name']} partly filled decode steps", extra=("--max-num-seqs", "8"), pool=pool)
+    pages = ru.read_pages(str(tmp_path))
+    shapes = pages["decode_graph_shapes"]
+    assert {rows for rows, _, _ in shapes} == {4, 8}, shapes
+    from lyapunov_engine_b200.parts.attention_kernels import decode_splits
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    apart = 0
+    for rows, fill in ((8, 5), (4, 3)):
+        width = next(w for r, w, _ in shapes if r == rows)
+        want = decode_splits(fill, nh, nkv, width * 16, hd)
+        apart += want != decode_splits(rows, nh, nkv, width * 16, hd)
+        assert [rows, width, [want]] in shapes, shapes
+    assert apart, "the test's sizes no longer tell a partly filled step from a full one"
+
+
 def test_greedy_generation_in_bfloat16(small, tmp_path):
     """Through LLMEngine.generate: every token the engine chose must be a
     maximum of the plain implementation's logits at its place, given the same
