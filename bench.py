@@ -643,6 +643,60 @@ def _reference_line(args):
     }
 
 
+# The reference's serving benchmark (benchmarks/bench_serving.py:10-43: the model; 46-77: what is timed): a small
+# Llama with random weights, every request a prompt of 128 tokens (ids 100, 101, ...), 32 tokens generated
+# greedily, batches of 1, 4, 8, 16.  TTFT is the first step (all prompts in it), ITL the mean of the steps after
+# it, each with a device synchronisation on both sides; tok/s counts prompt and generated tokens over the sum of
+# those times.  Here in bfloat16, and each batch runs twice untimed first (kernels compiled, step graphs captured).
+SERVING_MODEL = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 32000, "hidden_size": 1024,
+    "intermediate_size": 4096, "num_hidden_layers": 8, "num_attention_heads": 16, "num_key_value_heads": 4,
+    "head_dim": 64, "max_position_embeddings": 8192, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+    "rope_scaling": None, "tie_word_embeddings": False, "hidden_act": "silu", "attention_bias": False,
+    "mlp_bias": False, "bos_token_id": 1, "eos_token_id": 2, "torch_dtype": "bfloat16",
+}
+
+
+def run_serving(args):
+    import torch
+
+    from lyapunov_engine_b200 import EngineConfig, LLMEngine, SamplingParams, load_model
+
+    prompt_len, generated = 128, 32
+    loaded = load_model(config=dict(SERVING_MODEL), random_seed=0, dtype="bfloat16", device="cuda:0", max_model_len=1024)
+    rows = []
+    for batch in args.batch_sizes:
+        engine = LLMEngine(loaded, EngineConfig(num_blocks=2048, block_size=BLOCK_SIZE, max_num_seqs=batch,
+                                                max_num_batched_tokens=4096, dtype="bfloat16", device="cuda:0",
+                                                max_model_len=1024))
+        for run in range(3):        # two untimed runs (a prompt step is captured as a graph at its second use), one timed
+            for _ in range(batch):
+                engine.add_request([100 + i for i in range(prompt_len)],
+                                   SamplingParams(temperature=0.0, max_tokens=generated, ignore_eos=True))
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            engine.step()
+            torch.cuda.synchronize()
+            ttft = (time.perf_counter() - t0) * 1e3
+            steps = []
+            while engine.has_unfinished_requests():
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                engine.step()
+                torch.cuda.synchronize()
+                steps.append((time.perf_counter() - t0) * 1e3)
+        total_s = (ttft + sum(steps)) / 1e3
+        rows.append({"batch": batch, "ttft_ms": round(ttft, 3), "itl_ms": round(sum(steps) / max(len(steps), 1), 4),
+                     "decode_steps": len(steps),
+                     "tokens_per_s": round(batch * (prompt_len + generated) / total_s, 1)})
+        print(f"batch {batch:3d}: TTFT {ttft:7.3f} ms   ITL {rows[-1]['itl_ms']:7.4f} ms   {rows[-1]['tokens_per_s']:10.1f} tok/s",
+              file=sys.stderr)
+        del engine
+    print(json.dumps({"only": "serving", "model": "V32000 H1024 I4096 L8 nh16 nkv4 hd64, random weights", "dtype": "bf16",
+                      "prompt": prompt_len, "generated": generated, "rows": rows}))
+    return 0
+
+
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
@@ -650,9 +704,11 @@ def main():
     p.add_argument("--warmup", type=int, default=16)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    p.add_argument("--only", choices=["decode", "prefill", "mixed"], default=None,
+    p.add_argument("--only", choices=["decode", "prefill", "mixed", "serving"], default=None,
                    help="run one kind of step and exit (for profilers and for further sizes); mixed = --batch decoding "
-                        "requests beside one --tokens portion of a prompt in every step")
+                        "requests beside one --tokens portion of a prompt in every step; serving = the reference's "
+                        "serving benchmark (small model, prompts of 128 tokens, 32 generated: TTFT, ITL, tokens/s)")
+    p.add_argument("--batch-sizes", nargs="+", type=int, default=[1, 4, 8, 16], help="with --only serving")
     p.add_argument("--shapes", choices=sorted(SHAPES), default="1b", help="with --only: layer sizes of Llama-3.2-1B, 3.2-3B or 3.1-8B")
     p.add_argument("--batch", type=int, default=8, help="batch of --only decode")
     p.add_argument("--max-num-seqs", type=int, default=0,
@@ -672,6 +728,8 @@ def main():
         return 2
     if not args.only:
         args.warmup = max(args.warmup, 3)
+    if args.only == "serving" and args.impl == "ours":
+        return run_serving(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)

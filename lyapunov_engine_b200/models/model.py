@@ -46,6 +46,7 @@ class Model:
         self._plan_cache()
         # query-tile sizes that the mixers' kernels want listed in every step's integers
         self.tile_sizes: list[int] = sorted({int(t) for b in self.blocks for t in b.mixer.tile_sizes()})
+        self._decode_variants: dict[tuple, tuple] = {}
 
     # ---- what the cache must hold
     def _plan_cache(self) -> None:
@@ -102,17 +103,22 @@ class Model:
         self.runtime = runtime
         for part in self.parts():
             part.bind(get, runtime)
+        self._decode_variants.clear()
 
     # ---- one step
     def decode_variant(self, fill: int, num_decode: int, context_bound: int) -> tuple:
         """The mixers' launch choices that depend on how many of a step's
         one-token requests are real (see Mixer.decode_variant)."""
-        seen = []
-        for b in self.blocks:
-            v = b.mixer.decode_variant(fill, num_decode, context_bound)
-            if v is not None and v not in seen:
-                seen.append(v)
-        return tuple(seen)
+        key = (fill, num_decode, context_bound)
+        found = self._decode_variants.get(key)
+        if found is None:                      # asked at every step: the mixers answer once per shape
+            seen = []
+            for b in self.blocks:
+                v = b.mixer.decode_variant(fill, num_decode, context_bound)
+                if v is not None and v not in seen:
+                    seen.append(v)
+            found = self._decode_variants[key] = tuple(seen)
+        return found
 
     def forward(self, ctx, cache):
         """Logits [wanted rows, vocab] float32 (None when nothing is wanted).
