@@ -697,6 +697,71 @@ def run_serving(args):
     return 0
 
 
+# The reference's kernel benchmark (benchmarks/bench_kernels.py:7-27: CUDA events, the median of 100 launches after
+# 25 warm-ups; 40-41 and 74-79: the grids): RMSNorm with the residual add over widths 2048, 4096, 8192 and 32 to
+# 4,096 tokens; causal attention of one prompt of 512 to 4,096 tokens, 32 heads of 128 in 8 groups (here over the
+# paged cache, pages of 16).  Each row carries the bytes or flops the kernel must move and the share of the measured
+# peak that makes.  Every launch works on a fresh set of tensors until 256 MB have gone round (more than L2 holds).
+def run_kernels(args):
+    import torch
+
+    from lyapunov_engine_b200 import ops
+
+    pk = peaks()
+    dev = "cuda:0"
+
+    def median_us(launch, sets):
+        for i in range(25):
+            launch(i % sets)
+        events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(100)]
+        torch.cuda.synchronize()
+        for i, (a, b) in enumerate(events):
+            a.record()
+            launch(i % sets)
+            b.record()
+        torch.cuda.synchronize()
+        times = sorted(a.elapsed_time(b) * 1e3 for a, b in events)
+        return times[len(times) // 2]
+
+    rows = []
+    for hidden in (2048, 4096, 8192):
+        for tokens in (32, 256, 1024, 4096):
+            nbytes = tokens * hidden * (4 + 2 + 4 + 2) + 4 * hidden       # residual in and out (float32), delta in, normed out
+            sets = max(2, min(64, (256 << 20) // nbytes + 1))
+            resid = [torch.randn(tokens, hidden, device=dev) for _ in range(sets)]
+            delta = [torch.randn(tokens, hidden, device=dev).bfloat16() for _ in range(sets)]
+            out = [torch.empty(tokens, hidden, device=dev, dtype=torch.bfloat16) for _ in range(sets)]
+            weight = torch.ones(hidden, device=dev)
+            us = median_us(lambda i: ops.rmsnorm(out[i], resid[i], delta[i], weight, 1e-5), sets)
+            rows.append({"kernel": "rmsnorm + residual", "hidden": hidden, "tokens": tokens, "us": round(us, 2),
+                         "gbs": round(nbytes / us / 1e3, 1), "hbm_frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)})
+            del resid, delta, out
+    nh, nkv, hd, page = 32, 8, 128, BLOCK_SIZE
+    status = ops.new_status(dev)
+    for seq in (512, 1024, 2048, 4096):
+        pages = seq // page
+        k = torch.randn(pages + 1, nkv, page, hd, device=dev).bfloat16()
+        v = torch.randn(pages + 1, nkv, page, hd, device=dev).bfloat16()
+        q = torch.randn(seq, (nh + 2 * nkv) * hd, device=dev).bfloat16()
+        out = torch.empty(seq, nh * hd, device=dev, dtype=torch.bfloat16)
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, -1).contiguous()
+        cu = torch.tensor([0, seq], dtype=torch.int32, device=dev)
+        ctx = torch.zeros(1, dtype=torch.int32, device=dev)
+        tiles = (seq + 127) // 128
+        tile_request = torch.zeros(tiles, dtype=torch.int32, device=dev)
+        tile_q0 = torch.arange(0, seq, 128, dtype=torch.int32, device=dev)
+        us = median_us(lambda i: ops.attention_prefill_tc_bf16(out, q, q.stride(0), k, v, table, cu, ctx, tile_request, tile_q0,
+                                                               tiles, nh, nkv, hd, page, 0, hd ** -0.5, status), 1)
+        flops = 4 * nh * hd * seq * (seq + 1) // 2
+        rows.append({"kernel": "prefill attention (tcgen05), 32 heads of 128 in 8 groups", "tokens": seq, "us": round(us, 2),
+                     "tflops": round(flops / us / 1e6, 1), "bf16_frac": round(flops / us / 1e6 / pk["bf16_tflops"], 3)})
+    ops.check_status(status)
+    for r in rows:
+        print("  ".join(f"{k}={v}" for k, v in r.items()), file=sys.stderr)
+    print(json.dumps({"only": "kernels", "peaks": pk["source"], "rows": rows}))
+    return 0
+
+
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
@@ -704,10 +769,11 @@ def main():
     p.add_argument("--warmup", type=int, default=16)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    p.add_argument("--only", choices=["decode", "prefill", "mixed", "serving"], default=None,
+    p.add_argument("--only", choices=["decode", "prefill", "mixed", "serving", "kernels"], default=None,
                    help="run one kind of step and exit (for profilers and for further sizes); mixed = --batch decoding "
                         "requests beside one --tokens portion of a prompt in every step; serving = the reference's "
-                        "serving benchmark (small model, prompts of 128 tokens, 32 generated: TTFT, ITL, tokens/s)")
+                        "serving benchmark (small model, prompts of 128 tokens, 32 generated: TTFT, ITL, tokens/s); "
+                        "kernels = its kernel benchmark (RMSNorm and prefill attention over a grid of sizes)")
     p.add_argument("--batch-sizes", nargs="+", type=int, default=[1, 4, 8, 16], help="with --only serving")
     p.add_argument("--shapes", choices=sorted(SHAPES), default="1b", help="with --only: layer sizes of Llama-3.2-1B, 3.2-3B or 3.1-8B")
     p.add_argument("--batch", type=int, default=8, help="batch of --only decode")
@@ -730,6 +796,8 @@ def main():
         args.warmup = max(args.warmup, 3)
     if args.only == "serving" and args.impl == "ours":
         return run_serving(args)
+    if args.only == "kernels" and args.impl == "ours":
+        return run_kernels(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
