@@ -844,6 +844,8 @@ LE_API int le_attention_decode_resident_blocks(int num_splits) {
   return sms * per_sm;
 }
 
+// The pool's last page (num_pages - 1) is the page that nobody owns: a request at position 0 whose first page it
+// is counts as padding of a step of fixed shape; its blocks end at once and its row of `out` is written as zeros.
 // `requests` (optional): the indices of the batch's decode requests; without
 // it requests 0 .. num_requests-1 are taken.  `scratch` holds
 // le_attention_decode_scratch_floats(...) floats; it is used when the keys are

@@ -41,6 +41,9 @@
  *     streams, or the same call from two threads) race on it: order them.
  *   - Apart from that first call, neither this function nor anything it
  *     calls allocates or frees memory.
+ *   - As in le_attention_decode_bf16, the pool's last page (num_pages - 1) is
+ *     the page that nobody owns: a request at position 0 whose block table
+ *     starts with it is taken for padding and gets a row of zeros.
  *
  * Arguments and result are those of le_attention_decode_bf16 without the
  * scratch pointer.
