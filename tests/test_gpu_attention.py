@@ -167,3 +167,27 @@ def test_decode_splits_choice():
             assert 1 <= s <= 4096 // DECODE_KEYS_PER_SPLIT
             if s > 1:
                 assert n * 8 * s <= ops.attention_decode_resident_blocks(hd, s), (hd, n, s)
+
+
+@pytest.mark.parametrize("splits", [1, 3, 8, 20])
+def test_decode_padding_requests_get_zero_rows(splits):
+    """A request at position 0 whose table starts with the page nobody owns
+    (the pool's last) is padding of a step of fixed shape: its blocks end at
+    once, its row comes out as zeros, and the real requests beside it (one of
+    them at position 0 too, on a page of its own) get what they get alone."""
+    from lyapunov_engine_b200 import ops
+    nh, nkv, hd, page = 12, 3, 64, 16
+    c = build_case(torch.bfloat16, nh, nkv, hd, page, [1, 1, 1], [700, 0, 95], seed=41)
+    status = ops.new_status(DEV)
+    null_page = c["k"].shape[0] - 1
+    table = torch.cat([c["table"], torch.full((2, c["table"].shape[1]), null_page, dtype=torch.int32, device=DEV)])
+    cu = torch.arange(6, dtype=torch.int32, device=DEV)
+    ctx = torch.cat([c["ctx"], torch.zeros(2, dtype=torch.int32, device=DEV)])
+    q = torch.cat([c["q"], torch.randn(2, c["q"].shape[1], device=DEV).to(torch.bfloat16)])
+    out = torch.full((5, nh * hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    scratch = torch.full((max(ops.attention_decode_scratch_floats(hd, 5, nh, splits), 1),), float("nan"), device=DEV)
+    ops.attention_decode_bf16(out, scratch, q, q.stride(0), c["k"], c["v"], table, cu, ctx, None, 5, nh, nkv, hd, page,
+                              None, 1.0 / hd ** 0.5, splits, status)
+    ops.check_status(status)
+    torch.testing.assert_close(out[:3].float().cpu(), c["want"], atol=2e-2, rtol=2e-2)
+    assert bool((out[3:] == 0).all())
