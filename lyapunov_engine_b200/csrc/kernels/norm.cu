@@ -185,6 +185,7 @@ int launch(void *out, float *resid, const void *delta, int num_partials, int64_t
     if (PER > 0 && PER <= 2) {                                                                                          \
       if (delta == nullptr || num_partials == 1) LE_NORM_P(VEC, PER, 1);                                                \
       if (num_partials == 2) LE_NORM_P(VEC, PER, 2);                                                                    \
+      if (num_partials == 3) LE_NORM_P(VEC, PER, 3);                                                                    \
       if (num_partials == 4) LE_NORM_P(VEC, PER, 4);                                                                    \
     }                                                                                                                   \
     LE_NORM_P(VEC, PER, 0);                                                                                             \
