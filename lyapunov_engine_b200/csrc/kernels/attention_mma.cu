@@ -120,12 +120,13 @@ __device__ __forceinline__ void load_kv_tile(bf16 *k_tile, bf16 *v_tile, const K
   }
 }
 
-// One warp copies 32 keys whose first key starts a page (pages of 1..32 keys,
+// One warp copies ROWS (16 or 32) keys whose first key starts a page (pages of 1..ROWS keys,
 // a power of two): each lane looks one page of the tile up and the others get
 // it by shuffle, so a tile costs one block-table read per lane.
-__device__ __forceinline__ void load_kv_tile_warp32(bf16 *k_tile, bf16 *v_tile, const KvLayout &kv, int k0, int k_end,
-                                                    int lane, int *status) {
-  const int pages_in_tile = 32 >> kv.page_shift;
+template <int ROWS>
+__device__ __forceinline__ void load_kv_tile_warp(bf16 *k_tile, bf16 *v_tile, const KvLayout &kv, int k0, int k_end,
+                                                  int lane, int *status) {
+  const int pages_in_tile = ROWS >> kv.page_shift;
   int my_page = -1;
   if (lane < pages_in_tile && k0 + (lane << kv.page_shift) < k_end) {
     my_page = kv.table[(k0 >> kv.page_shift) + lane];
@@ -135,7 +136,7 @@ __device__ __forceinline__ void load_kv_tile_warp32(bf16 *k_tile, bf16 *v_tile, 
     }
   }
 #pragma unroll
-  for (int i = 0; i < CPR; ++i) {
+  for (int i = 0; i < ROWS * CPR / 32; ++i) {
     const int c = lane + 32 * i;
     const int row = c / CPR, chunk = c % CPR;
     const int page = __shfl_sync(0xffffffffu, my_page, row >> kv.page_shift);
@@ -395,7 +396,10 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
 constexpr int DC_MAX_CLUSTER = 16;                // the most splits a cluster of blocks merges by itself
 constexpr int DC_WARPS = 4;
 constexpr int DC_THREADS = DC_WARPS * 32;
-constexpr int DC_TILE = 32;                       // keys per warp and pipeline stage
+// Keys per warp and pipeline stage.  16 for the large heads: a block's stages are then 96 KB whatever the head
+// size, two blocks fit a multiprocessor, and every scheduler has two warps to switch between (with one, the
+// dependent instructions of a tile, some thousand per warp at head 128, run at their full latency: 2.4 us a tile).
+constexpr int DC_TILE = HD > 64 ? 16 : 32;
 constexpr int DC_STAGES = 3;                      // stages per warp
 constexpr int DC_WARP_SMEM = DC_STAGES * 2 * DC_TILE * HD;   // bf16 elements per warp
 
@@ -473,7 +477,7 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
   // pages that divide a tile and tiles that start on a page boundary take the cheap loader
   const bool paged_tiles = page_shift >= 0 && page_size <= DC_TILE && (k_begin & (page_size - 1)) == 0;
   auto load_tile = [&](int stage, int i) {
-    if (paged_tiles) load_kv_tile_warp32(k_stage(stage), v_stage(stage), kv, tile_start(i), k_end, lane, status);
+    if (paged_tiles) load_kv_tile_warp<DC_TILE>(k_stage(stage), v_stage(stage), kv, tile_start(i), k_end, lane, status);
     else load_kv_tile<DC_TILE>(k_stage(stage), v_stage(stage), kv, tile_start(i), k_end, lane, 32, status);
   };
   // The first tiles are asked for while the kernel before this one still runs, unless they hold the key at
