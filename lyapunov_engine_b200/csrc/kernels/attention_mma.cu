@@ -399,9 +399,9 @@ constexpr int DC_THREADS = DC_WARPS * 32;
 // Keys per warp and pipeline stage.  16 for the large heads: a block's stages are then 96 KB whatever the head
 // size, two blocks fit a multiprocessor, and every scheduler has two warps to switch between (with one, the
 // dependent instructions of a tile, some thousand per warp at head 128, run at their full latency: 2.4 us a tile).
-constexpr int DC_TILE = HD > 64 ? 16 : 32;
+constexpr int DC_TILE_DEFAULT = HD > 64 ? 16 : 32;
 constexpr int DC_STAGES = 3;                      // stages per warp
-constexpr int DC_WARP_SMEM = DC_STAGES * 2 * DC_TILE * HD;   // bf16 elements per warp
+constexpr int dc_warp_smem(int tile) { return DC_STAGES * 2 * tile * HD; }   // bf16 elements per warp
 
 // One block per (split of the keys, kv head, request).  Its four warps take
 // the split's tiles of 32 keys in turn, each with a cp.async pipeline of its
@@ -410,6 +410,7 @@ constexpr int DC_WARP_SMEM = DC_STAGES * 2 * DC_TILE * HD;   // bf16 elements pe
 // written as the split's partial result (or, with one split, as the result).
 // Scratch per (request, head, split): HD floats of unnormalised output, then
 // the maximum (in log2 units) and the sum.
+template <int DC_TILE>
 __global__ void __launch_bounds__(DC_THREADS)
 attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__restrict__ part_o, float *__restrict__ part_ml,
                         const bf16 *__restrict__ q, int64_t q_stride, const bf16 *__restrict__ k_cache,
@@ -465,7 +466,7 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
   const int tiles_in_split = k_end > k_begin ? (k_end - k_begin + DC_TILE - 1) / DC_TILE : 0;
   const int my_tiles = tiles_in_split > warp ? (tiles_in_split - warp + DC_WARPS - 1) / DC_WARPS : 0;   // tiles warp, warp+4, ...
 
-  bf16 *my_smem = reinterpret_cast<bf16 *>(smem_raw) + warp * DC_WARP_SMEM;
+  bf16 *my_smem = reinterpret_cast<bf16 *>(smem_raw) + warp * (DC_STAGES * 2 * DC_TILE * HD);
   auto k_stage = [&](int s) { return my_smem + s * 2 * DC_TILE * HD; };
   auto v_stage = [&](int s) { return my_smem + s * 2 * DC_TILE * HD + DC_TILE * HD; };
   auto tile_start = [&](int i) { return k_begin + (warp + i * DC_WARPS) * DC_TILE; };
@@ -780,8 +781,17 @@ LE_API int64_t le_attention_decode_scratch_floats(int num_requests, int num_head
 // LYAPUNOV_CLUSTER_MERGE=<n> sets another limit up to 16, 0 switches it off.
 
 
-static size_t decode_smem_bytes() {
-  size_t smem = static_cast<size_t>(DC_WARPS) * DC_WARP_SMEM * sizeof(bf16);
+// LYAPUNOV_DECODE_SMALL_TILES=0: the tile of the head size in every case.
+static bool small_tiles_enabled() {
+  static const bool on = [] {
+    const char *env = getenv("LYAPUNOV_DECODE_SMALL_TILES");
+    return env == nullptr || env[0] != '0';
+  }();
+  return on;
+}
+
+static size_t decode_smem_bytes(int tile = DC_TILE_DEFAULT) {
+  size_t smem = static_cast<size_t>(DC_WARPS) * dc_warp_smem(tile) * sizeof(bf16);
   // the warps' partial results, and behind them the block's own for the merge across a cluster
   const size_t merge = static_cast<size_t>(DC_WARPS * 16 * HD + 2 * DC_WARPS * 16 + 16 * HD + 32) * sizeof(float);
   return merge > smem ? merge : smem;
@@ -800,7 +810,7 @@ static int decode_clusters_resident(int num_splits, size_t smem) {
   config.attrs = attr;
   config.numAttrs = 1;
   int clusters = 0;
-  const bool ok = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel, &config) == cudaSuccess;
+  const bool ok = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<DC_TILE_DEFAULT>, &config) == cudaSuccess;
   cudaGetLastError();                                    // a refusal is an answer, not an error of the caller
   return ok && clusters > 0 ? clusters : 0;
 }
@@ -817,7 +827,7 @@ static bool cluster_splits_fit(int num_splits, size_t smem) {
   if (known[num_splits] == 0) {
     bool fits = true;
     if (num_splits > 8)
-      fits = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+      fits = cudaFuncSetAttribute(attention_decode_kernel<DC_TILE_DEFAULT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
     if (fits) fits = decode_clusters_resident(num_splits, smem) > 0;
     cudaGetLastError();                                  // a refusal above is an answer, not an error of the caller
     known[num_splits] = fits ? 1 : -1;
@@ -833,15 +843,28 @@ static bool cluster_splits_fit(int num_splits, size_t smem) {
 LE_API int le_attention_decode_resident_blocks(int num_splits) {
   const size_t smem = decode_smem_bytes();
   if (smem > 48 * 1024 &&
-      cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+      cudaFuncSetAttribute(attention_decode_kernel<DC_TILE_DEFAULT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
   if (cluster_splits_fit(num_splits, smem)) return num_splits * decode_clusters_resident(num_splits, smem);
   int device = 0, sms = 0, per_sm = 0;
-  if (cudaGetDevice(&device) != cudaSuccess ||
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel, DC_THREADS, smem) != cudaSuccess) {
+  if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  if constexpr (DC_TILE_DEFAULT == 32) {
+    // unsplit keys: where the blocks with 32-key tiles do not fit at once, those with 16-key tiles are launched,
+    // and twice as many of them fit (up to the former's number both take one wave)
+    const size_t small = decode_smem_bytes(16);
+    if (num_splits == 1 && small_tiles_enabled() &&
+        (small <= 48 * 1024 ||
+         cudaFuncSetAttribute(attention_decode_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(small)) == cudaSuccess) &&
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<16>, DC_THREADS, small) == cudaSuccess && per_sm > 0)
+      return sms * per_sm;
+    cudaGetLastError();
+  }
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<DC_TILE_DEFAULT>, DC_THREADS, smem) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
@@ -867,24 +890,49 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
   if (num_kv_heads * row_tiles > 65535 || num_requests > 65535) return le::invalid("le_attention_decode_bf16: the batch is too large for one launch");
   const size_t smem = decode_smem_bytes();
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<DC_TILE_DEFAULT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return le::invalid("le_attention_decode_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   }
   dim3 grid(num_splits, num_kv_heads * row_tiles, num_requests);
   if (cluster_splits_fit(num_splits, smem)) {
     // the splits of a (request, kv head) as one cluster: merged through shared memory, no scratch, no second kernel
-    return le::launch_chained_cluster(attention_decode_kernel, grid, dim3(DC_THREADS), smem, stream, num_splits,
+    return le::launch_chained_cluster(attention_decode_kernel<DC_TILE_DEFAULT>, grid, dim3(DC_THREADS), smem, stream, num_splits,
                                       static_cast<bf16 *>(out), out_stride, static_cast<float *>(nullptr),
                                       static_cast<float *>(nullptr), static_cast<const bf16 *>(q), q_stride,
                                       static_cast<const bf16 *>(k_cache), static_cast<const bf16 *>(v_cache), block_table,
                                       max_blocks, cu_q, ctx_before, requests, num_heads, num_kv_heads, page_size,
                                       page_shift_of(page_size), num_pages, window, scale, num_splits, 1, status);
   }
+  if constexpr (DC_TILE_DEFAULT == 32) {
+    // Unsplit keys and more blocks than the device holds at once, several waves of them: 16 keys a tile make the
+    // blocks half as large, twice as many are resident, and the ends of some overlap the streaming of others
+    // (64 requests of Llama-3.2-1B shapes: 2.28 -> 2.22 ms a step; with split keys or fewer blocks it is slower).
+    static const int64_t resident = [] {
+      int device = 0, sms = 0, per_sm = 0;
+      const size_t bytes = decode_smem_bytes();
+      if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<DC_TILE_DEFAULT>, DC_THREADS, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return int64_t{1} << 40;
+      }
+      return static_cast<int64_t>(sms) * per_sm;
+    }();
+    const size_t small = decode_smem_bytes(16);
+    if (num_splits == 1 && small_tiles_enabled() && static_cast<int64_t>(grid.y) * grid.z > resident &&
+        (small <= 48 * 1024 ||
+         cudaFuncSetAttribute(attention_decode_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(small)) == cudaSuccess))
+      return le::launch_chained(attention_decode_kernel<16>, grid, dim3(DC_THREADS), small, stream, static_cast<bf16 *>(out), out_stride,
+                                static_cast<float *>(nullptr), static_cast<float *>(nullptr), static_cast<const bf16 *>(q), q_stride,
+                                static_cast<const bf16 *>(k_cache), static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q,
+                                ctx_before, requests, num_heads, num_kv_heads, page_size, page_shift_of(page_size), num_pages, window,
+                                scale, 1, 0, status);
+    cudaGetLastError();
+  }
   if (num_splits > 1 && scratch == nullptr) return le::invalid("le_attention_decode_bf16: splitting the keys %d ways needs scratch memory", num_splits);
   if (reinterpret_cast<uintptr_t>(scratch) % 8) return le::invalid("le_attention_decode_bf16: the scratch memory must start on an 8-byte boundary");
   float *part_o = scratch;
   float *part_ml = scratch ? scratch + static_cast<int64_t>(num_requests) * num_heads * num_splits * HD : nullptr;
-  int rc = le::launch_chained(attention_decode_kernel, grid, dim3(DC_THREADS), smem, stream, static_cast<bf16 *>(out), out_stride,
+  int rc = le::launch_chained(attention_decode_kernel<DC_TILE_DEFAULT>, grid, dim3(DC_THREADS), smem, stream, static_cast<bf16 *>(out), out_stride,
                               part_o, part_ml, static_cast<const bf16 *>(q), q_stride, static_cast<const bf16 *>(k_cache),
                               static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before, requests, num_heads,
                               num_kv_heads, page_size, page_shift_of(page_size), num_pages, window, scale, num_splits, 0, status);

@@ -191,3 +191,20 @@ def test_decode_padding_requests_get_zero_rows(splits):
     ops.check_status(status)
     torch.testing.assert_close(out[:3].float().cpu(), c["want"], atol=2e-2, rtol=2e-2)
     assert bool((out[3:] == 0).all())
+
+
+def test_decode_many_unsplit_blocks_take_small_tiles():
+    """More blocks than the device holds at once and unsplit keys: at head
+    size 64 the launcher takes the form of the kernel with 16-key tiles (twice
+    as many blocks fit).  Contexts around tile and page edges, one long."""
+    from lyapunov_engine_b200 import ops
+    nh, nkv, hd, page = 16, 8, 64, 16
+    contexts = [0, 1, 15, 16, 17, 31, 32, 33, 47, 48, 63, 64, 65, 100, 127, 128, 129, 255, 256, 700] * 2
+    assert len(contexts) * nkv > ops.attention_decode_resident_blocks(hd, 2)
+    c = build_case(torch.bfloat16, nh, nkv, hd, page, [1] * len(contexts), contexts, seed=77)
+    status = ops.new_status(DEV)
+    out = torch.full((c["T"], nh * hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.attention_decode_bf16(out, None, c["q"], c["q"].stride(0), c["k"], c["v"], c["table"], c["cu"], c["ctx"], None,
+                              len(contexts), nh, nkv, hd, page, None, 1.0 / hd ** 0.5, 1, status)
+    ops.check_status(status)
+    torch.testing.assert_close(out.float().cpu(), c["want"], atol=2e-2, rtol=2e-2)
