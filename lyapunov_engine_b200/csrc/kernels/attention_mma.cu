@@ -797,78 +797,121 @@ static size_t decode_smem_bytes(int tile = DC_TILE_DEFAULT) {
   return merge > smem ? merge : smem;
 }
 
-// Clusters of `num_splits` of the decode kernel's blocks that the device holds at once; 0 if it takes none.
-static int decode_clusters_resident(int num_splits, size_t smem) {
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(num_splits, 1, 1);
-  config.blockDim = dim3(DC_THREADS);
-  config.dynamicSmemBytes = smem;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = static_cast<unsigned>(num_splits);
-  attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
-  config.attrs = attr;
-  config.numAttrs = 1;
-  int clusters = 0;
-  const bool ok = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<DC_TILE_DEFAULT>, &config) == cudaSuccess;
-  cudaGetLastError();                                    // a refusal is an answer, not an error of the caller
-  return ok && clusters > 0 ? clusters : 0;
+// The decode kernel with tiles of TILE keys: what the device holds of it and how it is launched.
+template <int TILE>
+struct DecodeForm {
+  static size_t smem() { return decode_smem_bytes(TILE); }
+  // the kernel may ask for its shared memory (done once)
+  static bool ready() {
+    static const bool ok = smem() <= 48 * 1024 ||
+                           cudaFuncSetAttribute(attention_decode_kernel<TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                static_cast<int>(smem())) == cudaSuccess;
+    if (!ok) cudaGetLastError();
+    return ok;
+  }
+  // Clusters of `num_splits` blocks that the device holds at once; 0 if it takes none.
+  static int clusters_resident(int num_splits) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(num_splits, 1, 1);
+    config.blockDim = dim3(DC_THREADS);
+    config.dynamicSmemBytes = smem();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(num_splits);
+    attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    int clusters = 0;
+    const bool ok = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<TILE>, &config) == cudaSuccess;
+    cudaGetLastError();                                    // a refusal is an answer, not an error of the caller
+    return ok && clusters > 0 ? clusters : 0;
+  }
+  // Clusters the device holds at once where the splits run as one cluster that merges by itself, else 0 (asked of
+  // the device once per size).
+  static int cluster_count(int num_splits) {
+    static const int limit = [] {
+      const char *env = getenv("LYAPUNOV_CLUSTER_MERGE");
+      const int n = env == nullptr ? 8 : atoi(env);
+      return n < 0 ? 0 : (n > DC_MAX_CLUSTER ? DC_MAX_CLUSTER : n);
+    }();
+    if (num_splits < 2 || num_splits > limit || !ready()) return 0;
+    static int known[DC_MAX_CLUSTER + 1] = {};            // 0: not asked yet, > 0: clusters resident, -1: does not fit
+    if (known[num_splits] == 0) {
+      bool fits = true;
+      if (num_splits > 8)
+        fits = cudaFuncSetAttribute(attention_decode_kernel<TILE>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+      const int clusters = fits ? clusters_resident(num_splits) : 0;
+      cudaGetLastError();                                  // a refusal above is an answer, not an error of the caller
+      known[num_splits] = clusters > 0 ? clusters : -1;
+    }
+    return known[num_splits] > 0 ? known[num_splits] : 0;
+  }
+  static bool cluster_fits(int num_splits) { return cluster_count(num_splits) > 0; }
+  // Blocks the device holds at once when the keys are cut `num_splits` ways: whole clusters where the splits run
+  // as a cluster (clusters stay inside one part of the chip, so fewer blocks fit than the multiprocessors' shared
+  // memory alone would take), single blocks otherwise.  0 if the device could not be asked.
+  static int64_t blocks_resident(int num_splits) {
+    if (!ready()) return 0;
+    if (const int clusters = cluster_count(num_splits)) return static_cast<int64_t>(num_splits) * clusters;
+    static const int64_t single = [] {
+      int device = 0, sms = 0, per_sm = 0;
+      if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<TILE>, DC_THREADS, smem()) != cudaSuccess) {
+        cudaGetLastError();
+        return int64_t{0};
+      }
+      return static_cast<int64_t>(sms) * per_sm;
+    }();
+    return single;
+  }
+  static int launch(dim3 grid, cudaStream_t stream, void *out, int64_t out_stride, float *scratch, const void *q, int64_t q_stride,
+                    const void *k_cache, const void *v_cache, const int32_t *block_table, int max_blocks, const int32_t *cu_q,
+                    const int32_t *ctx_before, const int32_t *requests, int num_requests, int num_heads, int num_kv_heads,
+                    int page_size, int num_pages, int window, float scale, int num_splits, int *status) {
+    if (!ready()) return le::invalid("le_attention_decode_bf16: cannot get %zu bytes of shared memory", smem());
+    if (cluster_fits(num_splits)) {
+      // the splits of a (request, kv head) as one cluster: merged through shared memory, no scratch, no second kernel
+      return le::launch_chained_cluster(attention_decode_kernel<TILE>, grid, dim3(DC_THREADS), smem(), stream, num_splits,
+                                        static_cast<bf16 *>(out), out_stride, static_cast<float *>(nullptr),
+                                        static_cast<float *>(nullptr), static_cast<const bf16 *>(q), q_stride,
+                                        static_cast<const bf16 *>(k_cache), static_cast<const bf16 *>(v_cache), block_table,
+                                        max_blocks, cu_q, ctx_before, requests, num_heads, num_kv_heads, page_size,
+                                        page_shift_of(page_size), num_pages, window, scale, num_splits, 1, status);
+    }
+    if (num_splits > 1 && scratch == nullptr) return le::invalid("le_attention_decode_bf16: splitting the keys %d ways needs scratch memory", num_splits);
+    if (reinterpret_cast<uintptr_t>(scratch) % 8) return le::invalid("le_attention_decode_bf16: the scratch memory must start on an 8-byte boundary");
+    float *part_o = scratch;
+    float *part_ml = scratch ? scratch + static_cast<int64_t>(num_requests) * num_heads * num_splits * HD : nullptr;
+    int rc = le::launch_chained(attention_decode_kernel<TILE>, grid, dim3(DC_THREADS), smem(), stream, static_cast<bf16 *>(out), out_stride,
+                                part_o, part_ml, static_cast<const bf16 *>(q), q_stride, static_cast<const bf16 *>(k_cache),
+                                static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before, requests, num_heads,
+                                num_kv_heads, page_size, page_shift_of(page_size), num_pages, window, scale, num_splits, 0, status);
+    if (rc != 0 || num_splits == 1) return rc;
+    dim3 mgrid(num_heads, num_requests);
+    return le::launch_chained(attention_merge_kernel, mgrid, dim3(HD < 32 ? 32 : (HD > 128 ? 128 : HD)),
+                              (static_cast<size_t>(num_splits) + 1) * sizeof(float), stream,
+                              static_cast<bf16 *>(out), out_stride, static_cast<const float *>(part_o),
+                              static_cast<const float *>(part_ml), cu_q, requests, num_heads, num_splits);
+  }
+};
+
+// Where even the unsplit blocks of the usual form (32-key tiles at head sizes up to 64) are more than the device
+// holds at once, the form with 16-key tiles runs instead: its blocks are half as large, twice as many are resident,
+// the waves are finer and the ends of some blocks overlap the streaming of others (64 requests of Llama-3.2-1B
+// shapes: 2.28 -> 2.22 ms a step; 80 requests, the keys cut in three: 3.24 -> 2.82 ms).  With fewer blocks it is
+// slower: a block alone takes longer per key.  (`blocks`: before splitting.)
+static bool small_form(int64_t blocks) {
+  if constexpr (DC_TILE_DEFAULT != 32) return false;
+  if (!small_tiles_enabled()) return false;
+  return blocks > DecodeForm<DC_TILE_DEFAULT>::blocks_resident(1) && DecodeForm<16>::ready();
 }
 
-// Whether the device can hold a cluster of `num_splits` of the decode kernel's blocks (asked once per size).
-static bool cluster_splits_fit(int num_splits, size_t smem) {
-  static const int limit = [] {
-    const char *env = getenv("LYAPUNOV_CLUSTER_MERGE");
-    const int n = env == nullptr ? 8 : atoi(env);
-    return n < 0 ? 0 : (n > DC_MAX_CLUSTER ? DC_MAX_CLUSTER : n);
-  }();
-  if (num_splits < 2 || num_splits > limit) return false;
-  static int known[DC_MAX_CLUSTER + 1] = {};            // 0: not asked yet, 1: fits, -1: does not
-  if (known[num_splits] == 0) {
-    bool fits = true;
-    if (num_splits > 8)
-      fits = cudaFuncSetAttribute(attention_decode_kernel<DC_TILE_DEFAULT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
-    if (fits) fits = decode_clusters_resident(num_splits, smem) > 0;
-    cudaGetLastError();                                  // a refusal above is an answer, not an error of the caller
-    known[num_splits] = fits ? 1 : -1;
-  }
-  return known[num_splits] > 0;
-}
-
-// Blocks of the decode kernel that the device holds at once when the keys are
-// cut `num_splits` ways: whole clusters where the splits run as a cluster
-// (clusters stay inside one part of the chip, so fewer blocks fit than the
-// multiprocessors' shared memory alone would take), single blocks otherwise.
-// 0 if the device could not be asked.
-LE_API int le_attention_decode_resident_blocks(int num_splits) {
-  const size_t smem = decode_smem_bytes();
-  if (smem > 48 * 1024 &&
-      cudaFuncSetAttribute(attention_decode_kernel<DC_TILE_DEFAULT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
-    cudaGetLastError();
-    return 0;
-  }
-  if (cluster_splits_fit(num_splits, smem)) return num_splits * decode_clusters_resident(num_splits, smem);
-  int device = 0, sms = 0, per_sm = 0;
-  if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
-    cudaGetLastError();
-    return 0;
-  }
-  if constexpr (DC_TILE_DEFAULT == 32) {
-    // unsplit keys: where the blocks with 32-key tiles do not fit at once, those with 16-key tiles are launched,
-    // and twice as many of them fit (up to the former's number both take one wave)
-    const size_t small = decode_smem_bytes(16);
-    if (num_splits == 1 && small_tiles_enabled() &&
-        (small <= 48 * 1024 ||
-         cudaFuncSetAttribute(attention_decode_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(small)) == cudaSuccess) &&
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<16>, DC_THREADS, small) == cudaSuccess && per_sm > 0)
-      return sms * per_sm;
-    cudaGetLastError();
-  }
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<DC_TILE_DEFAULT>, DC_THREADS, smem) != cudaSuccess) {
-    cudaGetLastError();
-    return 0;
-  }
-  return sms * per_sm;
+// Blocks of the decode kernel that the device holds at once when the keys are cut `num_splits` ways, in the usual
+// form (small = 0) or in the form with 16-key tiles that takes over where the usual one's blocks do not all fit.
+LE_API int le_attention_decode_resident_blocks(int num_splits, int small) {
+  if (num_splits < 1) return 0;
+  if (small && DC_TILE_DEFAULT == 32 && small_tiles_enabled()) return static_cast<int>(DecodeForm<16>::blocks_resident(num_splits));
+  return static_cast<int>(DecodeForm<DC_TILE_DEFAULT>::blocks_resident(num_splits));
 }
 
 // The pool's last page (num_pages - 1) is the page that nobody owns: a request at position 0 whose first page it
@@ -888,60 +931,14 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
   const int group = num_heads / num_kv_heads;
   const int row_tiles = (group + 15) / 16;
   if (num_kv_heads * row_tiles > 65535 || num_requests > 65535) return le::invalid("le_attention_decode_bf16: the batch is too large for one launch");
-  const size_t smem = decode_smem_bytes();
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<DC_TILE_DEFAULT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return le::invalid("le_attention_decode_bf16: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-  }
   dim3 grid(num_splits, num_kv_heads * row_tiles, num_requests);
-  if (cluster_splits_fit(num_splits, smem)) {
-    // the splits of a (request, kv head) as one cluster: merged through shared memory, no scratch, no second kernel
-    return le::launch_chained_cluster(attention_decode_kernel<DC_TILE_DEFAULT>, grid, dim3(DC_THREADS), smem, stream, num_splits,
-                                      static_cast<bf16 *>(out), out_stride, static_cast<float *>(nullptr),
-                                      static_cast<float *>(nullptr), static_cast<const bf16 *>(q), q_stride,
-                                      static_cast<const bf16 *>(k_cache), static_cast<const bf16 *>(v_cache), block_table,
-                                      max_blocks, cu_q, ctx_before, requests, num_heads, num_kv_heads, page_size,
-                                      page_shift_of(page_size), num_pages, window, scale, num_splits, 1, status);
-  }
-  if constexpr (DC_TILE_DEFAULT == 32) {
-    // Unsplit keys and more blocks than the device holds at once, several waves of them: 16 keys a tile make the
-    // blocks half as large, twice as many are resident, and the ends of some overlap the streaming of others
-    // (64 requests of Llama-3.2-1B shapes: 2.28 -> 2.22 ms a step; with split keys or fewer blocks it is slower).
-    static const int64_t resident = [] {
-      int device = 0, sms = 0, per_sm = 0;
-      const size_t bytes = decode_smem_bytes();
-      if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
-          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<DC_TILE_DEFAULT>, DC_THREADS, bytes) != cudaSuccess) {
-        cudaGetLastError();
-        return int64_t{1} << 40;
-      }
-      return static_cast<int64_t>(sms) * per_sm;
-    }();
-    const size_t small = decode_smem_bytes(16);
-    if (num_splits == 1 && small_tiles_enabled() && static_cast<int64_t>(grid.y) * grid.z > resident &&
-        (small <= 48 * 1024 ||
-         cudaFuncSetAttribute(attention_decode_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(small)) == cudaSuccess))
-      return le::launch_chained(attention_decode_kernel<16>, grid, dim3(DC_THREADS), small, stream, static_cast<bf16 *>(out), out_stride,
-                                static_cast<float *>(nullptr), static_cast<float *>(nullptr), static_cast<const bf16 *>(q), q_stride,
-                                static_cast<const bf16 *>(k_cache), static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q,
-                                ctx_before, requests, num_heads, num_kv_heads, page_size, page_shift_of(page_size), num_pages, window,
-                                scale, 1, 0, status);
-    cudaGetLastError();
-  }
-  if (num_splits > 1 && scratch == nullptr) return le::invalid("le_attention_decode_bf16: splitting the keys %d ways needs scratch memory", num_splits);
-  if (reinterpret_cast<uintptr_t>(scratch) % 8) return le::invalid("le_attention_decode_bf16: the scratch memory must start on an 8-byte boundary");
-  float *part_o = scratch;
-  float *part_ml = scratch ? scratch + static_cast<int64_t>(num_requests) * num_heads * num_splits * HD : nullptr;
-  int rc = le::launch_chained(attention_decode_kernel<DC_TILE_DEFAULT>, grid, dim3(DC_THREADS), smem, stream, static_cast<bf16 *>(out), out_stride,
-                              part_o, part_ml, static_cast<const bf16 *>(q), q_stride, static_cast<const bf16 *>(k_cache),
-                              static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before, requests, num_heads,
-                              num_kv_heads, page_size, page_shift_of(page_size), num_pages, window, scale, num_splits, 0, status);
-  if (rc != 0 || num_splits == 1) return rc;
-  dim3 mgrid(num_heads, num_requests);
-  return le::launch_chained(attention_merge_kernel, mgrid, dim3(HD < 32 ? 32 : (HD > 128 ? 128 : HD)),
-                            (static_cast<size_t>(num_splits) + 1) * sizeof(float), stream,
-                            static_cast<bf16 *>(out), out_stride, static_cast<const float *>(part_o),
-                            static_cast<const float *>(part_ml), cu_q, requests, num_heads, num_splits);
+  if (small_form(static_cast<int64_t>(grid.y) * grid.z))
+    return DecodeForm<16>::launch(grid, stream, out, out_stride, scratch, q, q_stride, k_cache, v_cache, block_table, max_blocks, cu_q,
+                                  ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size, num_pages, window, scale,
+                                  num_splits, status);
+  return DecodeForm<DC_TILE_DEFAULT>::launch(grid, stream, out, out_stride, scratch, q, q_stride, k_cache, v_cache, block_table,
+                                             max_blocks, cu_q, ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size,
+                                             num_pages, window, scale, num_splits, status);
 }
 
 // ---------------------------------------------------------------- no allocation

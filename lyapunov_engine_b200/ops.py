@@ -549,17 +549,19 @@ def attention_decode_scratch_floats(head_dim: int, num_requests: int, num_heads:
 _decode_resident: dict[tuple, int] = {}
 
 
-def attention_decode_resident_blocks(head_dim: int, num_splits: int) -> int:
+def attention_decode_resident_blocks(head_dim: int, num_splits: int, small: bool = False) -> int:
     """Blocks of the split-key decode attention that the current device holds
     at once when the keys are cut ``num_splits`` ways (asked once per size).
     Splits that run as a thread-block cluster come in whole clusters, and fewer
-    of those fit than twice the multiprocessor count suggests."""
-    key = (torch.cuda.current_device(), head_dim, num_splits)
+    of those fit than twice the multiprocessor count suggests.  ``small``: of
+    the form with 16-key tiles, which the launcher takes where the blocks of the
+    usual form (32-key tiles at head sizes up to 64) do not all fit at once."""
+    key = (torch.cuda.current_device(), head_dim, num_splits, bool(small))
     n = _decode_resident.get(key)
     if n is None:
         fn = attention_lib(head_dim).le_attention_decode_resident_blocks
-        fn.restype, fn.argtypes = c_int, [c_int]
-        n = int(fn(num_splits))
+        fn.restype, fn.argtypes = c_int, [c_int, c_int]
+        n = int(fn(num_splits, 1 if small else 0))
         if n <= 0:
             raise KernelError(f"the device did not say how many decode attention blocks of head size {head_dim} it holds")
         _decode_resident[key] = n

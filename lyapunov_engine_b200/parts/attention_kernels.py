@@ -31,6 +31,9 @@ DECODE_WAVE_US = 5.0            # a wave's fixed time
 DECODE_KEY_US = 0.0075          # a block's time per key of head size 64 (keys and values, latency-bound)
 DECODE_MERGE_US = 1.5           # the second kernel of splits beyond a cluster
 DECODE_BYTES_PER_US = 6.5e6     # what all blocks together read from memory
+DECODE_SMALL_FORM_FILL = 0.9       # the part of its resident blocks that a wave of the form with 16-key tiles can count on
+DECODE_SMALL_FORM_SHARING = 0.4    # what each block sharing the multiprocessor adds to such a block's time per key
+DECODE_SMALL_FORM_CLUSTER_US = 4.0  # what a wave of clusters of such blocks costs more than one of single blocks
 
 
 def tile_sizes() -> list[int]:
@@ -43,7 +46,7 @@ def prepare(head_dim: int) -> None:
     ops.attention_lib(head_dim)
 
 
-def choose_decode_splits(blocks: int, context_bound: int, head_dim: int, resident) -> int:
+def choose_decode_splits(blocks: int, context_bound: int, head_dim: int, resident, resident_small=None, sms: int = 148) -> int:
     """The number of splits with the least estimated time.
 
     ``blocks``: thread blocks before splitting; ``resident(splits)``: blocks the
@@ -51,19 +54,38 @@ def choose_decode_splits(blocks: int, context_bound: int, head_dim: int, residen
     takes a fixed time plus the time of a split's keys, so more splits shorten
     the wave until their blocks no longer fit in one, and then a second wave
     costs more than the shorter keys save.  A step's kernels overlap at their
-    edges, so the last few places of a wave are not counted on.  The constants
-    are measured on decode steps of the 1B layer sizes at 4,096 keys (batches 1
-    to 32, every split count from 1 to 8)."""
+    edges, so the last few places of a wave are not counted on.
+
+    ``resident_small(splits)`` (None: there is no such form): the same of the
+    form with 16-key tiles, which the launcher takes where even the unsplit
+    blocks of the usual form do not fit at once (``sms``: multiprocessors).
+    Its blocks are half as large and twice as many run at once; a block's time
+    per key grows with the blocks that share its multiprocessor, and a cluster
+    of them costs more to merge.
+
+    The constants are measured on decode steps of the 1B layer sizes at 4,096
+    keys: batches 1 to 32 with every split count from 1 to 8, batches 36 to 128
+    in both forms with 1 to 4 splits."""
     by_keys = max(1, (context_bound + DECODE_KEYS_PER_SPLIT - 1) // DECODE_KEYS_PER_SPLIT)
     limit = max(1, min(by_keys, DECODE_MAX_SPLITS))
     # however the keys are cut, all of them cross the memory bus once
     floor = blocks * context_bound * 4 * head_dim / DECODE_BYTES_PER_US
+    small = resident_small is not None and blocks > resident(1)
     best, best_cost = 1, float("inf")
     for splits in range(1, limit + 1):
-        places = max(1, int(DECODE_WAVE_FILL * resident(splits)))
-        waves = -(-blocks * splits // places)
         keys = -(-context_bound // splits)
-        cost = max(floor, waves * (DECODE_WAVE_US + keys * DECODE_KEY_US * head_dim / 64))
+        key_us = DECODE_KEY_US * head_dim / 64
+        if small:
+            places = max(1, int(DECODE_SMALL_FORM_FILL * resident_small(splits)))
+            sharing = min(4.0, min(blocks * splits, places) / sms)
+            wave_us = DECODE_WAVE_US + (DECODE_SMALL_FORM_CLUSTER_US if splits > 1 else 0.0) \
+                + keys * key_us * (1.0 + DECODE_SMALL_FORM_SHARING * sharing)
+        else:
+            # (single blocks fill a wave to the last place; clusters do not)
+            places = max(1, int((DECODE_WAVE_FILL if splits > 1 else 1.0) * resident(splits)))
+            wave_us = DECODE_WAVE_US + keys * key_us
+        waves = -(-blocks * splits // places)
+        cost = max(floor, waves * wave_us)
         if splits > DECODE_CLUSTER_SPLITS:
             cost += DECODE_MERGE_US
         if cost < best_cost - 1e-9:          # on a tie the fewer splits stay
@@ -74,7 +96,9 @@ def choose_decode_splits(blocks: int, context_bound: int, head_dim: int, residen
 def decode_splits(num_requests: int, num_heads: int, num_kv_heads: int, context_bound: int, head_dim: int) -> int:
     group = num_heads // num_kv_heads
     blocks = num_requests * num_kv_heads * ((group + 15) // 16)
-    return choose_decode_splits(blocks, context_bound, head_dim, lambda s: ops.attention_decode_resident_blocks(head_dim, s))
+    small = (lambda s: ops.attention_decode_resident_blocks(head_dim, s, small=True)) if head_dim <= 64 else None
+    return choose_decode_splits(blocks, context_bound, head_dim, lambda s: ops.attention_decode_resident_blocks(head_dim, s),
+                                small, ops.sm_count())
 
 
 def decode_variant(fill: int, num_heads: int, num_kv_heads: int, head_dim: int, context_bound: int):

@@ -29,6 +29,24 @@ def test_a_wave_is_never_overfilled_by_a_cluster():
             assert batch * 8 * s <= 0.97 * resident(s) + 1, (batch, s)
 
 
+# the same of the form with 16-key tiles (four blocks a multiprocessor), which runs where even the unsplit
+# blocks are more than 296
+B200_HD64_SMALL = [592, 592, 561, 568, 560, 558, 546, 568]
+
+
+def test_more_blocks_than_the_device_holds():
+    """Measured at 36 to 128 requests (ms per step with 1, 2, 3 splits where
+    taken): 64 requests 2.22 with 1; 80 requests 3.24, 2.93, 2.82; 96 requests
+    3.41, 3.05; 112 and 128 requests best unsplit; up to 37 requests (296
+    blocks) the usual form holds them all and nothing changes."""
+    small = lambda s: B200_HD64_SMALL[s - 1] if s <= 8 else 592
+    pick = lambda batch: choose_decode_splits(batch * 8, 4096, 64, resident, small, 148)
+    assert [pick(b) for b in (36, 37, 40, 48, 64)] == [1, 1, 1, 1, 1]
+    assert pick(80) == 3 and pick(96) == 2 and pick(112) == 1 and pick(128) == 1
+    for batch in (5, 8, 16, 20, 24, 32):          # not touched by the other form's figures
+        assert pick(batch) == choose_decode_splits(batch * 8, 4096, 64, resident)
+
+
 def test_long_contexts_and_short_ones():
     assert choose_decode_splits(8 * 8, 32768, 64, resident) == 4     # 3 splits: 2.19 ms a step, 4: 1.91 ms
     assert choose_decode_splits(16 * 8, 32768, 64, resident) == 2    # 1 split: 5.43 ms, 2: 3.35 ms
