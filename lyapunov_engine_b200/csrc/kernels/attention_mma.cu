@@ -920,11 +920,14 @@ LE_API int le_attention_decode_resident_blocks(int num_splits, int small) {
 // it requests 0 .. num_requests-1 are taken.  `scratch` holds
 // le_attention_decode_scratch_floats(...) floats; it is used when the keys are
 // cut into more splits than a thread-block cluster merges by itself.
-LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratch, const void *q, int64_t q_stride,
-                                    const void *k_cache, const void *v_cache, const int32_t *block_table, int max_blocks,
-                                    const int32_t *cu_q, const int32_t *ctx_before, const int32_t *requests,
-                                    int num_requests, int num_heads, int num_kv_heads, int page_size, int num_pages,
-                                    int window, float scale, int num_splits, int *status, cudaStream_t stream) {
+// `form`: 0 lets the number of blocks decide between the usual form of the kernel and the one with 16-key tiles
+// (see small_form); 1 asks for the usual form, 2 for the small one where the head size has it (a caller that pads
+// the step with dummy requests knows how many of the blocks are real; the grid does not show it).
+LE_API int le_attention_decode_bf16_form(void *out, int64_t out_stride, float *scratch, const void *q, int64_t q_stride,
+                                         const void *k_cache, const void *v_cache, const int32_t *block_table, int max_blocks,
+                                         const int32_t *cu_q, const int32_t *ctx_before, const int32_t *requests,
+                                         int num_requests, int num_heads, int num_kv_heads, int page_size, int num_pages,
+                                         int window, float scale, int num_splits, int form, int *status, cudaStream_t stream) {
   if (num_requests <= 0) return 0;
   if (num_kv_heads <= 0 || num_heads % num_kv_heads) return le::invalid("le_attention_decode_bf16: %d heads do not divide into %d groups", num_heads, num_kv_heads);
   if (num_splits < 1 || num_splits > MERGE_MAX_SPLITS) return le::invalid("le_attention_decode_bf16: %d splits (1..%d)", num_splits, MERGE_MAX_SPLITS);
@@ -932,13 +935,25 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
   const int row_tiles = (group + 15) / 16;
   if (num_kv_heads * row_tiles > 65535 || num_requests > 65535) return le::invalid("le_attention_decode_bf16: the batch is too large for one launch");
   dim3 grid(num_splits, num_kv_heads * row_tiles, num_requests);
-  if (small_form(static_cast<int64_t>(grid.y) * grid.z))
+  const bool small = form == 0 ? small_form(static_cast<int64_t>(grid.y) * grid.z)
+                               : (form == 2 && DC_TILE_DEFAULT == 32 && small_tiles_enabled() && DecodeForm<16>::ready());
+  if (small)
     return DecodeForm<16>::launch(grid, stream, out, out_stride, scratch, q, q_stride, k_cache, v_cache, block_table, max_blocks, cu_q,
                                   ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size, num_pages, window, scale,
                                   num_splits, status);
   return DecodeForm<DC_TILE_DEFAULT>::launch(grid, stream, out, out_stride, scratch, q, q_stride, k_cache, v_cache, block_table,
                                              max_blocks, cu_q, ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size,
                                              num_pages, window, scale, num_splits, status);
+}
+
+LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratch, const void *q, int64_t q_stride,
+                                    const void *k_cache, const void *v_cache, const int32_t *block_table, int max_blocks,
+                                    const int32_t *cu_q, const int32_t *ctx_before, const int32_t *requests,
+                                    int num_requests, int num_heads, int num_kv_heads, int page_size, int num_pages,
+                                    int window, float scale, int num_splits, int *status, cudaStream_t stream) {
+  return le_attention_decode_bf16_form(out, out_stride, scratch, q, q_stride, k_cache, v_cache, block_table, max_blocks, cu_q,
+                                       ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size, num_pages, window,
+                                       scale, num_splits, 0, status, stream);
 }
 
 // ---------------------------------------------------------------- no allocation

@@ -138,6 +138,9 @@ _EXTRA_ATTENTION_SIGNATURES: dict[str, list] = {
     "le_attention_decode_bf16": [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                  c_int, c_void_p, c_void_p],
+    "le_attention_decode_bf16_form": [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                      c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                      c_int, c_int, c_void_p, c_void_p],
 }
 
 
@@ -570,9 +573,12 @@ def attention_decode_resident_blocks(head_dim: int, num_splits: int, small: bool
 
 def attention_decode_bf16(out, scratch, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, requests,
                           num_requests, num_heads, num_kv_heads, head_dim, page_size, window, scale, num_splits,
-                          status) -> None:
+                          status, small_form=None) -> None:
     """Split-key tensor-core attention for requests that bring one token.
-    ``scratch``: float32, attention_decode_scratch_floats(...) elements."""
+    ``scratch``: float32, attention_decode_scratch_floats(...) elements.
+    ``small_form``: None lets the launcher choose between the kernel's usual
+    form and the one with 16-key tiles by the number of blocks; a caller that
+    knows how many of the requests are real says True or False."""
     _need_cuda(out, q, k_cache, v_cache, block_table, scratch)
     lib = attention_lib(head_dim)
     assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[1] == num_heads * head_dim
@@ -580,11 +586,12 @@ def attention_decode_bf16(out, scratch, q, q_stride, k_cache, v_cache, block_tab
     if num_splits > 1:
         assert scratch is not None and scratch.dtype == torch.float32
         assert scratch.numel() >= attention_decode_scratch_floats(head_dim, num_requests, num_heads, num_splits)
-    _check(lib.le_attention_decode_bf16(_ptr(out), out.stride(0), _ptr(scratch), _ptr(q), q_stride, _ptr(k_cache),
-                                        _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
-                                        _ptr(ctx_before), _ptr(requests), num_requests, num_heads, num_kv_heads,
-                                        page_size, k_cache.shape[0], int(window or 0), float(scale), num_splits,
-                                        _ptr(status), _stream()), "le_attention_decode_bf16", lib,
+    form = 0 if small_form is None else (2 if small_form else 1)
+    _check(lib.le_attention_decode_bf16_form(_ptr(out), out.stride(0), _ptr(scratch), _ptr(q), q_stride, _ptr(k_cache),
+                                             _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
+                                             _ptr(ctx_before), _ptr(requests), num_requests, num_heads, num_kv_heads,
+                                             page_size, k_cache.shape[0], int(window or 0), float(scale), num_splits,
+                                             form, _ptr(status), _stream()), "le_attention_decode_bf16", lib,
            launches=2 if num_splits > 1 else 1)       # the attention kernel and the merge
 
 

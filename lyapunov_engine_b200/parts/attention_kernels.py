@@ -93,9 +93,20 @@ def choose_decode_splits(blocks: int, context_bound: int, head_dim: int, residen
     return best
 
 
+def decode_blocks(num_requests: int, num_heads: int, num_kv_heads: int) -> int:
+    """Thread blocks of the decode kernel before the keys are split."""
+    return num_requests * num_kv_heads * ((num_heads // num_kv_heads + 15) // 16)
+
+
+def decode_small_form(num_requests: int, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    """Whether the kernel's form with 16-key tiles runs: where the head size
+    has it and even the unsplit blocks of the real requests are more than the
+    device holds of the usual form at once."""
+    return head_dim <= 64 and decode_blocks(num_requests, num_heads, num_kv_heads) > ops.attention_decode_resident_blocks(head_dim, 1)
+
+
 def decode_splits(num_requests: int, num_heads: int, num_kv_heads: int, context_bound: int, head_dim: int) -> int:
-    group = num_heads // num_kv_heads
-    blocks = num_requests * num_kv_heads * ((group + 15) // 16)
+    blocks = decode_blocks(num_requests, num_heads, num_kv_heads)
     small = (lambda s: ops.attention_decode_resident_blocks(head_dim, s, small=True)) if head_dim <= 64 else None
     return choose_decode_splits(blocks, context_bound, head_dim, lambda s: ops.attention_decode_resident_blocks(head_dim, s),
                                 small, ops.sm_count())
@@ -122,12 +133,13 @@ def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, window, scale) -> 
         if ctx.num_decode:
             real = min(ctx.decode_fill, ctx.num_decode) if SPLITS_BY_FILL else 0     # dummy requests finish at once
             splits = decode_splits(real or ctx.num_decode, num_heads, num_kv_heads, ctx.context_bound, head_dim)
+            small = decode_small_form(real or ctx.num_decode, num_heads, num_kv_heads, head_dim)
             floats = ops.attention_decode_scratch_floats(head_dim, ctx.num_decode, num_heads, splits)
             scratch = ctx.workspace.get("attention_scratch", (floats,), torch.float32) if floats else None
             requests = None if ctx.num_decode == ctx.num_requests else ctx.decode_requests
             ops.attention_decode_bf16(out, scratch, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before,
                                       requests, ctx.num_decode, num_heads, num_kv_heads, head_dim, kv.page_size,
-                                      window, scale, splits, ctx.status)
+                                      window, scale, splits, ctx.status, small_form=small)
         return
     req, q0, n_tiles, _ = ctx.tiles[GENERIC_TILE]
     ops.attention_generic(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0, n_tiles,
