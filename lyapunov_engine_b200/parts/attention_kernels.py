@@ -113,12 +113,16 @@ def decode_splits(num_requests: int, num_heads: int, num_kv_heads: int, context_
 
 
 def decode_variant(fill: int, num_heads: int, num_kv_heads: int, head_dim: int, context_bound: int):
-    """The split count of a step in which ``fill`` of the one-token requests
-    are real: dummy requests finish at once, so the real ones alone fill the
-    waves (9 real requests in a step of 16 take 3 splits, 16 take 2)."""
+    """The split count (and the kernel's form, where it is not the usual one)
+    of a step in which ``fill`` of the one-token requests are real: dummy
+    requests finish at once, so the real ones alone fill the waves (9 real
+    requests in a step of 16 take 3 splits, 16 take 2)."""
     if not SPLITS_BY_FILL or not ops.attention_mma_available(head_dim):
         return None
-    return decode_splits(max(1, fill), num_heads, num_kv_heads, context_bound, head_dim)
+    fill = max(1, fill)
+    splits = decode_splits(fill, num_heads, num_kv_heads, context_bound, head_dim)
+    # (the kernel's form follows the real requests too)
+    return (splits, "small") if decode_small_form(fill, num_heads, num_kv_heads, head_dim) else splits
 
 
 def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, window, scale) -> None:

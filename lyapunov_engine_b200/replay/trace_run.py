@@ -130,8 +130,8 @@ def main(argv=None) -> int:
                        "peak_used_pages": peak_used, "steps": runner.num_steps, "graph_steps": runner.num_graph_steps,
                        "decode_graphs_captured": sum(g.graph is not None for g in runner._graphs.values()),
                        # (rows, width of the block tables, what the mixers launch differently in a partly filled step)
-                       "decode_graph_shapes": sorted([k[0], k[1], list(k[2])] for k, g in runner._graphs.items()
-                                                     if g.graph is not None),
+                       "decode_graph_shapes": sorted(([k[0], k[1], list(k[2])] for k, g in runner._graphs.items()
+                                                      if g.graph is not None), key=repr),
                        "prompt_graphs_captured": sum(g.graph is not None for g in runner._prompt_graphs.values())}, f)
         problem = manager.audit()
         if problem:
