@@ -248,10 +248,22 @@ class ModelRunner:
         return min(width, max(self.fixed_max_blocks)) if self.fixed_max_blocks else width
 
     def _bucket(self, n: int) -> int:
+        """Rows of the captured step that takes ``n`` requests: powers of two,
+        and from 48 on the steps between them too (48, 96, 192, ...: the matrix
+        products of 33 to 48 rows cost a tenth less than those of 64)."""
         b = 1
         while b < n:
             b *= 2
+        if b >= 64 and n <= b // 4 * 3:
+            b = b // 4 * 3
         return min(b, max(self.max_num_seqs, n))
+
+    def _bucket_below(self, bucket: int) -> int:
+        """The largest number of requests that a smaller captured step takes."""
+        n = bucket - 1
+        while n > 0 and self._bucket(n) >= bucket:
+            n -= 1
+        return n
 
     def _workspace_for_graphs(self):
         if self._graph_workspace is None:
@@ -307,6 +319,8 @@ class ModelRunner:
             buckets, b = [], 1
             while b < self.max_num_seqs:
                 buckets.append(b)
+                if b >= 32 and b // 2 * 3 < self.max_num_seqs:
+                    buckets.append(b // 2 * 3)
                 b *= 2
             buckets.append(self.max_num_seqs)
         if contexts is None:
@@ -323,7 +337,7 @@ class ModelRunner:
                 # the full step first, then what partly filled ones launch differently (fills down to where the
                 # next smaller bucket takes over)
                 seen = set()
-                for fill in range(bucket, bucket // 2, -1):
+                for fill in range(bucket, self._bucket_below(bucket), -1):
                     variant = self.model.decode_variant(fill, bucket, bound)
                     if variant in seen:
                         continue
