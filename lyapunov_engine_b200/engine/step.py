@@ -308,7 +308,7 @@ class ModelRunner:
     def warm_up(self, contexts=None, buckets=None) -> int:
         """Captures the decode graphs a server will need before the first
         request arrives, so that no request pays for a first use: one graph
-        per batch bucket (powers of two up to ``max_num_seqs``) and per width
+        per batch bucket (powers of two, and 48, 96, ... between them, up to ``max_num_seqs``) and per width
         of the block tables (one for every doubling of the context up to
         ``max_model_len``, or those that hold the given ``contexts``).  The
         steps it runs hold dummy requests only: they read and write the page
