@@ -50,6 +50,32 @@ def prompt_bucket(tokens: int) -> int:
     return (tokens + step - 1) // step * step
 
 
+def padded_portion(count: int, bucket: int) -> int:
+    """Rows that a prompt portion of ``count`` tokens takes in a captured step
+    beside ``bucket`` rows of decoded tokens.  The portion is padded to a round
+    number, or, where that saves a tile of 128 rows (the matrix products work
+    in such tiles), the step's rows as a whole are: a portion of 504 tokens
+    beside 8 decoded ones is a step of 512 rows, not of 512 + 8 (2.47 -> 2.23
+    ms at Llama-3.2-1B shapes)."""
+    padded, whole = prompt_bucket(count), prompt_bucket(count + bucket) - bucket
+    if (whole + bucket + 127) // 128 < (padded + bucket + 127) // 128:
+        return whole
+    return padded
+
+
+def decode_bucket(n: int, max_num_seqs: int) -> int:
+    """Rows of the captured step that takes ``n`` requests: powers of two, and
+    from 48 on the steps between them too (48, 96, 192, ...: the matrix
+    products of 33 to 48 rows cost a tenth less than those of 64); never more
+    than ``max_num_seqs`` unless ``n`` itself is."""
+    b = 1
+    while b < n:
+        b *= 2
+    if b >= 64 and n <= b // 4 * 3:
+        b = b // 4 * 3
+    return min(b, max(max_num_seqs, n))
+
+
 class StepContext:
     """The step's integers on the device (views into one buffer) and the few
     numbers the host keeps."""
@@ -248,15 +274,7 @@ class ModelRunner:
         return min(width, max(self.fixed_max_blocks)) if self.fixed_max_blocks else width
 
     def _bucket(self, n: int) -> int:
-        """Rows of the captured step that takes ``n`` requests: powers of two,
-        and from 48 on the steps between them too (48, 96, 192, ...: the matrix
-        products of 33 to 48 rows cost a tenth less than those of 64)."""
-        b = 1
-        while b < n:
-            b *= 2
-        if b >= 64 and n <= b // 4 * 3:
-            b = b // 4 * 3
-        return min(b, max(self.max_num_seqs, n))
+        return decode_bucket(n, self.max_num_seqs)
 
     def _bucket_below(self, bucket: int) -> int:
         """The largest number of requests that a smaller captured step takes."""
@@ -369,12 +387,7 @@ class ModelRunner:
             return None
         singles = len(entries) - 1
         bucket = self._bucket(singles) if singles else 0
-        # The portion is padded to a round number, or, where that saves a tile of 128 rows (the products work in
-        # such tiles), the step's rows as a whole are: a portion of 504 tokens beside 8 decoded ones is a step of
-        # 512 rows, not of 512 + 8 (2.47 -> 2.23 ms at Llama-3.2-1B shapes)
-        padded, whole = prompt_bucket(e.count), prompt_bucket(e.count + bucket) - bucket
-        if (whole + bucket + 127) // 128 < (padded + bucket + 127) // 128:
-            padded = whole
+        padded = padded_portion(e.count, bucket)
         if e.start + padded > self.max_model_len:
             return None                                   # the dummies' positions would run past the tables
         if 1 + bucket > self._most_requests or padded + bucket > self._most_rows:
